@@ -1,0 +1,1159 @@
+// The C ABI (include/fortis_b200.h): process-wide session state, run-time configuration, host-array staging, the
+// step driver (which kernels run for which model / precision / fusion mode) and CUDA-graph replay.
+//
+// Mirrors, entry by entry, the generated shim (driver/fortis_shim.py:61-133), the generated gather/scatter host
+// entries (driver/fortis_gather_emit.py:37-48, 63-70, 84-97), the run-time-extent stub (driver/fortis_stub.c) and
+// the runtime (runtime/fortis_rt.c:5-75).  Like the reference it is single-threaded by contract: one host thread,
+// file-scope state, one stream.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/fortis_b200.h"
+#include "fortis_device.cuh"
+#include "fortis_kernels.h"
+#include "fortis_model.h"
+#include "fortis_plan.h"
+
+using namespace fortis;
+
+int fortis_capturing = 0;
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------------------
+// errors: the reference prints and carries on; so do we, and additionally keep the last message
+// ---------------------------------------------------------------------------------------------------------------
+int g_err = 0;
+std::string g_errmsg;
+void set_error(const std::string& msg) {
+  g_err = -1;
+  g_errmsg = msg;
+  std::fprintf(stderr, "fortis: %s\n", msg.c_str());
+}
+bool cuda_ok(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return true;
+  set_error(std::string(what) + ": " + cudaGetErrorString(e));
+  return false;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// stream and pool  (runtime/fortis_rt.c:5-40)
+// ---------------------------------------------------------------------------------------------------------------
+cudaStream_t g_stream = nullptr;
+cudaStream_t stream() {
+  if (!g_stream) cuda_ok(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+  return g_stream;
+}
+
+constexpr int kPool = 256;
+struct PoolSlot { long n; void* p; int used; } g_pool[kPool];
+
+void* pool_alloc(long n) {
+  if (n <= 0) n = 1;
+  int best = -1;
+  for (int i = 0; i < kPool; i++)
+    if (g_pool[i].p && !g_pool[i].used && g_pool[i].n >= n && (best < 0 || g_pool[i].n < g_pool[best].n)) best = i;
+  if (best >= 0) { g_pool[best].used = 1; return g_pool[best].p; }
+  for (int attempt = 0; attempt < 2; attempt++) {
+    for (int i = 0; i < kPool; i++)
+      if (!g_pool[i].p) {
+        if (cudaMalloc(&g_pool[i].p, (size_t)n) == cudaSuccess) { g_pool[i].n = n; g_pool[i].used = 1; return g_pool[i].p; }
+        g_pool[i].p = nullptr;
+        break;
+      }
+    cudaGetLastError();
+    for (int i = 0; i < kPool; i++)
+      if (g_pool[i].p && !g_pool[i].used) { cudaFree(g_pool[i].p); g_pool[i].p = nullptr; g_pool[i].n = 0; }
+  }
+  std::fprintf(stderr, "fortis_alloc: cudaMalloc(%ld) failed\n", n);
+  return nullptr;
+}
+void pool_free(void* p) {
+  if (!p) return;
+  for (int i = 0; i < kPool; i++) if (g_pool[i].p == p) { g_pool[i].used = 0; return; }
+  cudaFree(p);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// session
+// ---------------------------------------------------------------------------------------------------------------
+struct PlanDev {
+  IoPlanHost h;
+  IoPlanDev* hdr = nullptr;
+  void* items = nullptr;                     // Access[n] (gather) or StoreTarget[nstores] (scatter)
+  std::vector<void*> stage;                  // device staging buffer per array (host-resident arrays only)
+  std::vector<long long> stage_elems;
+  std::vector<const void*> reg;              // pinned registration: nullptr = none yet, (void*)1 = never again
+  std::vector<const void*> cur;              // this call's pointers
+  std::vector<char> on_dev;
+  void* vec_dev[kMaxVecs] = {};
+};
+
+struct Session {
+  JValue jg, js, jl, jk, jl2;
+  bool have_g = false, have_s = false, have_l = false, have_k = false, have_l2 = false;
+  bool planned = false, env_loaded = false;
+  LoopInfo loop;
+  PlanDev G, S;
+  std::map<std::string, std::pair<std::vector<char>, int>> vectors;   // name -> (bytes, elt)
+
+  bool have_model = false, model_on_dev = false;
+  ModelHost model;
+  std::vector<float*> dW, dB;
+  float *d_in_div = nullptr, *d_out_mul = nullptr, *d_relu_mask = nullptr;
+  bool small_ok = false;
+  TcModel* tc = nullptr;
+  ConvModel* conv = nullptr;
+  int conv_shape[4] = {0, 0, 0, 0};
+
+  int precision = PREC_F32;
+  bool fuse = true, graph = false, async = false, want_checksum = false;
+  long long begin_count = -1;
+
+  long long buf_rows = 0;
+  float *din = nullptr, *dout = nullptr, *act0 = nullptr, *act1 = nullptr;
+  float *X_pinned = nullptr, *Y_pinned = nullptr;
+  long long pinned_rows = 0;
+  bool pack_pending = false, gather_pending = false;
+  int gather_args[8] = {};
+  const void *reg_in = nullptr, *reg_out = nullptr;
+  bool nopin = false;
+
+  double *d_partials = nullptr, *d_sum = nullptr;
+  int* d_status = nullptr;
+  long long partials_cap = 0;
+
+  cudaGraphExec_t gexec = nullptr;
+  std::string gkey;
+  int ncalls = 0;
+};
+Session* g_S = nullptr;
+Session& S() {
+  if (!g_S) g_S = new Session();
+  return *g_S;
+}
+
+std::string read_file(const std::string& path) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) throw std::runtime_error("cannot open " + path);
+  std::stringstream ss;
+  ss << f.rdbuf();
+  return ss.str();
+}
+
+void free_plan(PlanDev& P) {
+  for (size_t i = 0; i < P.reg.size(); i++)
+    if (P.reg[i] && P.reg[i] != (const void*)1) { cudaHostUnregister((void*)P.reg[i]); cudaGetLastError(); }
+  for (void* p : P.stage) pool_free(p);
+  for (void*& v : P.vec_dev) { pool_free(v); v = nullptr; }
+  pool_free(P.hdr); pool_free(P.items);
+  P = PlanDev();
+}
+
+void drop_graph() {
+  Session& s = S();
+  if (s.gexec) { cudaGraphExecDestroy(s.gexec); s.gexec = nullptr; }
+  s.gkey.clear();
+  s.ncalls = 0;
+}
+
+void free_model_dev() {
+  Session& s = S();
+  for (float* p : s.dW) pool_free(p);
+  for (float* p : s.dB) pool_free(p);
+  s.dW.clear(); s.dB.clear();
+  pool_free(s.d_in_div); pool_free(s.d_out_mul); pool_free(s.d_relu_mask);
+  s.d_in_div = s.d_out_mul = s.d_relu_mask = nullptr;
+  if (s.tc) { tc_model_destroy(s.tc); s.tc = nullptr; }
+  if (s.conv) { conv_model_destroy(s.conv); s.conv = nullptr; }
+  s.model_on_dev = false;
+  s.small_ok = false;
+}
+
+void upload_plan(PlanDev& P) {
+  IoPlanDev hd;
+  std::memset(&hd, 0, sizeof hd);
+  hd.n = P.h.n;
+  hd.nscalars = (int)P.h.scalars.size();
+  hd.nstores = (int)P.h.stores.size();
+  hd.has_prog = P.h.prog.nops > 0;
+  for (size_t i = 0; i < P.h.scalars.size(); i++) { hd.scalars[i] = P.h.scalars[i]; hd.scalar_ids[i] = P.h.scalar_ids[i]; }
+  hd.prog = P.h.prog;
+  P.hdr = (IoPlanDev*)pool_alloc(sizeof hd);
+  if (!P.hdr) throw std::runtime_error("out of device memory for a layout plan");
+  cudaMemcpy(P.hdr, &hd, sizeof hd, cudaMemcpyHostToDevice);
+  if (!P.h.is_scatter) {
+    const size_t nb = sizeof(Access) * P.h.slots.size();
+    P.items = pool_alloc((long)nb);
+    if (nb) cudaMemcpy(P.items, P.h.slots.data(), nb, cudaMemcpyHostToDevice);
+  } else {
+    const size_t nb = sizeof(StoreTarget) * P.h.stores.size();
+    P.items = pool_alloc((long)nb);
+    if (nb) cudaMemcpy(P.items, P.h.stores.data(), nb, cudaMemcpyHostToDevice);
+  }
+  const size_t na = P.h.arrays.size();
+  P.stage.assign(na, nullptr); P.stage_elems.assign(na, 0); P.reg.assign(na, nullptr); P.cur.assign(na, nullptr);
+  P.on_dev.assign(na, 0);
+}
+
+void load_env_config() {
+  Session& s = S();
+  if (s.env_loaded) return;
+  s.env_loaded = true;
+  const struct { const char* env; const char* key; } E[] = {{"FORTIS_GATHER_JSON", "gather"}, {"FORTIS_SCATTER_JSON", "scatter"},
+      {"FORTIS_LOOP_JSON", "loop"}, {"FORTIS_KDIST_JSON", "kdist"}, {"FORTIS_LIFT2D_JSON", "lift2d"}};
+  for (auto& e : E) {
+    const char* v = std::getenv(e.env);
+    if (v && *v) fortis_configure_file(e.key, v);
+  }
+  if (!s.have_model) { const char* m = std::getenv("FORTIS_MODEL"); if (m && *m) fortis_load_model(m); }
+  if (const char* p = std::getenv("FORTIS_PRECISION")) fortis_set_option("precision", p);
+  if (std::getenv("FORTIS_GRAPH")) s.graph = true;                  // driver/fortis_shim.py:84
+  if (const char* b = std::getenv("FORTIS_BATCH")) if (s.begin_count < 0) s.begin_count = std::atoll(b);
+}
+
+void ensure_plans() {
+  Session& s = S();
+  if (!s.have_g && !s.have_s && !s.have_l && !s.have_l2) load_env_config();
+  if (s.planned) return;
+  free_plan(s.G); free_plan(s.S);
+  if (s.have_l2) {
+    make_lift2d_plans(s.jl2, &s.G.h, &s.S.h, &s.loop);
+  } else {
+    if (s.have_l) s.loop = make_loop(&s.jl, s.have_k ? &s.jk : nullptr);
+    if (s.have_g) { if (!s.have_l) throw std::runtime_error("gather.json needs loop.json"); s.G.h = make_io_plan(s.jg, s.loop, false); }
+    if (s.have_s) { if (!s.have_l) throw std::runtime_error("scatter.json needs loop.json"); s.S.h = make_io_plan(s.js, s.loop, true); }
+  }
+  if (s.G.h.ok) upload_plan(s.G);
+  if (s.S.h.ok) upload_plan(s.S);
+  // per-feature vectors of a boundary
+  for (PlanDev* P : {&s.G, &s.S})
+    for (size_t v = 0; v < P->h.vec_names.size(); v++) {
+      auto it = s.vectors.find(P->h.vec_names[v]);
+      if (it == s.vectors.end()) throw std::runtime_error("lift2d vector \"" + P->h.vec_names[v] + "\" was not set (fortis_set_vector)");
+      if (it->second.second != P->h.prog.tv_double) throw std::runtime_error("lift2d vector \"" + P->h.vec_names[v] + "\" has the wrong element type");
+      P->vec_dev[v] = pool_alloc((long)it->second.first.size());
+      cudaMemcpy(P->vec_dev[v], it->second.first.data(), it->second.first.size(), cudaMemcpyHostToDevice);
+    }
+  s.planned = true;
+  drop_graph();
+}
+
+void ensure_model() {
+  Session& s = S();
+  if (!s.have_model) { load_env_config(); }
+  if (!s.have_model) throw std::runtime_error("no model loaded (fortis_load_model or FORTIS_MODEL)");
+  if (s.model_on_dev) return;
+  cudaStream_t st = stream();
+  for (auto& L : s.model.layers) {
+    float* w = (float*)pool_alloc((long)(L.W.size() * 4));
+    float* b = (float*)pool_alloc((long)(L.b.size() * 4));
+    if (!w || !b) throw std::runtime_error("out of device memory for weights");
+    cudaMemcpy(w, L.W.data(), L.W.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(b, L.b.data(), L.b.size() * 4, cudaMemcpyHostToDevice);
+    s.dW.push_back(w); s.dB.push_back(b);
+  }
+  auto up = [&](const std::vector<float>& v) -> float* {
+    if (v.empty()) return nullptr;
+    float* d = (float*)pool_alloc((long)(v.size() * 4));
+    cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    return d;
+  };
+  s.d_in_div = up(s.model.in_div); s.d_out_mul = up(s.model.out_mul); s.d_relu_mask = up(s.model.relu_mask);
+  if (s.model.is_mlp()) {
+    std::vector<int> dims{s.model.n_in()};
+    for (auto& L : s.model.layers) dims.push_back(L.cout);
+    const int nl = (int)s.model.layers.size();
+    if (small_mlp_supported(nl, dims.data()) && s.model.relu_mask.empty()) {
+      std::vector<float> img(kSmallConstFloats, 0.f);
+      std::vector<const float*> W, B;
+      for (auto& L : s.model.layers) { W.push_back(L.W.data()); B.push_back(L.b.data()); }
+      const int nf = small_mlp_pack(nl, dims.data(), W.data(), B.data(), s.model.in_div.empty() ? nullptr : s.model.in_div.data(),
+                                    s.model.out_mul.empty() ? nullptr : s.model.out_mul.data(), img.data());
+      if (cuda_ok(small_mlp_upload(img.data(), nf, st), "small-MLP constant upload")) s.small_ok = true;
+      cudaStreamSynchronize(st);
+    }
+    if (s.precision != PREC_F32) {
+      std::string err;
+      s.tc = tc_model_create(s.model, s.precision, st, &err);
+      if (!s.tc) throw std::runtime_error("precision " + std::string(s.precision == PREC_BF16 ? "bf16" : "fp8w") +
+                                          " needs the tensor-core kernel, which cannot take this model: " + err);
+    }
+  } else if (s.model.is_conv()) {
+    std::string err;
+    s.conv = conv_model_create(s.model, s.precision, st, &err);
+    if (!s.conv) throw std::runtime_error("conv3d model: " + err);
+  } else {
+    throw std::runtime_error("a model must be all Linear or all Conv3d layers");
+  }
+  s.model_on_dev = true;
+  drop_graph();
+}
+
+long long model_rows() {
+  Session& s = S();
+  if (s.model.is_conv()) return (long long)s.conv_shape[0] * s.conv_shape[1] * s.conv_shape[2] * s.conv_shape[3];
+  if (s.planned && (s.G.h.ok || s.S.h.ok || s.have_l)) {
+    if (s.begin_count >= 0 && s.have_l && !s.have_l2) return s.begin_count * s.loop.nk;   // run-time extent
+    return s.loop.count * s.loop.nk;
+  }
+  return s.begin_count > 0 ? s.begin_count : 1;
+}
+
+void ensure_buffers(long long rows) {
+  Session& s = S();
+  if (rows <= s.buf_rows && s.din) return;
+  pool_free(s.din); pool_free(s.dout); pool_free(s.act0); pool_free(s.act1);
+  int wmax = 1;
+  for (auto& L : s.model.layers) wmax = L.cout > wmax ? L.cout : wmax;
+  const long long nin = s.model.n_in(), nout = s.model.n_out();
+  s.din = (float*)pool_alloc(rows * nin * 4);
+  s.dout = (float*)pool_alloc(rows * nout * 4);
+  const bool need_act = s.model.is_mlp() && s.model.layers.size() > 1;
+  s.act0 = need_act ? (float*)pool_alloc(rows * wmax * 4) : nullptr;
+  s.act1 = need_act && s.model.layers.size() > 2 ? (float*)pool_alloc(rows * wmax * 4) : nullptr;
+  if (!s.din || !s.dout || (need_act && !s.act0)) throw std::runtime_error("out of device memory for the model buffers");
+  s.buf_rows = rows;
+  drop_graph();
+}
+
+void ensure_aux(long long npartials) {
+  Session& s = S();
+  if (!s.d_sum) {
+    s.d_sum = (double*)pool_alloc(sizeof(double));
+    s.d_status = (int*)pool_alloc(sizeof(int));
+    cudaMemset(s.d_sum, 0, sizeof(double));
+    cudaMemset(s.d_status, 0, sizeof(int));
+  }
+  if (npartials > s.partials_cap) {
+    pool_free(s.d_partials);
+    s.d_partials = (double*)pool_alloc(npartials * (long long)sizeof(double));
+    s.partials_cap = npartials;
+    drop_graph();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host-array staging  (driver/fortis_gather_emit.py:37-48, 66-68, 86-97)
+// ---------------------------------------------------------------------------------------------------------------
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+// pin once; an array whose address moves between calls is a temporary: unpin it and never pin it again
+void pin_policy(PlanDev& P, int ai, const void* H, size_t bytes) {
+  if (P.reg[ai] == (const void*)1 || P.reg[ai] == H) return;
+  if (P.reg[ai]) { cudaHostUnregister((void*)P.reg[ai]); cudaGetLastError(); P.reg[ai] = (const void*)1; return; }
+  if (std::getenv("FORTIS_NO_PIN")) { P.reg[ai] = (const void*)1; return; }
+  if (cudaHostRegister((void*)H, bytes, cudaHostRegisterDefault) == cudaSuccess) P.reg[ai] = H;
+  else { cudaGetLastError(); P.reg[ai] = (const void*)1; }
+}
+
+size_t elt_size(int elt) { return elt ? 8 : 4; }
+
+long long plane_off_args(const ArrayInfo& a, const int* args, int nargs) {
+  long long off = 0;
+  for (auto& t : a.vterms) {
+    const int av = t.first < nargs ? args[t.first] : 1;
+    off += (long long)(av - 1) * t.second;
+  }
+  return off;
+}
+
+// Bind this call's arrays into an ArrayTable.  `multi_plane`: all planes klo..klo+nk-1 are addressed through kk
+// (k-distributed gather, fused step); otherwise the plane chosen by the integer arguments.
+void bind_arrays(PlanDev& P, void* const* ptrs, const int* args, int nargs, bool multi_plane, bool upload_readonly,
+                 ArrayTable* T) {
+  Session& s = S();
+  cudaStream_t st = stream();
+  std::memset(T, 0, sizeof *T);
+  for (size_t ai = 0; ai < P.h.arrays.size(); ai++) {
+    const ArrayInfo& a = P.h.arrays[ai];
+    const size_t es = elt_size(a.elt);
+    char* H = (char*)ptrs[ai];
+    P.cur[ai] = H;
+    const bool planes = multi_plane && !a.vdims.empty();
+    const long long first = planes ? (long long)(s.loop.klo - 1) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
+    P.on_dev[ai] = is_device_ptr(H);
+    if (P.on_dev[ai]) { T->base[ai] = H + first * es; continue; }
+    const long long need = planes ? a.plane * s.loop.nk : a.plane;
+    if (P.stage_elems[ai] < need) {
+      pool_free(P.stage[ai]);
+      P.stage[ai] = pool_alloc(need * (long long)es);
+      if (!P.stage[ai]) throw std::runtime_error("out of device memory staging array " + a.name);
+      P.stage_elems[ai] = need;
+    }
+    pin_policy(P, (int)ai, H, (size_t)a.total * es);
+    const bool written = P.h.is_scatter && ai < P.h.written.size() && P.h.written[ai];
+    if (a.used && (!written) && upload_readonly)
+      cuda_ok(cudaMemcpyAsync(P.stage[ai], H + first * es, (size_t)need * es, cudaMemcpyHostToDevice, st), "H2D of a host array");
+    T->base[ai] = P.stage[ai];
+  }
+  for (int v = 0; v < kMaxVecs; v++) T->vec[v] = P.vec_dev[v];
+}
+
+// copy the visited cells of every stored array back to the host (the reference's cudaMemcpy2DAsync rectangles);
+// stores that form one contiguous run in an array (column physics: level after level) are merged into one copy
+void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
+  Session& s = S();
+  cudaStream_t st = stream();
+  const long long ni = s.loop.ni, nj = s.loop.count / (s.loop.ni > 0 ? s.loop.ni : 1);
+  struct Run { int array; long long off, len; };
+  std::vector<Run> runs;
+  for (auto& t : P.h.stores) {
+    const int ai = t.a.array;
+    if (P.on_dev[ai]) continue;
+    const ArrayInfo& a = P.h.arrays[ai];
+    const size_t es = elt_size(a.elt);
+    if (t.a.si == 1 && (t.a.sj == 0 || nj == 1)) { runs.push_back({ai, t.a.off0, ni}); continue; }
+    const bool planes = multi_plane && !a.vdims.empty();
+    const int nplanes = planes ? s.loop.nk : 1;
+    for (int kk = 0; kk < nplanes; kk++) {
+      const long long hoff = planes ? (long long)(s.loop.klo - 1 + kk) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
+      char* dsrc = (char*)P.stage[ai] + ((long long)kk * a.plane + t.a.off0) * es;
+      char* hdst = (char*)P.cur[ai] + (hoff + t.a.off0) * es;
+      if (t.a.si == 1)
+        cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.sj * es, dsrc, (size_t)t.a.sj * es, (size_t)ni * es, (size_t)nj,
+                                  cudaMemcpyDeviceToHost, st), "D2H of a stored rectangle");
+      else if (t.a.sj == 0 || nj == 1)
+        cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.si * es, dsrc, (size_t)t.a.si * es, es, (size_t)ni, cudaMemcpyDeviceToHost, st),
+                "D2H of a stored column");
+      else
+        throw std::runtime_error("store into host-resident " + a.name + " has a stride pattern that is not a rectangle; pass a device array");
+    }
+  }
+  std::sort(runs.begin(), runs.end(), [](const Run& x, const Run& y) { return x.array != y.array ? x.array < y.array : x.off < y.off; });
+  for (size_t i = 0; i < runs.size();) {
+    Run r = runs[i++];
+    while (i < runs.size() && runs[i].array == r.array && runs[i].off <= r.off + r.len) {
+      const long long e = runs[i].off + runs[i].len;
+      if (e > r.off + r.len) r.len = e - r.off;
+      i++;
+    }
+    const ArrayInfo& a = P.h.arrays[r.array];
+    const size_t es = elt_size(a.elt);
+    const bool planes = multi_plane && !a.vdims.empty();
+    const int nplanes = planes ? s.loop.nk : 1;
+    for (int kk = 0; kk < nplanes; kk++) {
+      const long long hoff = planes ? (long long)(s.loop.klo - 1 + kk) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
+      cuda_ok(cudaMemcpyAsync((char*)P.cur[r.array] + (hoff + r.off) * es, (char*)P.stage[r.array] + ((long long)kk * a.plane + r.off) * es,
+                              (size_t)r.len * es, cudaMemcpyDeviceToHost, st), "D2H of a stored run");
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// the step
+// ---------------------------------------------------------------------------------------------------------------
+struct StepArgs {
+  bool use_gather = false;      // model input comes from the gather plan (else din)
+  bool fuse_scatter = false;    // outputs go straight to the host arrays (all planes)
+  ArrayTable TG{}, TS{};
+  long long rows = 0;
+};
+
+RowGeom geom_all(long long rows) {
+  Session& s = S();
+  RowGeom g;
+  g.nk = s.loop.nk > 0 ? s.loop.nk : 1;
+  g.count = rows / g.nk;
+  g.ni = s.loop.ni > 0 ? s.loop.ni : 1;
+  g.kk0 = 0;
+  return g;
+}
+
+void run_step_kernels(const StepArgs& A) {
+  Session& s = S();
+  cudaStream_t st = stream();
+  const long long rows = A.rows;
+  const RowGeom g = geom_all(rows);
+  const int nl = (int)s.model.layers.size();
+  if (s.model.is_conv()) {
+    std::string err;
+    if (!conv_forward(s.conv, s.din, s.dout, s.conv_shape[0], s.conv_shape[1], s.conv_shape[2], s.conv_shape[3], st, &err))
+      throw std::runtime_error(err);
+    return;
+  }
+  const bool fused_gather = A.use_gather && s.fuse;
+  if (s.precision != PREC_F32) {
+    TcLaunch L{};
+    if (A.use_gather) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; } else L.X = s.din;
+    if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS; }
+    L.Y = A.fuse_scatter ? nullptr : s.dout;
+    L.g = g;
+    ensure_aux(tc_grid(rows));
+    L.partials = (A.fuse_scatter && s.want_checksum) ? s.d_partials : nullptr;
+    L.status = s.d_status;
+    std::string err;
+    if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
+    if (L.partials) launch_fold(s.d_partials, tc_grid(rows), s.d_sum, 1, st);
+    return;
+  }
+  if (fused_gather && s.small_ok) {
+    std::vector<int> dims{s.model.n_in()};
+    SmallMlpLaunch L{};
+    for (int l = 0; l < nl; l++) { dims.push_back(s.model.layers[l].cout); L.act[l] = s.model.layers[l].act; L.slope[l] = s.model.layers[l].slope; }
+    L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG;
+    if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS; }
+    L.g = g;
+    L.has_in_div = !s.model.in_div.empty(); L.has_out_mul = !s.model.out_mul.empty();
+    L.Yout = A.fuse_scatter ? nullptr : s.dout;
+    L.grid = small_mlp_grid(rows);
+    if (A.fuse_scatter && s.want_checksum) { ensure_aux(L.grid); L.partials = s.d_partials; }
+    launch_small_mlp(nl, dims.data(), L, st);
+    if (L.partials) launch_fold(s.d_partials, L.grid, s.d_sum, 1, st);
+    return;
+  }
+  // generic fp32 path: gather kernel -> one FFMA kernel per layer -> scatter kernel
+  if (A.use_gather) launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, A.TG, g, s.din, st);
+  const float* src = s.din;
+  for (int l = 0; l < nl; l++) {
+    const LayerHost& L = s.model.layers[l];
+    float* dst = l == nl - 1 ? s.dout : ((l & 1) ? s.act1 : s.act0);
+    launch_linear_f32(src, s.dW[l], s.dB[l], dst, rows, L.cout, L.cin, L.act, L.slope, l == 0 ? s.d_in_div : nullptr,
+                      l == nl - 1 ? s.d_out_mul : nullptr, l == nl - 1 ? s.d_relu_mask : nullptr, st);
+    src = dst;
+  }
+  if (A.fuse_scatter) launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, A.TS, g, s.dout, st);
+}
+
+std::string step_key(const StepArgs& A) {
+  std::string k((const char*)&A.use_gather, sizeof(bool));
+  k.append((const char*)&A.fuse_scatter, sizeof(bool));
+  k.append((const char*)&A.rows, sizeof A.rows);
+  if (A.use_gather) k.append((const char*)&A.TG, sizeof A.TG);
+  if (A.fuse_scatter) k.append((const char*)&A.TS, sizeof A.TS);
+  return k;
+}
+
+// driver/fortis_shim.py:82-90: replay if captured; capture on the second call when asked; eager on failure
+void run_step(const StepArgs& A) {
+  Session& s = S();
+  cudaStream_t st = stream();
+  if (!s.graph) { run_step_kernels(A); return; }
+  const std::string key = step_key(A);
+  if (s.gexec && key == s.gkey) { cuda_ok(cudaGraphLaunch(s.gexec, st), "cudaGraphLaunch"); return; }
+  if (key != s.gkey) { drop_graph(); s.gkey = key; }
+  const bool cap = (++s.ncalls == 2);
+  if (!cap) { run_step_kernels(A); return; }
+  fortis_capturing = 1;
+  if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError(); fortis_capturing = 0; run_step_kernels(A); return;
+  }
+  bool threw = false; std::string what;
+  try { run_step_kernels(A); } catch (const std::exception& e) { threw = true; what = e.what(); }
+  cudaGraph_t gr = nullptr;
+  fortis_capturing = 0;
+  const bool ok = cudaStreamEndCapture(st, &gr) == cudaSuccess && !threw &&
+                  cudaGraphInstantiate(&s.gexec, gr, 0) == cudaSuccess;
+  if (gr) cudaGraphDestroy(gr);
+  if (ok) { cuda_ok(cudaGraphLaunch(s.gexec, st), "cudaGraphLaunch"); return; }
+  std::fprintf(stderr, "fortis: graph capture failed, running eagerly\n");
+  s.gexec = nullptr; cudaGetLastError();
+  if (threw) throw std::runtime_error(what);
+  run_step_kernels(A);
+}
+
+void prepare(long long* rows_out) {
+  ensure_plans();
+  ensure_model();
+  const long long rows = model_rows();
+  ensure_buffers(rows);
+  *rows_out = rows;
+}
+
+void collect_args(PlanDev& P, bool skip_ints, long first, va_list ap, bool first_is_named, std::vector<int>* ints,
+                  std::vector<void*>* ptrs) {
+  const int nint = skip_ints ? 0 : P.h.nargs;
+  const int narr = (int)P.h.arrays.size();
+  bool used_first = !first_is_named;
+  for (int i = 0; i < nint; i++) {
+    if (!used_first) { ints->push_back((int)first); used_first = true; }
+    else ints->push_back(va_arg(ap, int));
+  }
+  for (int i = 0; i < narr; i++) {
+    if (!used_first) { ptrs->push_back((void*)first); used_first = true; }
+    else ptrs->push_back(va_arg(ap, void*));
+  }
+}
+
+void do_gather(const int* iargs, int nint, void* const* ptrs, int narr) {
+  Session& s = S();
+  ensure_plans();
+  if (!s.G.h.ok) throw std::runtime_error("fortis_gather: no gather descriptor is configured");
+  if (narr != (int)s.G.h.arrays.size()) throw std::runtime_error("fortis_gather: wrong number of arrays");
+  ensure_model();
+  for (int i = 0; i < 8; i++) s.gather_args[i] = i < nint ? iargs[i] : 1;
+  // staging happens now (the host may change its arrays after this call returns); the gather itself is deferred
+  ArrayTable T;
+  bind_arrays(s.G, ptrs, s.gather_args, nint, s.loop.kdist, true, &T);
+  s.gather_pending = true;
+}
+
+ArrayTable current_gather_table() {
+  Session& s = S();
+  ArrayTable T;
+  std::memset(&T, 0, sizeof T);
+  for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+    const ArrayInfo& a = s.G.h.arrays[ai];
+    if (!s.G.on_dev[ai]) { T.base[ai] = s.G.stage[ai]; continue; }
+    const bool planes = s.loop.kdist && !a.vdims.empty();
+    const long long first = planes ? (long long)(s.loop.klo - 1) * a.plane : (s.loop.kdist ? 0 : plane_off_args(a, s.gather_args, 8));
+    T.base[ai] = (char*)s.G.cur[ai] + first * elt_size(a.elt);
+  }
+  for (int v = 0; v < kMaxVecs; v++) T.vec[v] = s.G.vec_dev[v];
+  return T;
+}
+
+void do_forward_batched(void* in, void* out) {
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  cudaStream_t st = stream();
+  const long long nin = s.model.n_in(), nout = s.model.n_out();
+  StepArgs A;
+  A.rows = rows;
+  if (s.gather_pending) {
+    A.use_gather = true;
+    A.TG = current_gather_table();
+    run_step(A);
+    s.gather_pending = false;
+    if (!s.S.h.ok && s.Y_pinned) {    // gather lifted but outputs unpacked on the host (FORTIS_GATHER only: shim :111-113)
+      cuda_ok(cudaMemcpyAsync(s.Y_pinned, s.dout, rows * nout * 4, cudaMemcpyDeviceToHost, st), "D2H of Y");
+      cudaStreamSynchronize(st);
+    }
+    return;
+  }
+  if (s.pack_pending) {              // packed form: X -> din, step, dout -> Y   (driver/fortis_shim.py:115)
+    cuda_ok(cudaMemcpyAsync(s.din, s.X_pinned, rows * nin * 4, cudaMemcpyHostToDevice, st), "H2D of X");
+    run_step(A);
+    if (!s.S.h.ok) {
+      cuda_ok(cudaMemcpyAsync(s.Y_pinned, s.dout, rows * nout * 4, cudaMemcpyDeviceToHost, st), "D2H of Y");
+      cudaStreamSynchronize(st);
+    }
+    s.pack_pending = false;
+    return;
+  }
+  // array form  (driver/fortis_shim.py:117-121)
+  if (!in || !out) throw std::runtime_error("mlp_forward_batched: no gather or pack is pending and no arrays were given");
+  if (is_device_ptr(in)) cuda_ok(cudaMemcpyAsync(s.din, in, rows * nin * 4, cudaMemcpyDeviceToDevice, st), "D2D of the input");
+  else cuda_ok(cudaMemcpyAsync(s.din, in, rows * nin * 4, cudaMemcpyHostToDevice, st), "H2D of the input");
+  run_step(A);
+  cuda_ok(cudaMemcpyAsync(out, s.dout, rows * nout * 4, is_device_ptr(out) ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st),
+          "copy of the output");
+  cudaStreamSynchronize(st);
+}
+
+void do_scatter(const int* iargs, int nint, void* const* ptrs, int narr) {
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  if (!s.S.h.ok) throw std::runtime_error("fortis_scatter: no scatter descriptor is configured");
+  if (narr != (int)s.S.h.arrays.size()) throw std::runtime_error("fortis_scatter: wrong number of arrays");
+  cudaStream_t st = stream();
+  int args[8];
+  for (int i = 0; i < 8; i++) args[i] = i < nint ? iargs[i] : 1;
+  ArrayTable T;
+  bind_arrays(s.S, ptrs, args, nint, false, true, &T);
+  RowGeom g = geom_all(rows);
+  const long long count = g.count;
+  g.nk = 1; g.kk0 = 0;
+  const long long yoff = s.loop.kdist ? (long long)(args[0] - s.loop.klo) * count * s.model.n_out() : 0;
+  if (s.loop.kdist && (args[0] < s.loop.klo || args[0] >= s.loop.klo + s.loop.nk))
+    throw std::runtime_error("fortis_scatter: enclosing-loop index outside the distributed range");
+  launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, T, g, s.dout + yoff, st);
+  download_stores(s.S, args, nint, false);
+  if (!s.async) cudaStreamSynchronize(st);
+}
+
+void do_step(void* const* gptrs, int ng, void* const* sptrs, int ns) {
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  if (!s.G.h.ok || !s.S.h.ok) throw std::runtime_error("fortis_step: needs both a gather and a scatter descriptor");
+  if (ng != (int)s.G.h.arrays.size() || ns != (int)s.S.h.arrays.size()) throw std::runtime_error("fortis_step: wrong number of arrays");
+  if (s.loop.nk > 1)
+    for (auto& t : s.S.h.stores)
+      if (s.S.h.arrays[t.a.array].vdims.empty())
+        throw std::runtime_error("fortis_step: stored array " + s.S.h.arrays[t.a.array].name +
+                                 " has no plane dimension; the host consumes it between planes, use fortis_scatter per plane");
+  cudaStream_t st = stream();
+  int args[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  StepArgs A;
+  A.rows = rows; A.use_gather = true; A.fuse_scatter = true;
+  bind_arrays(s.G, gptrs, args, 0, true, true, &A.TG);
+  bind_arrays(s.S, sptrs, args, 0, true, true, &A.TS);
+  run_step(A);
+  download_stores(s.S, args, 0, true);
+  if (!s.async) cudaStreamSynchronize(st);
+}
+
+#define FORTIS_TRY try {
+#define FORTIS_CATCH(ret) } catch (const std::exception& e) { set_error(e.what()); ret; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------
+// exported entries
+// ---------------------------------------------------------------------------------------------------------------
+extern "C" {
+
+void* mgpuStreamCreate(void) { return (void*)stream(); }
+void mgpuStreamDestroy(void*) {}
+void mgpuStreamSynchronize(void*) {}
+
+void* fortis_alloc(long n) { return pool_alloc(n); }
+void fortis_free(void* p) { pool_free(p); }
+
+int fortis_last_error(void) { return g_err; }
+const char* fortis_last_error_message(void) { return g_errmsg.c_str(); }
+void fortis_sync(void) { cudaStreamSynchronize(stream()); }
+
+int fortis_configure(const char* key, const char* text) {
+  FORTIS_TRY
+  Session& s = S();
+  const std::string k = key ? key : "";
+  JValue v = parse_json(text ? text : "");
+  if (k == "gather") { s.jg = v; s.have_g = true; }
+  else if (k == "scatter") { s.js = v; s.have_s = true; }
+  else if (k == "loop") { s.jl = v; s.have_l = true; }
+  else if (k == "kdist") { s.jk = v; s.have_k = true; }
+  else if (k == "lift2d") { s.jl2 = v; s.have_l2 = true; }
+  else throw std::runtime_error("fortis_configure: unknown key \"" + k + "\"");
+  s.planned = false;
+  g_err = 0;
+  return 0;
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_configure_file(const char* key, const char* path) {
+  FORTIS_TRY
+  const std::string text = read_file(path ? path : "");
+  return fortis_configure(key, text.c_str());
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_set_vector(const char* name, const void* data, long n, int elt) {
+  FORTIS_TRY
+  if (!name || !data || n <= 0) throw std::runtime_error("fortis_set_vector: bad arguments");
+  std::vector<char> bytes((size_t)n * elt_size(elt));
+  std::memcpy(bytes.data(), data, bytes.size());
+  S().vectors[name] = std::make_pair(std::move(bytes), elt);
+  S().planned = false;
+  return 0;
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_load_model_mem(const void* blob, long nbytes) {
+  FORTIS_TRY
+  Session& s = S();
+  ModelHost M = parse_model_blob(blob, (size_t)nbytes);
+  free_model_dev();
+  s.model = std::move(M);
+  s.have_model = true;
+  pool_free(s.din); pool_free(s.dout); pool_free(s.act0); pool_free(s.act1);
+  s.din = s.dout = s.act0 = s.act1 = nullptr; s.buf_rows = 0;
+  g_err = 0;
+  return 0;
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_load_model(const char* path) {
+  FORTIS_TRY
+  const std::string b = read_file(path ? path : "");
+  return fortis_load_model_mem(b.data(), (long)b.size());
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_set_option(const char* key, const char* value) {
+  FORTIS_TRY
+  Session& s = S();
+  const std::string k = key ? key : "", v = value ? value : "";
+  if (k == "precision") {
+    int p;
+    if (v == "fp32" || v == "f32") p = PREC_F32;
+    else if (v == "bf16") p = PREC_BF16;
+    else if (v == "fp8w") p = PREC_FP8W;
+    else throw std::runtime_error("precision must be fp32, bf16 or fp8w");
+    if (p != s.precision) { s.precision = p; free_model_dev(); }
+  } else if (k == "fuse") { s.fuse = v != "0"; drop_graph(); }
+  else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
+  else if (k == "async") { s.async = v != "0"; }
+  else if (k == "checksum") { s.want_checksum = v != "0"; drop_graph(); }
+  else if (k == "conv_shape") {
+    if (std::sscanf(v.c_str(), "%d,%d,%d,%d", &s.conv_shape[0], &s.conv_shape[1], &s.conv_shape[2], &s.conv_shape[3]) != 4)
+      throw std::runtime_error("conv_shape must be N,D,H,W");
+    s.buf_rows = 0;
+  } else throw std::runtime_error("fortis_set_option: unknown option \"" + k + "\"");
+  return 0;
+  FORTIS_CATCH(return -1)
+}
+
+void fortis_reset(void) {
+  if (!g_S) return;
+  if (g_stream) cudaStreamSynchronize(g_stream);
+  Session& s = S();
+  drop_graph();
+  free_plan(s.G); free_plan(s.S);
+  free_model_dev();
+  pool_free(s.din); pool_free(s.dout); pool_free(s.act0); pool_free(s.act1);
+  pool_free(s.d_partials); pool_free(s.d_sum); pool_free(s.d_status);
+  if (s.X_pinned) cudaFreeHost(s.X_pinned);
+  if (s.Y_pinned) cudaFreeHost(s.Y_pinned);
+  if (s.reg_in) cudaHostUnregister((void*)s.reg_in);
+  if (s.reg_out) cudaHostUnregister((void*)s.reg_out);
+  cudaGetLastError();
+  delete g_S;
+  g_S = nullptr;
+  g_err = 0;
+  g_errmsg.clear();
+}
+
+void fortis_begin(int count) {
+  Session& s = S();
+  if (s.begin_count != count) { s.begin_count = count; drop_graph(); }
+}
+
+void* fortis_model_input(void) {
+  FORTIS_TRY
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  if (s.gather_pending) {     // make the buffer valid for a caller that consumes X itself
+    launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, current_gather_table(), geom_all(rows), s.din, stream());
+    s.gather_pending = false;
+  }
+  return s.din;
+  FORTIS_CATCH(return nullptr)
+}
+
+void* fortis_model_output(void) {
+  FORTIS_TRY
+  long long rows;
+  prepare(&rows);
+  return S().dout;
+  FORTIS_CATCH(return nullptr)
+}
+
+void fortis_gatherv(const int* iargs, int nint, const void* const* arrays, int narrays) {
+  FORTIS_TRY
+  do_gather(iargs, nint, (void* const*)arrays, narrays);
+  FORTIS_CATCH(return)
+}
+
+void fortis_scatterv(const int* iargs, int nint, void* const* arrays, int narrays) {
+  FORTIS_TRY
+  do_scatter(iargs, nint, arrays, narrays);
+  FORTIS_CATCH(return)
+}
+
+void fortis_stepv(const void* const* ga, int ng, void* const* sa, int ns) {
+  FORTIS_TRY
+  do_step((void* const*)ga, ng, sa, ns);
+  FORTIS_CATCH(return)
+}
+
+void fortis_gather(long a0, ...) {
+  FORTIS_TRY
+  ensure_plans();
+  Session& s = S();
+  if (!s.G.h.ok) throw std::runtime_error("fortis_gather: no gather descriptor is configured");
+  std::vector<int> ints; std::vector<void*> ptrs;
+  va_list ap; va_start(ap, a0);
+  collect_args(s.G, s.loop.kdist, a0, ap, true, &ints, &ptrs);   // no integer arguments under kdist (emit :63)
+  va_end(ap);
+  do_gather(ints.data(), (int)ints.size(), ptrs.data(), (int)ptrs.size());
+  FORTIS_CATCH(return)
+}
+
+void fortis_scatter(long a0, ...) {
+  FORTIS_TRY
+  ensure_plans();
+  Session& s = S();
+  if (!s.S.h.ok) throw std::runtime_error("fortis_scatter: no scatter descriptor is configured");
+  std::vector<int> ints; std::vector<void*> ptrs;
+  va_list ap; va_start(ap, a0);
+  collect_args(s.S, false, a0, ap, true, &ints, &ptrs);
+  va_end(ap);
+  do_scatter(ints.data(), (int)ints.size(), ptrs.data(), (int)ptrs.size());
+  FORTIS_CATCH(return)
+}
+
+void fortis_step(const void* first, ...) {
+  FORTIS_TRY
+  ensure_plans();
+  Session& s = S();
+  if (!s.G.h.ok || !s.S.h.ok) throw std::runtime_error("fortis_step: needs both a gather and a scatter descriptor");
+  std::vector<void*> g, sc;
+  va_list ap; va_start(ap, first);
+  for (size_t i = 0; i < s.G.h.arrays.size(); i++) g.push_back(i == 0 ? (void*)first : va_arg(ap, void*));
+  for (size_t i = 0; i < s.S.h.arrays.size(); i++) sc.push_back(va_arg(ap, void*));
+  va_end(ap);
+  do_step(g.data(), (int)g.size(), sc.data(), (int)sc.size());
+  FORTIS_CATCH(return)
+}
+
+void mlp_forward_batched(void* in, void* out) {
+  FORTIS_TRY
+  do_forward_batched(in, out);
+  FORTIS_CATCH(return)
+}
+
+void mlp_upload(void* in) {
+  FORTIS_TRY
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  cuda_ok(cudaMemcpy(s.din, in, rows * s.model.n_in() * 4, is_device_ptr(in) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice), "mlp_upload");
+  FORTIS_CATCH(return)
+}
+
+void mlp_forward_dev(void) {
+  FORTIS_TRY
+  long long rows;
+  prepare(&rows);
+  StepArgs A;
+  A.rows = rows;
+  run_step(A);
+  FORTIS_CATCH(return)
+}
+
+void mlp_download(void* out) {
+  FORTIS_TRY
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  cudaStreamSynchronize(stream());
+  cuda_ok(cudaMemcpy(out, s.dout, rows * s.model.n_out() * 4, is_device_ptr(out) ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost), "mlp_download");
+  FORTIS_CATCH(return)
+}
+
+void mlp_forward(void* in, void* out) {
+  FORTIS_TRY
+  Session& s = S();
+  ensure_plans();
+  if (s.have_l2) {
+    // boundary verdict: the host's own arrays, their element type and memory order; pinned once
+    // (driver/fortis_shim.py:123-133); transpose + cast + lifted expressions run fused around the model
+    void* gp[1] = {in};
+    void* sp[1] = {out};
+    do_step(gp, 1, sp, 1);
+    cudaStreamSynchronize(stream());
+    return;
+  }
+  ensure_model();
+  const long long nin = s.model.n_in(), nout = s.model.n_out();
+  cudaStream_t st = stream();
+  if (s.have_l) {
+    // batched verdict: single-row entry for calls outside the loop (driver/fortis_shim.py:122)
+    const long long keep = s.begin_count; const bool had_l = s.have_l;
+    ensure_buffers(model_rows());
+    cuda_ok(cudaMemcpyAsync(s.din, in, nin * 4, cudaMemcpyDefault, st), "H2D of one row");
+    StepArgs A; A.rows = 1;
+    const LoopInfo saved = s.loop;
+    s.loop.nk = 1; s.loop.count = 1; s.loop.ni = 1;
+    try { run_step_kernels(A); } catch (...) { s.loop = saved; throw; }
+    s.loop = saved; (void)keep; (void)had_l;
+    cuda_ok(cudaMemcpyAsync(out, s.dout, nout * 4, cudaMemcpyDefault, st), "D2H of one row");
+    cudaStreamSynchronize(st);
+    return;
+  }
+  // whole-array call without a boundary: row-major (batch, n_in) -> (batch, n_out), pinned once
+  long long rows;
+  prepare(&rows);
+  auto pin = [&](const void** reg, void* p, size_t n) {
+    if (s.nopin || *reg == p || std::getenv("FORTIS_NO_PIN") || is_device_ptr(p)) return;
+    if (*reg) { cudaHostUnregister((void*)*reg); *reg = nullptr; s.nopin = true; cudaGetLastError(); return; }
+    *reg = cudaHostRegister(p, n, cudaHostRegisterDefault) == cudaSuccess ? p : nullptr;
+    if (!*reg) cudaGetLastError();
+  };
+  pin(&s.reg_in, in, (size_t)rows * nin * 4);
+  pin(&s.reg_out, out, (size_t)rows * nout * 4);
+  cuda_ok(cudaMemcpyAsync(s.din, in, rows * nin * 4, cudaMemcpyDefault, st), "H2D of the input");
+  StepArgs A; A.rows = rows;
+  run_step(A);
+  cuda_ok(cudaMemcpyAsync(out, s.dout, rows * nout * 4, cudaMemcpyDefault, st), "D2H of the output");
+  cudaStreamSynchronize(st);
+  FORTIS_CATCH(return)
+}
+
+static void ensure_pinned(long long rows) {
+  Session& s = S();
+  if (s.X_pinned && s.pinned_rows >= rows) return;
+  if (s.X_pinned) cudaFreeHost(s.X_pinned);
+  if (s.Y_pinned) cudaFreeHost(s.Y_pinned);
+  cuda_ok(cudaHostAlloc((void**)&s.X_pinned, (size_t)rows * s.model.n_in() * 4, cudaHostAllocDefault), "cudaHostAlloc X");
+  cuda_ok(cudaHostAlloc((void**)&s.Y_pinned, (size_t)rows * s.model.n_out() * 4, cudaHostAllocDefault), "cudaHostAlloc Y");
+  s.pinned_rows = rows;
+}
+
+void fortis_pack(void* f, int col) {
+  FORTIS_TRY
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  ensure_pinned(rows);
+  if (col < 0 || col >= rows) throw std::runtime_error("fortis_pack: column out of range");
+  std::memcpy(s.X_pinned + (size_t)col * s.model.n_in(), f, (size_t)s.model.n_in() * 4);
+  s.pack_pending = true;
+  FORTIS_CATCH(return)
+}
+
+void fortis_unpack(void* o, int col) {
+  FORTIS_TRY
+  Session& s = S();
+  long long rows;
+  prepare(&rows);
+  ensure_pinned(rows);
+  if (col < 0 || col >= rows) throw std::runtime_error("fortis_unpack: column out of range");
+  std::memcpy(o, s.Y_pinned + (size_t)col * s.model.n_out(), (size_t)s.model.n_out() * 4);
+  FORTIS_CATCH(return)
+}
+
+void fortis_gemm(float* Aa, float* A, long Ao, long As0, long As1, long At0, long At1,
+                 float* Wa, float* W, long Wo, long Ws0, long Ws1, long Wt0, long Wt1,
+                 float* Ca, float* C, long Co, long Cs0, long Cs1, long Ct0, long Ct1, long B, long N, long K) {
+  (void)Aa; (void)As0; (void)As1; (void)At0; (void)At1; (void)Wa; (void)Ws0; (void)Ws1; (void)Wt0; (void)Wt1;
+  (void)Ca; (void)Cs0; (void)Cs1; (void)Ct0; (void)Ct1;
+  launch_linear_f32(A + Ao, W + Wo, nullptr, C + Co, B, (int)N, (int)K, ACT_NONE, 0.f, nullptr, nullptr, nullptr, stream());
+}
+
+static void conv3d_entry(const char* who, float* x, long xo, float* w, long wo, float* y, long yo, long N, long C, long Din, long Hin,
+                         long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout, long sd, long sh, long sw,
+                         long pd, long ph, long pw) {
+  if (sd != 1 || sh != 1 || sw != 1 || KD != KH || KD != KW || pd != ph || pd != pw || Dout != Din + 2 * pd - KD + 1 ||
+      Hout != Hin + 2 * ph - KH + 1 || Wout != Win + 2 * pw - KW + 1) {
+    std::fprintf(stderr, "%s: unsupported shape\n", who);
+    return;
+  }
+  std::string err;
+  if (!conv3d_ncdhw(x + xo, w + wo, y + yo, (int)N, (int)C, (int)Din, (int)Hin, (int)Win, (int)F, (int)KD, (int)pd, stream(), &err))
+    std::fprintf(stderr, "%s: %s\n", who, err.c_str());
+}
+
+void fortis_conv3d(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
+                   long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
+                   long sd, long sh, long sw, long pd, long ph, long pw) {
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)xt0; (void)xt1; (void)xt2; (void)xt3; (void)xt4;
+  (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; (void)wt0; (void)wt1; (void)wt2; (void)wt3; (void)wt4;
+  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; (void)yt0; (void)yt1; (void)yt2; (void)yt3; (void)yt4;
+  conv3d_entry("fortis_conv3d", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw);
+}
+
+void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
+                   long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
+                   long sd, long sh, long sw, long pd, long ph, long pw) {
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)xt0; (void)xt1; (void)xt2; (void)xt3; (void)xt4;
+  (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; (void)wt0; (void)wt1; (void)wt2; (void)wt3; (void)wt4;
+  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; (void)yt0; (void)yt1; (void)yt2; (void)yt3; (void)yt4;
+  conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw);
+}
+
+int fortis_checksum(const void* data, long n, int elt, double* out) {
+  FORTIS_TRY
+  Session& s = S();
+  cudaStream_t st = stream();
+  ensure_aux(kChecksumBlocks);
+  const void* d = data;
+  void* tmp = nullptr;
+  if (!is_device_ptr(data)) {
+    tmp = pool_alloc((long)(n * (long)elt_size(elt)));
+    if (!tmp) throw std::runtime_error("fortis_checksum: out of device memory");
+    cuda_ok(cudaMemcpyAsync(tmp, data, (size_t)n * elt_size(elt), cudaMemcpyHostToDevice, st), "H2D for checksum");
+    d = tmp;
+  }
+  double* dres = (double*)pool_alloc(sizeof(double));
+  launch_checksum(d, n, elt, s.d_partials, dres, 0, st);
+  cuda_ok(cudaMemcpyAsync(out, dres, sizeof(double), cudaMemcpyDeviceToHost, st), "D2H of the checksum");
+  cudaStreamSynchronize(st);
+  pool_free(dres); pool_free(tmp);
+  return cuda_ok(cudaGetLastError(), "checksum kernels") ? 0 : -1;
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_step_checksum(double* out) {
+  FORTIS_TRY
+  Session& s = S();
+  ensure_aux(1);
+  cudaStream_t st = stream();
+  cuda_ok(cudaMemcpyAsync(out, s.d_sum, sizeof(double), cudaMemcpyDeviceToHost, st), "D2H of the step checksum");
+  cudaMemsetAsync(s.d_sum, 0, sizeof(double), st);
+  cudaStreamSynchronize(st);
+  return 0;
+  FORTIS_CATCH(return -1)
+}
+
+// ---- host-only introspection (no CUDA call): lets the CPU test-suite check the descriptor planner and the
+// expression compiler against the oracle
+int fortis_debug_eval_expr(const char* exprs_json, int tv_double, double tv, const double* scalars, const int* scalar_elt,
+                           int nscalars, double* out) {
+  FORTIS_TRY
+  JValue v = parse_json(exprs_json ? exprs_json : "[]");
+  std::vector<int> elt(kMaxScalars, -1);
+  double sc[kMaxScalars] = {};
+  for (int i = 0; i < nscalars && i < kMaxScalars; i++) { elt[i] = scalar_elt[i]; sc[i] = scalars[i]; }
+  ExprProg P{};
+  P.tv_double = tv_double;
+  for (size_t k = 0; k < v.size(); k++) compile_expr(v.at(k).as_str(), elt, &P);
+  *out = eval_prog_host(P, tv, sc, nullptr);
+  return P.nops;
+  FORTIS_CATCH(return -1)
+}
+
+// Element offsets (relative to each host array's first element) that `row` of a gather (is_scatter = 0: one per
+// slot) or scatter (is_scatter = 1: one per store) touches, with the enclosing-loop arguments `args`.
+int fortis_debug_plan(const char* desc_json, const char* loop_json, const char* kdist_json, int is_scatter, long row,
+                      const int* args, int nargs, long long* offsets, int* arrays, int* slots, int cap, long long* geom) {
+  FORTIS_TRY
+  JValue jd = parse_json(desc_json), jl = parse_json(loop_json);
+  JValue jk;
+  const bool hk = kdist_json && *kdist_json;
+  if (hk) jk = parse_json(kdist_json);
+  LoopInfo L = make_loop(&jl, hk ? &jk : nullptr);
+  IoPlanHost P = make_io_plan(jd, L, is_scatter != 0);
+  if (geom) { geom[0] = L.count; geom[1] = L.nk; geom[2] = L.ni; geom[3] = L.klo; geom[4] = L.ilo; geom[5] = L.jlo; geom[6] = P.nargs; }
+  if (!P.ok) return 0;
+  const long long col = row % L.count, kk = row / L.count, ci = col % L.ni, cj = col / L.ni;
+  const int n = is_scatter ? (int)P.stores.size() : (int)P.slots.size();
+  for (int q = 0; q < n && q < cap; q++) {
+    const Access& a = is_scatter ? P.stores[q].a : P.slots[q];
+    const ArrayInfo& ai = P.arrays[a.array];
+    long long base;
+    if (L.kdist && !is_scatter) base = ai.vdims.empty() ? 0 : (long long)(L.klo - 1 + kk) * ai.plane;
+    else base = plane_off_args(ai, args, nargs);
+    offsets[q] = base + a.off0 + ci * a.si + cj * a.sj;
+    arrays[q] = a.array;
+    if (slots) slots[q] = is_scatter ? P.stores[q].slot : q;
+  }
+  return n;
+  FORTIS_CATCH(return -1)
+}
+
+int fortis_device_status(void) {
+  FORTIS_TRY
+  Session& s = S();
+  ensure_aux(1);
+  int v = 0;
+  cudaStreamSynchronize(stream());
+  cudaMemcpy(&v, s.d_status, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+  FORTIS_CATCH(return -1)
+}
+
+}  // extern "C"

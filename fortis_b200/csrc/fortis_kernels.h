@@ -1,0 +1,75 @@
+// Launch interface of the CUDA-core kernels (fortis_kernels.cu) and of the tensor-core kernels (fortis_mlp_tc.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "fortis_plan.h"
+
+namespace fortis {
+
+struct IoPlanDev;
+
+enum { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2 };
+
+constexpr int kSmallConstFloats = 8192;     // constant-bank budget of the fused small-MLP kernel
+constexpr int kChecksumBlocks = 592;        // 4 x 148 SMs
+
+void launch_gather(const IoPlanDev* P, const Access* slots, int n, const ArrayTable& T, const RowGeom& g, float* X, cudaStream_t s);
+void launch_scatter(const IoPlanDev* P, const StoreTarget* stores, int nout, const ArrayTable& T, const RowGeom& g,
+                    const float* Y, cudaStream_t s);
+void launch_linear_f32(const float* A, const float* W, const float* bias, float* C, long long M, int N, int K, int act,
+                       float slope, const float* in_div, const float* out_mul, const float* relu_mask, cudaStream_t s);
+
+struct SmallMlpLaunch {
+  const IoPlanDev* GP; const Access* slots;          // gather plan (required)
+  const IoPlanDev* SP; const StoreTarget* stores;    // scatter plan (null: only Yout is written)
+  ArrayTable TG, TS;
+  RowGeom g;
+  int act[4]; float slope[4];
+  int has_in_div, has_out_mul;
+  float* Yout;                                       // optional (rows, nout) model output
+  double* partials;                                  // optional per-block checksum partials [grid]
+  int grid;                                          // 0: pick
+};
+bool small_mlp_supported(int nlayers, const int* dims);
+int small_mlp_grid(long long nrows);
+int small_mlp_pack(int nlayers, const int* dims, const float* const* W, const float* const* b, const float* in_div,
+                   const float* out_mul, float* dst);
+cudaError_t small_mlp_upload(const float* host, int nfloats, cudaStream_t s);
+void launch_small_mlp(int nlayers, const int* dims, const SmallMlpLaunch& L, cudaStream_t s);
+
+// ---- tensor-core fused MLP (fortis_mlp_tc.cu) ----------------------------------------------------------------
+struct ModelHost;
+struct TcModel;                                        // packed bf16 weights, TMA tensor maps, biases, scales
+enum { PREC_F32 = 0, PREC_BF16 = 1, PREC_FP8W = 2 };
+bool tc_model_supported(const ModelHost& M, std::string* why);
+TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
+void tc_model_destroy(TcModel* m);
+struct TcLaunch {
+  const IoPlanDev* GP; const Access* slots;          // gather plan, or null with X set
+  const IoPlanDev* SP; const StoreTarget* stores;    // scatter plan, or null with Y set
+  ArrayTable TG, TS;
+  RowGeom g;
+  const float* X;                                    // (rows, n_in) when there is no gather plan
+  float* Y;                                          // (rows, n_out) when there is no scatter plan (may be set with SP too)
+  double* partials;                                  // per-CTA checksum partials (size >= tc_grid())
+  int* status;                                       // device word: 0 ok, else the code of the wait that gave up
+};
+int tc_grid(long long nrows);
+bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err);
+
+// ---- conv3d network (fortis_conv3d.cu) -------------------------------------------------------------------------
+struct ConvModel;
+ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
+void conv_model_destroy(ConvModel* m);
+// x (N,D,H,W,Cin) fp32 NDHWC on the device -> y (N,D,H,W,Cout)
+bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
+// single layer, NCDHW fp32 (the memref ABI of runtime/fortis_rt.c:128-131)
+bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, int K, int pad,
+                  cudaStream_t s, std::string* err);
+
+void launch_checksum(const void* data, long long n, int elt, double* partials, double* out, int accumulate, cudaStream_t s);
+void launch_fold(const double* partials, int n, double* out, int accumulate, cudaStream_t s);
+
+}  // namespace fortis

@@ -272,24 +272,39 @@ def gather(G: Dict, Lp: Dict, K: Optional[Dict], arrays: Sequence[np.ndarray], a
 
 
 def _eval_c(ast, tv, scal):
-    """C usual-arithmetic-conversion evaluation: float unless an operand is double (an f64 array scalar or an
-    unsuffixed literal), result narrowed to float on assignment to tv."""
-    wide = _is_wide(ast, scal)
-    dt = np.float64 if wide else np.float32
-    sc = {k: (v.astype(dt) if isinstance(v, np.ndarray) else dt(v)) for k, v in scal.items()}
-    r = eval_expr(ast, tv.astype(dt), sc, dt)
-    return np.asarray(r, dtype=dt).astype(np.float32) if wide else np.asarray(r, dtype=np.float32)
+    """`tv = <expr>;` with C's usual arithmetic conversions applied PER OPERATION: an operation is done in double
+    iff one of its operands is double (an f64 array scalar or an unsuffixed literal), the *f functions take and
+    return float, and the assignment narrows the result to float."""
+    v, _ = _eval_typed(ast, np.asarray(tv, dtype=np.float32), scal)
+    return np.asarray(v).astype(np.float32)
 
 
-def _is_wide(ast, scal):
+def _eval_typed(ast, tv, scal):
     k = ast[0]
-    if k == "const":
-        return not ast[2]
-    if k == "scalar":
-        return np.asarray(scal[ast[1]]).dtype == np.float64
     if k == "tv":
-        return False
-    return any(_is_wide(a, scal) for a in ast[1:] if isinstance(a, tuple))
+        return tv, False
+    if k == "scalar":
+        v = scal[ast[1]]
+        return v, np.asarray(v).dtype == np.float64
+    if k == "const":
+        return (np.float32(ast[1]), False) if ast[2] else (np.float64(ast[1]), True)
+    if k == "neg":
+        v, d = _eval_typed(ast[1], tv, scal)
+        return -v, d
+    if k in ("sqrt", "exp", "log", "tanh"):
+        v, _ = _eval_typed(ast[1], tv, scal)
+        return getattr(np, k)(np.asarray(v).astype(np.float32)).astype(np.float32), False
+    a, da = _eval_typed(ast[1], tv, scal)
+    b, db = _eval_typed(ast[2], tv, scal)
+    if k in ("max", "min"):
+        f = np.fmax if k == "max" else np.fmin
+        return f(np.asarray(a).astype(np.float32), np.asarray(b).astype(np.float32)).astype(np.float32), False
+    d = da or db
+    dt = np.float64 if d else np.float32
+    a, b = np.asarray(a).astype(dt), np.asarray(b).astype(dt)
+    with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+        r = {"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide}[k](a, b)
+    return r, d
 
 
 def scatter(S: Dict, Lp: Dict, K: Optional[Dict], Y: np.ndarray, arrays: Sequence[np.ndarray],
@@ -560,13 +575,13 @@ def column_descriptors(ncol: int, nlev: int, nfields: int = 4, nscal: int = 4, n
     """Column physics: features [F0(1:nlev), F1(1:nlev), ..., s0, s1, ...] gathered from (ncol,nlev) fields and
     (ncol) vectors with constant level subscripts; outputs to `nout_fields` (ncol,nlev) arrays and `nout_scal`
     (ncol) vectors."""
-    arrays = [{"ssa": "%f%d" % f, "name": "f%d" % f, "shape": [ncol, nlev], "elt": elt} for f in range(nfields)]
-    arrays += [{"ssa": "%s%d" % s, "name": "s%d" % s, "shape": [ncol], "elt": elt} for s in range(nscal)]
+    arrays = [{"ssa": "%%f%d" % f, "name": "f%d" % f, "shape": [ncol, nlev], "elt": elt} for f in range(nfields)]
+    arrays += [{"ssa": "%%s%d" % s, "name": "s%d" % s, "shape": [ncol], "elt": elt} for s in range(nscal)]
     slots = [{"array": f, "idx": [["i", 0], ["c", l + 1]]} for f in range(nfields) for l in range(nlev)]
     slots += [{"array": nfields + s, "idx": [["i", 0]]} for s in range(nscal)]
     G = {"ok": True, "n": len(slots), "args": [], "arrays": arrays, "scalars": [], "exprs": [], "slots": slots}
-    oarr = [{"ssa": "%o%d" % f, "name": "o%d" % f, "shape": [ncol, nlev], "elt": elt} for f in range(nout_fields)]
-    oarr += [{"ssa": "%t%d" % s, "name": "t%d" % s, "shape": [ncol], "elt": elt} for s in range(nout_scal)]
+    oarr = [{"ssa": "%%o%d" % f, "name": "o%d" % f, "shape": [ncol, nlev], "elt": elt} for f in range(nout_fields)]
+    oarr += [{"ssa": "%%t%d" % s, "name": "t%d" % s, "shape": [ncol], "elt": elt} for s in range(nout_scal)]
     stores = [{"slot": f * nlev + l, "array": f, "idx": [["i", 0], ["c", l + 1]]}
               for f in range(nout_fields) for l in range(nlev)]
     stores += [{"slot": nout_fields * nlev + s, "array": nout_fields + s, "idx": [["i", 0]]}

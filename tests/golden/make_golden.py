@@ -140,7 +140,8 @@ def extra_cases():
          "arrays": [arr("p", [13, 9, 3], "f64"), arr("q", [13, 9, 3], "f32"), arr("w", [13, 9, 3], "f64")],
          "scalars": [{"name": "S0", "array": 2, "idx": [["i", 0], ["j", 0], ["v", 0]]},
                      {"name": "S1", "array": 1, "idx": [["i", 1], ["j", -1], ["v", 0]]}],
-         "exprs": ["((tv - S1) / (S0 + 1.000000e-30f))", "fmaxf(sqrtf((tv * tv)), 2.500000e-01f)"],
+         "exprs": ["(((tv * S1) - 1.100000e+00f) / (S0 + 1.000000e-30f))", "fmaxf(sqrtf((tv * tv)), 2.500000e-01f)",
+                   "((tv * 3.300000e-01) + (S1 * 7.000000e-01f))"],
          "slots": [{"array": 0, "idx": [["i", -1], ["j", 0], ["v", 0]]},
                    {"array": 0, "idx": [["i", 1], ["j", 1], ["v", 0]]},
                    {"array": 1, "idx": [["i", 0], ["j", -1], ["v", 0]]},
@@ -149,7 +150,7 @@ def extra_cases():
     S = {"ok": True, "n": 2, "args": [{"alloca": "%k", "name": "k"}],
          "arrays": [arr("w", [13, 9], "f64"), arr("r0", [13, 9, 3], "f64"), arr("r1", [13, 9], "f32")],
          "scalars": [{"name": "S0", "array": 0, "idx": [["i", 0], ["j", 0]]}],
-         "exprs": ["((tv * S0) + 1.250000e-01f)", "(-tv)"],
+         "exprs": ["(((tv * 1.700000e+00f) * S0) + 1.250000e-01f)", "(-tv)"],
          "stores": [{"slot": 1, "array": 1, "idx": [["i", 0], ["j", 0], ["v", 0]]},
                     {"slot": 0, "array": 2, "idx": [["i", 0], ["j", 0]]}]}
     Lp = {"batch": 11 * 7 * 3, "inner": {"lo": 2, "hi": 12, "n": 11}, "outer": {"lo": 2, "hi": 8}}

@@ -1,0 +1,60 @@
+"""The C-ABI library loads and exports every symbol include/fortis_b200.h declares (no compute call is made)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import fortis_b200
+from fortis_b200 import build as fb
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    fb.build()
+    return fortis_b200.load()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fortis_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"^\s*(?:const\s+)?(?:void|int|double|char|long)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
+    names += re.findall(r"^extern\s+int\s+(\w+)\s*;", text, flags=re.M)
+    return sorted(set(names))
+
+
+def test_header_lists_the_reference_surface():
+    names = declared_symbols()
+    for ref in ("fortis_gather", "fortis_scatter", "mlp_forward", "mlp_forward_batched", "mlp_upload", "mlp_forward_dev",
+                "mlp_download", "fortis_pack", "fortis_unpack", "fortis_model_input", "fortis_model_output", "fortis_begin",
+                "mgpuStreamCreate", "mgpuStreamDestroy", "mgpuStreamSynchronize", "fortis_alloc", "fortis_free",
+                "fortis_gemm", "fortis_conv3d", "fortis_conv3d_direct", "fortis_capturing"):
+        assert ref in names
+
+
+def test_every_declared_symbol_is_exported(lib):
+    for name in declared_symbols():
+        assert hasattr(lib, name), "libfortis_b200.so does not export %s" % name
+
+
+def test_configuration_errors_are_reported_not_thrown(lib):
+    assert lib.fortis_configure(b"gather", b"{not json") == -1
+    assert b"JSON" in lib.fortis_last_error_message()
+    assert lib.fortis_configure(b"nonsense", b"{}") == -1
+    assert lib.fortis_load_model_mem(ctypes.c_char_p(b"garbage!garbage!"), 16) == -1
+    assert b"magic" in lib.fortis_last_error_message()
+    blob = fortis_b200.write_blob(fortis_b200.mlp_layers([4, 8, 2], seed=0))
+    assert lib.fortis_load_model_mem(ctypes.c_char_p(blob[:40]), 40) == -1          # truncated
+    assert b"truncated" in lib.fortis_last_error_message()
+    assert lib.fortis_set_option(b"precision", b"int4") == -1
+    lib.fortis_reset()
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from fortis_b200 import lib as fl
+    monkeypatch.setattr(fl, "_LIB", None)
+    monkeypatch.setattr(fl, "HERE", str(tmp_path))
+    with pytest.raises(fl.FortisError):
+        fl.load()
