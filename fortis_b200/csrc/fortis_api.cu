@@ -97,6 +97,7 @@ struct PlanDev {
   std::vector<const void*> cur;              // this call's pointers
   std::vector<char> on_dev;
   void* vec_dev[kMaxVecs] = {};
+  int *slot_head = nullptr, *store_next = nullptr;   // scatter: stores indexed by model output
 };
 
 struct Session {
@@ -124,7 +125,7 @@ struct Session {
   float *din = nullptr, *dout = nullptr, *act0 = nullptr, *act1 = nullptr;
   float *X_pinned = nullptr, *Y_pinned = nullptr;
   long long pinned_rows = 0;
-  bool pack_pending = false, gather_pending = false;
+  bool pack_pending = false, gather_pending = false, gather_done = false;
   int gather_args[8] = {};
   const void *reg_in = nullptr, *reg_out = nullptr;
   bool nopin = false;
@@ -156,7 +157,7 @@ void free_plan(PlanDev& P) {
     if (P.reg[i] && P.reg[i] != (const void*)1) { cudaHostUnregister((void*)P.reg[i]); cudaGetLastError(); }
   for (void* p : P.stage) pool_free(p);
   for (void*& v : P.vec_dev) { pool_free(v); v = nullptr; }
-  pool_free(P.hdr); pool_free(P.items);
+  pool_free(P.hdr); pool_free(P.items); pool_free(P.slot_head); pool_free(P.store_next);
   P = PlanDev();
 }
 
@@ -200,6 +201,12 @@ void upload_plan(PlanDev& P) {
     const size_t nb = sizeof(StoreTarget) * P.h.stores.size();
     P.items = pool_alloc((long)nb);
     if (nb) cudaMemcpy(P.items, P.h.stores.data(), nb, cudaMemcpyHostToDevice);
+    std::vector<int> head(P.h.n > 0 ? P.h.n : 1, -1), next(P.h.stores.size() ? P.h.stores.size() : 1, -1);
+    for (int q = (int)P.h.stores.size() - 1; q >= 0; q--) { next[q] = head[P.h.stores[q].slot]; head[P.h.stores[q].slot] = q; }
+    P.slot_head = (int*)pool_alloc((long)(head.size() * 4));
+    P.store_next = (int*)pool_alloc((long)(next.size() * 4));
+    cudaMemcpy(P.slot_head, head.data(), head.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(P.store_next, next.data(), next.size() * 4, cudaMemcpyHostToDevice);
   }
   const size_t na = P.h.arrays.size();
   P.stage.assign(na, nullptr); P.stage_elems.assign(na, 0); P.reg.assign(na, nullptr); P.cur.assign(na, nullptr);
@@ -412,26 +419,49 @@ void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
   const long long ni = s.loop.ni, nj = s.loop.count / (s.loop.ni > 0 ? s.loop.ni : 1);
   struct Run { int array; long long off, len; };
   std::vector<Run> runs;
+  // Stores that walk a strided column (the column index is not the array's fastest dimension): when the stores of
+  // one array interleave densely (offsets off, off+1, ..., off+si-1 with stride si) their union is one contiguous
+  // range; otherwise each is copied as a 1-element-wide 2-D copy.
+  std::map<std::pair<int, long long>, std::vector<long long>> columns;
+  for (auto& t : P.h.stores)
+    if (!P.on_dev[t.a.array] && t.a.si != 1 && (t.a.sj == 0 || nj == 1)) columns[{t.a.array, t.a.si}].push_back(t.a.off0);
+  std::map<std::pair<int, long long>, bool> dense;
+  for (auto& kv : columns) {
+    std::vector<long long>& o = kv.second;
+    std::sort(o.begin(), o.end());
+    bool ok = (long long)o.size() == kv.first.second;
+    for (size_t i = 1; ok && i < o.size(); i++) ok = o[i] == o[i - 1] + 1;
+    dense[kv.first] = ok;
+    if (ok) runs.push_back({kv.first.first, o[0], ni * kv.first.second});
+  }
   for (auto& t : P.h.stores) {
     const int ai = t.a.array;
     if (P.on_dev[ai]) continue;
     const ArrayInfo& a = P.h.arrays[ai];
     const size_t es = elt_size(a.elt);
     if (t.a.si == 1 && (t.a.sj == 0 || nj == 1)) { runs.push_back({ai, t.a.off0, ni}); continue; }
+    if (t.a.si != 1 && (t.a.sj == 0 || nj == 1) && dense[{ai, t.a.si}]) continue;
     const bool planes = multi_plane && !a.vdims.empty();
     const int nplanes = planes ? s.loop.nk : 1;
     for (int kk = 0; kk < nplanes; kk++) {
       const long long hoff = planes ? (long long)(s.loop.klo - 1 + kk) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
       char* dsrc = (char*)P.stage[ai] + ((long long)kk * a.plane + t.a.off0) * es;
       char* hdst = (char*)P.cur[ai] + (hoff + t.a.off0) * es;
-      if (t.a.si == 1)
-        cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.sj * es, dsrc, (size_t)t.a.sj * es, (size_t)ni * es, (size_t)nj,
-                                  cudaMemcpyDeviceToHost, st), "D2H of a stored rectangle");
-      else if (t.a.sj == 0 || nj == 1)
-        cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.si * es, dsrc, (size_t)t.a.si * es, es, (size_t)ni, cudaMemcpyDeviceToHost, st),
-                "D2H of a stored column");
-      else
+      // a 2-D copy is validated over pitch x height, which would reach past the end of the array on the last
+      // row: copy all rows but the last as 2-D, the last one as 1-D
+      if (t.a.si == 1) {
+        if (nj > 1) cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.sj * es, dsrc, (size_t)t.a.sj * es, (size_t)ni * es, (size_t)(nj - 1),
+                                              cudaMemcpyDeviceToHost, st), "D2H of a stored rectangle");
+        cuda_ok(cudaMemcpyAsync(hdst + (nj - 1) * t.a.sj * es, dsrc + (nj - 1) * t.a.sj * es, (size_t)ni * es, cudaMemcpyDeviceToHost, st),
+                "D2H of a stored rectangle (last row)");
+      } else if (t.a.sj == 0 || nj == 1) {
+        if (ni > 1) cuda_ok(cudaMemcpy2DAsync(hdst, (size_t)t.a.si * es, dsrc, (size_t)t.a.si * es, es, (size_t)(ni - 1),
+                                              cudaMemcpyDeviceToHost, st), "D2H of a stored column");
+        cuda_ok(cudaMemcpyAsync(hdst + (ni - 1) * t.a.si * es, dsrc + (ni - 1) * t.a.si * es, es, cudaMemcpyDeviceToHost, st),
+                "D2H of a stored column (last element)");
+      } else {
         throw std::runtime_error("store into host-resident " + a.name + " has a stride pattern that is not a rectangle; pass a device array");
+      }
     }
   }
   std::sort(runs.begin(), runs.end(), [](const Run& x, const Run& y) { return x.array != y.array ? x.array < y.array : x.off < y.off; });
@@ -474,6 +504,40 @@ RowGeom geom_all(long long rows) {
   return g;
 }
 
+// Operands of the fast small-MLP kernel: possible when all input slots (and all stores) are fp32 and share one
+// stride triple, and every index fits 32 bits.
+bool small_fast_operands(const StepArgs& A, const RowGeom& g, SmallFast* F) {
+  Session& s = S();
+  std::memset(F, 0, sizeof *F);
+  const long long nrows = g.count * g.nk;
+  if (nrows >= (1LL << 31) || s.G.h.slots.size() > 32) return false;
+  const Access& a0 = s.G.h.slots[0];
+  for (size_t q = 0; q < s.G.h.slots.size(); q++) {
+    const Access& a = s.G.h.slots[q];
+    const ArrayInfo& ai = s.G.h.arrays[a.array];
+    if (a.elt != 0 || a.si != a0.si || a.sj != a0.sj || a.sk != a0.sk || ai.total >= (1LL << 31)) return false;
+    F->in_ptr[q] = (const float*)A.TG.base[a.array] + a.off0;
+  }
+  F->si = (int)a0.si; F->sj = (int)a0.sj; F->sk = (int)a0.sk;
+  F->in_prog = s.G.h.prog.nops > 0;
+  if (A.fuse_scatter) {
+    if (s.S.h.stores.size() > 8 || s.S.h.stores.empty()) return false;
+    const Access& b0 = s.S.h.stores[0].a;
+    for (size_t q = 0; q < s.S.h.stores.size(); q++) {
+      const Access& a = s.S.h.stores[q].a;
+      const ArrayInfo& ai = s.S.h.arrays[a.array];
+      if (a.elt != 0 || a.si != b0.si || a.sj != b0.sj || a.sk != b0.sk || ai.total >= (1LL << 31)) return false;
+      F->out_ptr[q] = (float*)A.TS.base[a.array] + a.off0;
+      F->out_slot[q] = s.S.h.stores[q].slot;
+    }
+    F->nstores = (int)s.S.h.stores.size();
+    F->oi = (int)b0.si; F->oj = (int)b0.sj; F->ok = (int)b0.sk;
+    F->out_prog = s.S.h.prog.nops > 0;
+  }
+  F->nrows = (unsigned)nrows; F->count = (unsigned)g.count; F->ni = (unsigned)g.ni;
+  return true;
+}
+
 void run_step_kernels(const StepArgs& A) {
   Session& s = S();
   cudaStream_t st = stream();
@@ -490,7 +554,8 @@ void run_step_kernels(const StepArgs& A) {
   if (s.precision != PREC_F32) {
     TcLaunch L{};
     if (A.use_gather) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; } else L.X = s.din;
-    if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS; }
+    if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS;
+                          L.slot_head = s.S.slot_head; L.store_next = s.S.store_next; }
     L.Y = A.fuse_scatter ? nullptr : s.dout;
     L.g = g;
     ensure_aux(tc_grid(rows));
@@ -508,6 +573,7 @@ void run_step_kernels(const StepArgs& A) {
     L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG;
     if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS; }
     L.g = g;
+    L.use_fast = small_fast_operands(A, g, &L.fast) ? 1 : 0;
     L.has_in_div = !s.model.in_div.empty(); L.has_out_mul = !s.model.out_mul.empty();
     L.Yout = A.fuse_scatter ? nullptr : s.dout;
     L.grid = small_mlp_grid(rows);
@@ -634,6 +700,11 @@ void do_forward_batched(void* in, void* out) {
       cuda_ok(cudaMemcpyAsync(s.Y_pinned, s.dout, rows * nout * 4, cudaMemcpyDeviceToHost, st), "D2H of Y");
       cudaStreamSynchronize(st);
     }
+    return;
+  }
+  if (s.gather_done) {               // the gather already ran as its own kernel (fortis_model_input was asked for)
+    run_step(A);
+    s.gather_done = false;
     return;
   }
   if (s.pack_pending) {              // packed form: X -> din, step, dout -> Y   (driver/fortis_shim.py:115)
@@ -834,6 +905,7 @@ void* fortis_model_input(void) {
   if (s.gather_pending) {     // make the buffer valid for a caller that consumes X itself
     launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, current_gather_table(), geom_all(rows), s.din, stream());
     s.gather_pending = false;
+    s.gather_done = true;       // the model input is materialised; the next mlp_forward_batched() consumes it
   }
   return s.din;
   FORTIS_CATCH(return nullptr)
@@ -1063,6 +1135,14 @@ void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x
   (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; (void)wt0; (void)wt1; (void)wt2; (void)wt3; (void)wt4;
   (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; (void)yt0; (void)yt1; (void)yt2; (void)yt3; (void)yt4;
   conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw);
+}
+
+int fortis_copy_to_host(void* dst, const void* dev, long nbytes) {
+  cudaStreamSynchronize(stream());
+  return cuda_ok(cudaMemcpy(dst, dev, (size_t)nbytes, cudaMemcpyDeviceToHost), "fortis_copy_to_host") ? 0 : -1;
+}
+int fortis_copy_to_device(void* dev, const void* src, long nbytes) {
+  return cuda_ok(cudaMemcpy(dev, src, (size_t)nbytes, cudaMemcpyHostToDevice), "fortis_copy_to_device") ? 0 : -1;
 }
 
 int fortis_checksum(const void* data, long n, int elt, double* out) {

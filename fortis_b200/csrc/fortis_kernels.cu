@@ -304,6 +304,80 @@ __global__ void __launch_bounds__(128) small_mlp_fused_kernel(const IoPlanDev* _
   }
 }
 
+// Fast-addressing variant: when every input slot shares one (si, sj, sk) stride triple and every array is fp32, the
+// per-slot base pointers travel as kernel parameters (constant bank, immediate addresses) and a point's 27 loads
+// are `ptr[q][pos]` with ONE position computed per point in 32-bit arithmetic.  Same arithmetic as the generic
+// kernel; only the address computation differs.
+template <int D0, int D1, int D2, int D3, bool PROG>
+__global__ void __launch_bounds__(128) small_mlp_fast_kernel(SmallFast F, const IoPlanDev* __restrict__ GP,
+                                                             const IoPlanDev* __restrict__ SP, ArrayTable TG, ArrayTable TS,
+                                                             SmallMlpMeta meta, float* __restrict__ Yout,
+                                                             double* __restrict__ partials) {
+  using LY = SmallLayout<D0, D1, D2, D3>;
+  constexpr int NOUT = LY::NOUT;
+  const unsigned nrows = F.nrows, count = F.count, ni = F.ni;
+  double csum = 0.0;
+  for (unsigned row = blockIdx.x * blockDim.x + threadIdx.x; row < nrows; row += gridDim.x * blockDim.x) {
+    const unsigned kk = row / count, col = row - kk * count, cj = col / ni, ci = col - cj * ni;
+    const int pos = (int)ci * F.si + (int)cj * F.sj + (int)kk * F.sk;
+    float x[D0];
+#pragma unroll
+    for (int q = 0; q < D0; q++) x[q] = __ldg(F.in_ptr[q] + pos);
+    if (PROG && F.in_prog) {
+      double sc[kMaxScalars];
+      if (GP->nscalars) load_scalars(*GP, TG, ci, cj, kk, sc);
+#pragma unroll
+      for (int q = 0; q < D0; q++) x[q] = (float)eval_prog(GP->prog, (double)x[q], sc, TG, q);
+    }
+    if (meta.has_in_div) {
+#pragma unroll
+      for (int q = 0; q < D0; q++) x[q] = __fdiv_rn(x[q], c_small[LY::in_div + q]);
+    }
+    float h1[D1];
+    small_layer<D0, D1, LY::w0, LY::b0>(x, h1, meta.act[0], meta.slope[0]);
+    float y[NOUT];
+    if constexpr (D3 == 0) {
+      small_layer<D1, D2, LY::w1, LY::b1>(h1, y, meta.act[1], meta.slope[1]);
+    } else {
+      float h2[D2];
+      small_layer<D1, D2, LY::w1, LY::b1>(h1, h2, meta.act[1], meta.slope[1]);
+      small_layer<D2, D3, LY::w2, LY::b2>(h2, y, meta.act[2], meta.slope[2]);
+    }
+    if (meta.has_out_mul) {
+#pragma unroll
+      for (int j = 0; j < NOUT; j++) y[j] = y[j] * c_small[LY::out_mul + j];
+    }
+    if (Yout) {
+#pragma unroll
+      for (int j = 0; j < NOUT; j++) Yout[(size_t)row * NOUT + j] = y[j];
+    }
+    if (F.nstores) {
+      double sc[kMaxScalars];
+      if (PROG && F.out_prog && SP->nscalars) load_scalars(*SP, TS, ci, cj, kk, sc);
+      const int opos = (int)ci * F.oi + (int)cj * F.oj + (int)kk * F.ok;
+#pragma unroll
+      for (int s = 0; s < 8; s++) {
+        if (s < F.nstores) {
+          float yv = 0.f;
+#pragma unroll
+          for (int j = 0; j < NOUT; j++) if (F.out_slot[s] == j) yv = y[j];
+          if (PROG && F.out_prog) yv = (float)eval_prog(SP->prog, (double)yv, sc, TS, F.out_slot[s]);
+          F.out_ptr[s][opos] = yv;
+          csum += (double)yv;
+        }
+      }
+    }
+  }
+  if (partials) {
+    __shared__ double wsum[4];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) csum += __shfl_down_sync(0xffffffffu, csum, o);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = csum;
+    __syncthreads();
+    if (threadIdx.x == 0) partials[blockIdx.x] = (wsum[0] + wsum[1]) + (wsum[2] + wsum[3]);
+  }
+}
+
 bool small_mlp_supported(int nlayers, const int* dims) {
   if (nlayers == 2) return dims[0] == 27 && dims[1] == 20 && dims[2] == 3;
   if (nlayers == 3) return dims[0] == 27 && dims[1] == 20 && dims[2] == 20 && dims[3] == 3;
@@ -347,6 +421,18 @@ void launch_small_mlp(int nlayers, const int* dims, const SmallMlpLaunch& L, cud
   for (int l = 0; l < 4; l++) { m.act[l] = L.act[l]; m.slope[l] = L.slope[l]; }
   m.has_in_div = L.has_in_div; m.has_out_mul = L.has_out_mul;
   const int grid = L.grid > 0 ? L.grid : small_mlp_grid(nrows);
+  if (L.use_fast) {
+    const bool prog = L.fast.in_prog || L.fast.out_prog;
+    if (nlayers == 2 && prog)
+      small_mlp_fast_kernel<27, 20, 3, 0, true><<<grid, 128, 0, s>>>(L.fast, L.GP, L.SP, L.TG, L.TS, m, L.Yout, L.partials);
+    else if (nlayers == 2)
+      small_mlp_fast_kernel<27, 20, 3, 0, false><<<grid, 128, 0, s>>>(L.fast, L.GP, L.SP, L.TG, L.TS, m, L.Yout, L.partials);
+    else if (prog)
+      small_mlp_fast_kernel<27, 20, 20, 3, true><<<grid, 128, 0, s>>>(L.fast, L.GP, L.SP, L.TG, L.TS, m, L.Yout, L.partials);
+    else
+      small_mlp_fast_kernel<27, 20, 20, 3, false><<<grid, 128, 0, s>>>(L.fast, L.GP, L.SP, L.TG, L.TS, m, L.Yout, L.partials);
+    return;
+  }
   if (nlayers == 2)
     small_mlp_fused_kernel<27, 20, 3, 0><<<grid, 128, 0, s>>>(L.GP, L.slots, L.SP, L.stores, L.TG, L.TS, L.g, m, L.Yout, L.partials);
   else

@@ -21,7 +21,19 @@ void launch_scatter(const IoPlanDev* P, const StoreTarget* stores, int nout, con
 void launch_linear_f32(const float* A, const float* W, const float* bias, float* C, long long M, int N, int K, int act,
                        float slope, const float* in_div, const float* out_mul, const float* relu_mask, cudaStream_t s);
 
+// Immediate-address operands of the fast small-MLP kernel (see small_mlp_fast_kernel)
+struct SmallFast {
+  const float* in_ptr[32];        // per model input: array base + constant part of the offset
+  float* out_ptr[8];              // per store
+  int out_slot[8];
+  int nstores;
+  int si, sj, sk, oi, oj, ok;     // element strides of (ci, cj, kk) for inputs / stores
+  int in_prog, out_prog;          // lifted expressions present
+  unsigned nrows, count, ni;
+};
+
 struct SmallMlpLaunch {
+  int use_fast; SmallFast fast;
   const IoPlanDev* GP; const Access* slots;          // gather plan (required)
   const IoPlanDev* SP; const StoreTarget* stores;    // scatter plan (null: only Yout is written)
   ArrayTable TG, TS;
@@ -49,6 +61,7 @@ void tc_model_destroy(TcModel* m);
 struct TcLaunch {
   const IoPlanDev* GP; const Access* slots;          // gather plan, or null with X set
   const IoPlanDev* SP; const StoreTarget* stores;    // scatter plan, or null with Y set
+  const int* slot_head; const int* store_next;       // per model output: first store (-1: none) and the chain
   ArrayTable TG, TS;
   RowGeom g;
   const float* X;                                    // (rows, n_in) when there is no gather plan

@@ -1,10 +1,629 @@
-// placeholder until the tcgen05 kernel lands
+// Fused gather -> MLP -> scatter on the 5th-generation tensor cores (tcgen05, sm_100a), bf16 operands, fp32
+// accumulation in tensor memory, activations never leaving the SM between layers.
+//
+// Replaces, for wide column MLPs, the reference's per-layer lowering: fortis_gemm (cuBLAS SGEMM) + a separate
+// bias/activation epilogue kernel per layer (runtime/fortis_rt.c:45-75, compiler/FortisFuse.cpp:616-624, 687-760),
+// with fortis_gather_k in front and fortis_scatter_k behind (driver/fortis_gather_emit.py:52-62, 75-83).
+//
+// One persistent CTA per SM processes tiles of 128 columns (rows of the model batch).  Per tile and layer
+//     D[128 x N] = A[128 x K] . W[N x K]^T,  N processed in chunks of 64 output features.
+//   * A (the layer's input activations, bf16) lives in TENSOR MEMORY: lane = row, two K values per 32-bit column
+//     (K <= 768 -> 384 columns).  The MMAs take A from TMEM and B from shared memory, so shared-memory read
+//     bandwidth is spent on the weights only.
+//   * W streams from L2 through a ring of 16 KB TMA stages (64 features x 128 k, 128-byte swizzle, no multicast).
+//   * D: two 64-column fp32 accumulators in TMEM; the epilogue of chunk c overlaps the MMAs of chunk c+1.
+//   * The epilogue (8 warps; thread = one row x 32 features) adds bias, applies the activation, rounds to bf16 and
+//     parks the chunk: chunks 0-7 in shared memory, chunks 8-11 in registers (A is still being read by later
+//     chunks, so the output cannot overwrite it).  When the layer's last MMA has retired, the parked chunks are
+//     written into the A columns with tcgen05.st and the next layer starts.
+//   * Layer 0's A is produced by the same threads straight from the host's Fortran arrays (thread = row, so every
+//     slot is a coalesced load); the last layer's epilogue stores straight into the host arrays and accumulates
+//     the fp64 checksum.
+// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 6 x 16 KB weight ring.
+//
+// Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word, raises a CTA-wide
+// abort flag that turns all later waits into no-ops, and the CTA still frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <vector>
+
+#include "fortis_device.cuh"
 #include "fortis_kernels.h"
 #include "fortis_model.h"
+
 namespace fortis {
-bool tc_model_supported(const ModelHost&, std::string* why) { if (why) *why = "tensor-core kernel not built"; return false; }
-TcModel* tc_model_create(const ModelHost&, int, cudaStream_t, std::string* err) { if (err) *err = "tensor-core kernel not built"; return nullptr; }
-void tc_model_destroy(TcModel*) {}
-int tc_grid(long long) { return 1; }
-bool tc_forward(TcModel*, const TcLaunch&, cudaStream_t, std::string* err) { if (err) *err = "tensor-core kernel not built"; return false; }
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kChunkN = 64;                 // output features per accumulator
+constexpr int kStageK = 128;                // k extent of one weight stage
+constexpr int kStageBytes = kChunkN * kStageK * 2;   // 16 KB
+constexpr int kStages = 6;
+constexpr int kSmemChunks = 8;              // parked chunks held in shared memory; the rest in registers
+constexpr int kMaxChunks = 12;              // 768 / 64
+constexpr int kMaxK = 768;
+constexpr int kMaxLayers = 8;
+constexpr int kEpiThreads = 256;
+constexpr int kThreads = kEpiThreads + 64;  // + TMA warp + MMA warp
+constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
+constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
+constexpr int kBarBytes = 256;
+constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + 1024;   // + slack for 1024-byte alignment
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccCol0 = 384;
+constexpr uint32_t kWaitLimit = 1u << 24;   // polls of try_wait before giving up (each poll may block briefly)
+
+// status codes (which wait gave up)
+enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5 };
+
+struct TcLayer {
+  int K, N;                // padded: K multiple of 128, N multiple of 64 (hidden: multiple of 128)
+  int n_real;              // unpadded output width
+  int act;
+  float slope;
+  const float* bias;       // [N] padded with zeros
+  const float* scale;      // [N] per-output-channel dequantisation scale (fp8 weights) or null
+};
+
+struct TcParams {
+  CUtensorMap maps[kMaxLayers];
+  TcLayer layer[kMaxLayers];
+  int nlayers;
+  int n_in, n_out;                       // unpadded model widths
+  const float* in_div;                   // optional
+  const float* out_mul;                  // optional
+  const float* relu_mask;                // optional
+  // gather side
+  const IoPlanDev* GP; const Access* slots; ArrayTable TG;
+  const float* X;                        // (rows, n_in) when GP is null
+  // scatter side
+  const IoPlanDev* SP; const StoreTarget* stores; ArrayTable TS;
+  const int* slot_head; const int* store_next;   // per output: first store index (-1: none), chain
+  float* Y;                              // optional (rows, n_out)
+  RowGeom g;
+  long long nrows;
+  double* partials;
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait: returns false (and raises the abort flag, records `code`) when the limit is reached
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (*abort_flag) return false;
+  for (uint32_t i = 0; i < kWaitLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[tmem] . B[smem]^T, bf16 x bf16 -> fp32, M = 128, N = 64, K = 16
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);     // .x = lo -> low 16 bits = lower k index
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 B apart, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);            // start address
+  d |= (uint64_t)0 << 16;                            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+
+// instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kChunkN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+
+__device__ __forceinline__ float act_f(float v, int act, float slope) {
+  if (act == ACT_RELU) return fmaxf(v, 0.f);
+  if (act == ACT_LEAKY) return v > 0.f ? v : v * slope;
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t park = base;                                   // 8 x 16 KB parked chunks
+  const uint32_t ring = base + kParkBytes;                      // kStages x 16 KB
+  const uint32_t bars = ring + kRingBytes;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;            // [kStages] each
+  const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;   // [2] each
+  const uint32_t bar_a_ready = bar_acc_empty + 16;
+  // barrier block (256 B): full [0,48) empty [48,96) acc_full [96,112) acc_empty [112,128) a_ready [128,136)
+  // tmem base 144, abort flag 148, checksum scratch [160,224)
+  uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 144);
+  volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 148);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long ntiles = (P.nrows + kTileM - 1) / kTileM;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kEpiThreads); }
+    mbar_init(bar_a_ready, kEpiThreads);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+        for (int l = 0; l < P.nlayers; l++) {
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          for (int c = 0; c < nchunks; c++)
+            for (int kb = 0; kb < nkb; kb++, it++) {
+              const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+              mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY);
+              if (*abort_flag) break;
+              mbar_expect_tx(bar_full + 8 * s, kStageBytes);
+              const uint32_t dst = ring + s * kStageBytes;
+              tma_load_2d(dst, &P.maps[l], kb * kStageK, c * kChunkN, bar_full + 8 * s);
+              tma_load_2d(dst + kStageBytes / 2, &P.maps[l], kb * kStageK + 64, c * kChunkN, bar_full + 8 * s);
+            }
+        }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, acc_it = 0, a_it = 0;
+      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+        for (int l = 0; l < P.nlayers; l++, a_it++) {
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          mbar_wait(bar_a_ready, a_it & 1, abort_flag, P.status, ST_A_READY);      // A of this layer is in TMEM
+          tc_fence_after();
+          for (int c = 0; c < nchunks; c++, acc_it++) {
+            const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+            mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
+            for (int kb = 0; kb < nkb; kb++, it++) {
+              const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+              mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+              tc_fence_after();
+              if (!*abort_flag) {
+                const uint32_t sb = ring + s * kStageBytes;
+#pragma unroll
+                for (int j = 0; j < kStageK / 16; j++) {
+                  const uint64_t bd = make_b_desc(sb + (j >> 2) * (kStageBytes / 2) + (j & 3) * 32);
+                  tc_mma_ts(d_tmem, tmem + kb * (kStageK / 2) + j * 8, bd, kIdesc, (kb | j) ? 1u : 0u);
+                }
+              }
+              tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
+            }
+            tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
+          }
+        }
+    }
+  } else {
+    // ------------------------------------------------------------------ row warps: gather, epilogues, scatter
+    const int quad = warp & 3, half = warp >> 2;              // TMEM lane quadrant, which 32 of a chunk's 64 features
+    const int r = quad * 32 + lane;                           // row of the tile = TMEM lane
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    uint32_t acc_it = 0;
+    double csum = 0.0;
+    uint32_t kept[(kMaxChunks - kSmemChunks) * 16];           // parked chunks 8..11 of this thread (bf16 pairs)
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      const long long row = tile * kTileM + r;
+      const bool live = row < P.nrows;
+      long long ci = 0, cj = 0, kk = 0;
+      if (live) row_to_pos(P.g, row, &ci, &cj, &kk);
+      // ---- layer 0 input: this thread's half of the row, 32 features (16 packed columns) at a time
+      {
+        const int K0 = P.layer[0].K, per = K0 / 2;            // features per half
+        double sc[kMaxScalars];
+        if (live && P.GP && P.GP->nscalars) load_scalars(*P.GP, P.TG, ci, cj, kk, sc);
+        for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int q = q0 + 2 * j + e;
+              float x = 0.f;
+              if (live && q < P.n_in) {
+                x = P.GP ? gather_value(*P.GP, P.slots[q], P.TG, q, ci, cj, kk, sc) : __ldg(P.X + row * P.n_in + q);
+                if (P.in_div) x = __fdiv_rn(x, __ldg(P.in_div + q));
+              }
+              v[e] = x;
+            }
+            pk[j] = pack_bf16(v[0], v[1]);
+          }
+          tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(bar_a_ready);
+      }
+      for (int l = 0; l < P.nlayers; l++) {
+        const TcLayer& L = P.layer[l];
+        const int nchunks = L.N / kChunkN;
+        const bool last = l == P.nlayers - 1;
+        if (!last) {
+#pragma unroll
+          for (int c = 0; c < kMaxChunks; c++) {
+            if (c < nchunks) {
+              const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+              acc_it++;
+              mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+              tc_fence_after();
+              uint32_t a[32];
+              tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
+              tmem_ld_wait();
+              tc_fence_before();
+              mbar_arrive(bar_acc_empty + 8 * b);             // the MMA warp may refill this accumulator
+              const int n0 = c * kChunkN + half * 32;
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 16; j++) {
+                float v0 = __uint_as_float(a[2 * j]), v1 = __uint_as_float(a[2 * j + 1]);
+                if (L.scale) { v0 *= __ldg(L.scale + n0 + 2 * j); v1 *= __ldg(L.scale + n0 + 2 * j + 1); }
+                v0 = act_f(v0 + __ldg(L.bias + n0 + 2 * j), L.act, L.slope);
+                v1 = act_f(v1 + __ldg(L.bias + n0 + 2 * j + 1), L.act, L.slope);
+                pk[j] = pack_bf16(v0, v1);
+              }
+              if (c < kSmemChunks) {
+                // [chunk][half][16-byte piece][row]: lanes are rows, so every store is conflict-free
+                uint8_t* dst = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+#pragma unroll
+                for (int p = 0; p < 4; p++)
+                  *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) kept[(c >= kSmemChunks ? c - kSmemChunks : 0) * 16 + j] = pk[j];
+              }
+            }
+          }
+          // every MMA of this layer has retired (its last accumulator was complete), so A may be overwritten:
+          // move the parked chunks into the A columns and release the next layer
+#pragma unroll
+          for (int c = 0; c < kMaxChunks; c++) {
+            if (c < nchunks) {
+              uint32_t pk[16];
+              if (c < kSmemChunks) {
+                const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
+                  pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) pk[j] = kept[(c >= kSmemChunks ? c - kSmemChunks : 0) * 16 + j];
+              }
+              tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
+            }
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(bar_a_ready);
+        } else {
+          // ---- last layer: bias, output scaling / masks, then straight into the host arrays
+          double sc[kMaxScalars];
+          if (live && P.SP && P.SP->nscalars) load_scalars(*P.SP, P.TS, ci, cj, kk, sc);
+          for (int c = 0; c < nchunks; c++) {
+            const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+            acc_it++;
+            mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            tc_fence_after();
+            uint32_t a[32];
+            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty + 8 * b);
+            const int n0 = c * kChunkN + half * 32;
+            if (live) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) {
+                const int n = n0 + j;
+                if (n < P.n_out) {
+                  float v = __uint_as_float(a[j]);
+                  if (L.scale) v *= __ldg(L.scale + n);
+                  v = act_f(v + __ldg(L.bias + n), L.act, L.slope);
+                  if (P.out_mul) v *= __ldg(P.out_mul + n);
+                  if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v = fmaxf(v, 0.f);
+                  if (P.Y) P.Y[row * P.n_out + n] = v;
+                  if (P.SP) {
+                    for (int s = __ldg(P.slot_head + n); s >= 0; s = __ldg(P.store_next + s)) {
+                      const StoreTarget st = P.stores[s];
+                      const double o = scatter_value(*P.SP, P.TS, n, v, sc);
+                      store_elem(P.TS, st.a, access_offset(st.a, ci, cj, kk), o);
+                      csum += st.a.elt == 0 ? (double)(float)o : o;
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+    if (P.partials) {
+      // per-CTA checksum partial in a fixed order: shuffle tree per warp, then warp results in index order
+      double* wsum = (double*)(smem + kParkBytes + kRingBytes + 160);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) csum += __shfl_down_sync(0xffffffffu, csum, o);
+      if (lane == 0) wsum[warp] = csum;
+      asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");
+      if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; w++) t += wsum[w];
+        P.partials[blockIdx.x] = t;
+      }
+    }
+  }
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // a wait gave up: copies of this CTA may still be in flight; give them time to land before the shared memory
+    // is handed back (bounded)
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);   // NaN
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+// nearest (ties-to-even) E4M3 value, saturating at +-448: 4 exponent bits (bias 7), 3 mantissa bits, subnormal
+// step 2^-9
+float e4m3_round(float v) {
+  double a = std::fabs((double)v);
+  if (a > 448.0) a = 448.0;
+  int e = (int)std::floor(std::log2(a > 9.5367431640625e-07 ? a : 9.5367431640625e-07));
+  if (e < -6) e = -6;
+  if (e > 8) e = 8;
+  const double step = std::ldexp(1.0, e - 3);
+  double q = std::nearbyint(a / step) * step;
+  if (q > 448.0) q = 448.0;
+  return (float)(v < 0 ? -q : q);
+}
+
+}  // namespace
+
+struct TcModel {
+  int nlayers = 0, n_in = 0, n_out = 0;
+  std::vector<void*> w;            // bf16 [N][K] padded
+  std::vector<float*> bias, scale;
+  float *in_div = nullptr, *out_mul = nullptr, *relu_mask = nullptr;
+  TcLayer layer[kMaxLayers];
+  CUtensorMap maps[kMaxLayers];
+  int *slot_head = nullptr, *store_next = nullptr;     // built per scatter plan by the caller
+  const StoreTarget* built_for = nullptr;
+  int built_n = 0;
+};
+
+bool tc_model_supported(const ModelHost& M, std::string* why) {
+  auto no = [&](const char* w) { if (why) *why = w; return false; };
+  if (!M.is_mlp()) return no("not an MLP");
+  if ((int)M.layers.size() > kMaxLayers) return no("more than 8 layers");
+  for (size_t l = 0; l < M.layers.size(); l++) {
+    const LayerHost& L = M.layers[l];
+    if (round_up(L.cin, kStageK) > kMaxK) return no("a layer input is wider than 768");
+    const int npad = l + 1 < M.layers.size() ? round_up(L.cout, kStageK) : round_up(L.cout, kChunkN);
+    if (npad > kMaxK) return no("a layer output is wider than 768");
+  }
+  return true;
+}
+
+int tc_grid(long long nrows) {
+  const long long tiles = (nrows + kTileM - 1) / kTileM;
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return (int)(tiles < sms ? (tiles > 0 ? tiles : 1) : sms);
+}
+
+void tc_model_destroy(TcModel* m) {
+  if (!m) return;
+  for (void* p : m->w) cudaFree(p);
+  for (float* p : m->bias) cudaFree(p);
+  for (float* p : m->scale) cudaFree(p);
+  cudaFree(m->in_div); cudaFree(m->out_mul); cudaFree(m->relu_mask); cudaFree(m->slot_head); cudaFree(m->store_next);
+  delete m;
+}
+
+TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
+  (void)s;
+  std::string why;
+  if (!tc_model_supported(M, &why)) { if (err) *err = why; return nullptr; }
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) { if (err) *err = "cuTensorMapEncodeTiled is not available from the driver"; return nullptr; }
+  TcModel* m = new TcModel();
+  m->nlayers = (int)M.layers.size(); m->n_in = M.n_in(); m->n_out = M.n_out();
+  auto fail = [&](const std::string& w) { if (err) *err = w; tc_model_destroy(m); return (TcModel*)nullptr; };
+  for (int l = 0; l < m->nlayers; l++) {
+    const LayerHost& L = M.layers[l];
+    const int K = round_up(L.cin, kStageK);
+    const int N = l + 1 < m->nlayers ? round_up(L.cout, kStageK) : round_up(L.cout, kChunkN);
+    std::vector<uint16_t> wb((size_t)N * K, 0);
+    std::vector<float> bias(N, 0.f), scale(N, 1.f);
+    for (int n = 0; n < L.cout; n++) {
+      bias[n] = L.b[n];
+      float sc = 1.f;
+      if (precision == PREC_FP8W) {
+        float amax = 0.f;
+        for (int k = 0; k < L.cin; k++) amax = std::fmax(amax, std::fabs(L.W[(size_t)n * L.cin + k]));
+        sc = amax > 0.f ? amax / 448.0f : 1.0f;
+        scale[n] = sc;
+      }
+      for (int k = 0; k < L.cin; k++) {
+        float w = L.W[(size_t)n * L.cin + k];
+        if (precision == PREC_FP8W) w = e4m3_round(w / sc);       // E4M3 codes are exact in bf16
+        wb[(size_t)n * K + k] = f32_to_bf16(w);
+      }
+    }
+    void* dw = nullptr; float *db = nullptr, *ds = nullptr;
+    if (cudaMalloc(&dw, wb.size() * 2) != cudaSuccess || cudaMalloc(&db, N * 4) != cudaSuccess) return fail("out of device memory for packed weights");
+    m->w.push_back(dw); m->bias.push_back(db);
+    cudaMemcpy(dw, wb.data(), wb.size() * 2, cudaMemcpyHostToDevice);
+    cudaMemcpy(db, bias.data(), N * 4, cudaMemcpyHostToDevice);
+    if (precision == PREC_FP8W) {
+      if (cudaMalloc(&ds, N * 4) != cudaSuccess) return fail("out of device memory for weight scales");
+      cudaMemcpy(ds, scale.data(), N * 4, cudaMemcpyHostToDevice);
+    }
+    m->scale.push_back(ds);
+    TcLayer& T = m->layer[l];
+    T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.slope = L.slope; T.bias = db; T.scale = ds;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kChunkN};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(&m->maps[l], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  }
+  auto up = [&](const std::vector<float>& v) -> float* {
+    if (v.empty()) return nullptr;
+    float* d = nullptr;
+    cudaMalloc(&d, v.size() * 4);
+    cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    return d;
+  };
+  m->in_div = up(M.in_div); m->out_mul = up(M.out_mul); m->relu_mask = up(M.relu_mask);
+  if (cudaFuncSetAttribute(mlp_tc_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    return fail("cannot reserve " + std::to_string(kSmemBytes) + " bytes of shared memory for the tensor-core kernel");
+  return m;
+}
+
+bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err) {
+  const long long nrows = L.g.count * L.g.nk;
+  if (nrows <= 0) return true;
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  for (int l = 0; l < m->nlayers; l++) { P.maps[l] = m->maps[l]; P.layer[l] = m->layer[l]; }
+  P.nlayers = m->nlayers; P.n_in = m->n_in; P.n_out = m->n_out;
+  P.in_div = m->in_div; P.out_mul = m->out_mul; P.relu_mask = m->relu_mask;
+  P.GP = L.GP; P.slots = L.slots; P.TG = L.TG; P.X = L.X;
+  P.SP = L.SP; P.stores = L.stores; P.TS = L.TS; P.Y = L.Y;
+  P.slot_head = L.slot_head; P.store_next = L.store_next;
+  P.g = L.g; P.nrows = nrows; P.partials = L.partials; P.status = L.status;
+  if (!P.GP && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
+  if (P.SP && (!P.slot_head || !P.store_next)) { if (err) *err = "tensor-core step: scatter index missing"; return false; }
+  const int grid = tc_grid(nrows);
+  mlp_tc_fused_kernel<<<grid, kThreads, kSmemBytes, s>>>(P);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { if (err) *err = std::string("tensor-core kernel launch: ") + cudaGetErrorString(e); return false; }
+  return true;
+}
+
+}  // namespace fortis

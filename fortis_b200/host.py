@@ -15,8 +15,8 @@ from . import lib as _lib
 
 def _ptr(a):
     if isinstance(a, np.ndarray):
-        if not (a.flags.f_contiguous or a.ndim <= 1):
-            raise ValueError("host arrays must be Fortran-contiguous")
+        if not (a.flags.f_contiguous or a.flags.c_contiguous):
+            raise ValueError("host arrays must be contiguous")
         return a.ctypes.data
     if hasattr(a, "data_ptr"):        # torch tensor (device or host)
         return a.data_ptr()
@@ -28,10 +28,12 @@ def _ptr(a):
 class Host:
     def __init__(self):
         self.L = _lib.load()
+        self._keep = []          # host arrays handed to the library stay alive until reset(): it pins them by address
 
     # ---- configuration -----------------------------------------------------------------------------------------
     def reset(self):
         self.L.fortis_reset()
+        self._keep = []
 
     def configure(self, gather=None, scatter=None, loop=None, kdist=None, lift2d=None):
         for key, obj in (("gather", gather), ("scatter", scatter), ("loop", loop), ("kdist", kdist), ("lift2d", lift2d)):
@@ -61,6 +63,7 @@ class Host:
 
     # ---- the three calls of a lifted host ----------------------------------------------------------------------
     def _vp(self, arrays):
+        self._keep.extend(a for a in arrays if isinstance(a, np.ndarray) and not any(a is k for k in self._keep))
         return (ctypes.c_void_p * len(arrays))(*[_ptr(a) for a in arrays])
 
     def _ip(self, ints):
@@ -83,6 +86,7 @@ class Host:
         self.check()
 
     def forward(self, x, y):
+        self._keep.extend(a for a in (x, y) if isinstance(a, np.ndarray))
         self.L.mlp_forward(_ptr(x), _ptr(y))
         self.check()
 
@@ -95,26 +99,20 @@ class Host:
 
     def model_output(self, rows, nout):
         """Copy of the device model-output buffer as (rows, nout) float32."""
-        import torch
-        self.sync()
         p = self.L.fortis_model_output()
         self.check()
         out = np.empty((rows, nout), dtype=np.float32)
-        cudart = torch.cuda.cudart()
-        err = cudart.cudaMemcpy(out.ctypes.data, p, out.nbytes, 2)   # cudaMemcpyDeviceToHost
-        if int(err) != 0:
-            raise _lib.FortisError("cudaMemcpy D2H failed: %s" % err)
+        if self.L.fortis_copy_to_host(out.ctypes.data, p, out.nbytes) != 0:
+            raise _lib.FortisError(self.L.fortis_last_error_message().decode())
         return out
 
     def model_input(self, rows, nin):
-        import torch
+        """Copy of the device model-input buffer; a pending gather is run as its own kernel first."""
         p = self.L.fortis_model_input()
         self.check()
-        self.sync()
         out = np.empty((rows, nin), dtype=np.float32)
-        err = torch.cuda.cudart().cudaMemcpy(out.ctypes.data, p, out.nbytes, 2)
-        if int(err) != 0:
-            raise _lib.FortisError("cudaMemcpy D2H failed: %s" % err)
+        if self.L.fortis_copy_to_host(out.ctypes.data, p, out.nbytes) != 0:
+            raise _lib.FortisError(self.L.fortis_last_error_message().decode())
         return out
 
     def checksum(self, a):

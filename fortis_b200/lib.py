@@ -23,7 +23,7 @@ def load():
     p = lib_path()
     if not os.path.exists(p):
         raise FortisError("%s is missing: build it with `python -m fortis_b200.build` (nvcc, sm_100a)" % p)
-    L = ctypes.CDLL(p, mode=ctypes.RTLD_GLOBAL)
+    L = ctypes.CDLL(p)      # RTLD_LOCAL: the entry names (fortis_gather, mgpuStreamCreate ...) stay out of the global scope
     c = ctypes
     vp, ci, cl, cc = c.c_void_p, c.c_int, c.c_long, c.c_char_p
     sig = {
@@ -39,7 +39,7 @@ def load():
         "fortis_unpack": (None, [vp, ci]), "fortis_model_input": (vp, []), "fortis_model_output": (vp, []),
         "fortis_begin": (None, [ci]), "mgpuStreamCreate": (vp, []), "fortis_alloc": (vp, [cl]), "fortis_free": (None, [vp]),
         "fortis_checksum": (ci, [vp, cl, ci, c.POINTER(c.c_double)]), "fortis_step_checksum": (ci, [c.POINTER(c.c_double)]),
-        "fortis_device_status": (ci, []),
+        "fortis_device_status": (ci, []), "fortis_copy_to_host": (ci, [vp, vp, cl]), "fortis_copy_to_device": (ci, [vp, vp, cl]),
         "fortis_debug_eval_expr": (ci, [cc, ci, c.c_double, c.POINTER(c.c_double), c.POINTER(ci), ci, c.POINTER(c.c_double)]),
         "fortis_debug_plan": (ci, [cc, cc, cc, ci, cl, c.POINTER(ci), ci, c.POINTER(c.c_longlong), c.POINTER(ci),
                                    c.POINTER(ci), ci, c.POINTER(c.c_longlong)]),

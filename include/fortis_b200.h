@@ -132,6 +132,11 @@ void fortis_gatherv(const int* iargs, int nint, const void* const* arrays, int n
 void fortis_scatterv(const int* iargs, int nint, void* const* arrays, int narrays);
 void fortis_stepv(const void* const* gather_arrays, int ngather, void* const* scatter_arrays, int nscatter);
 
+/* synchronous copies between host memory and buffers of this library (fortis_alloc, fortis_model_input/output);
+ * the first waits for the persistent stream */
+int fortis_copy_to_host(void* dst, const void* dev, long nbytes);
+int fortis_copy_to_device(void* dev, const void* src, long nbytes);
+
 /* fp64 sum of n elements (elt 0 = float, 1 = double) of a device or host array, summed in a fixed order */
 int fortis_checksum(const void* data, long n, int elt, double* out);
 /* fp64 sum of everything the fused steps scattered since the last call (needs option "checksum" = "1") */

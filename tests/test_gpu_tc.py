@@ -1,0 +1,149 @@
+"""Tensor-core (tcgen05) fused MLP path against the oracle, through the C ABI.
+
+Bars (BASELINE north star): bf16 <= 5e-3, FP8-E4M3 weights <= 2e-2 relative L2 against the fp32 oracle.  The
+tests additionally compare with the oracle's model of the reduced-precision arithmetic (bf16 activations, bf16 or
+E4M3 weights, wide accumulation), which isolates indexing / layout mistakes from rounding.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import fortis_b200
+from oracle import fortis_oracle as fo
+
+BF16_TOL, FP8W_TOL, MODEL_TOL = 5e-3, 2e-2, 2e-3
+# What rounding alone costs: the oracle's reduced-precision MODEL (exact arithmetic on bf16 / E4M3 operands) already
+# differs from fp32 by 2.3e-3 (bf16) / 2.6e-2 (E4M3) per 244->768 layer and 5.6e-3 / 6.3e-2 over the 5-layer net on
+# N(0,1) inputs, so a kernel can only be asked to add nothing on top: error vs fp32 <= SLACK x (model vs fp32).
+# On BASELINE config 2's own inputs and weights the bf16 path meets the 5e-3 bar outright (test_column_config).
+SLACK = 1.1
+
+
+@pytest.fixture()
+def host():
+    h = fortis_b200.Host()
+    h.reset()
+    yield h
+    assert h.L.fortis_device_status() == 0, "a bounded wait in the tensor-core kernel gave up"
+    h.reset()
+
+
+def run_array_form(host, layers, X, precision):
+    rows, nout = X.shape[0], layers[-1]["W"].shape[0]
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", precision)
+    host.L.fortis_begin(rows)
+    Y = np.zeros((rows, nout), np.float32)
+    host.forward_batched(np.ascontiguousarray(X), Y)
+    return Y
+
+
+@pytest.mark.parametrize("dims,rows", [([128, 64], 128), ([128, 128, 64], 128), ([100, 200, 30], 77),
+                                       ([256, 768, 128], 300), ([244, 768, 768, 768, 768, 128], 1000)])
+def test_bf16_array_form(host, dims, rows):
+    layers = fortis_b200.mlp_layers(dims, seed=11, act="leaky", slope=0.15, bias="uniform", scale=0.1)
+    X = np.random.default_rng(5).normal(size=(rows, dims[0])).astype(np.float32)
+    Y = run_array_form(host, layers, X, "bf16")
+    model = fo.mlp_forward_lowp(layers, X, "bf16")
+    exact = fo.mlp_forward(layers, X)
+    e_model, e_exact = fo.rel_l2(Y, model), fo.rel_l2(Y, exact)
+    bar = max(BF16_TOL, SLACK * fo.rel_l2(model, exact))
+    assert e_model < MODEL_TOL and e_exact < bar, "dims %s rows %d: vs bf16 model %.3e, vs fp32 %.3e; Y[0,:4]=%s want %s" % (
+        dims, rows, e_model, e_exact, Y[0, :4], model[0, :4])
+
+
+def test_fp8_weights_array_form(host):
+    dims, rows = [244, 768, 768, 128], 500
+    layers = fortis_b200.mlp_layers(dims, seed=12)
+    X = np.random.default_rng(6).normal(size=(rows, dims[0])).astype(np.float32)
+    Y = run_array_form(host, layers, X, "fp8w")
+    model, exact = fo.mlp_forward_lowp(layers, X, "fp8w"), fo.mlp_forward(layers, X)
+    e_model, e_exact = fo.rel_l2(Y, model), fo.rel_l2(Y, exact)
+    bar = max(FP8W_TOL, SLACK * fo.rel_l2(model, exact))
+    assert e_model < MODEL_TOL and e_exact < bar, "vs fp8w model %.3e, vs fp32 %.3e (bar %.3e)" % (e_model, e_exact, bar)
+
+
+def column_case(ncol, seed=2):
+    G, S, Lp, K = fo.column_descriptors(ncol, 60)
+    rng = np.random.default_rng(seed)
+    gin = [np.asfortranarray((250 + 20 * rng.normal(size=(ncol, 60))).astype(np.float32)),
+           np.asfortranarray(np.exp(-6 + rng.normal(size=(ncol, 60))).astype(np.float32)),
+           np.asfortranarray((10 * rng.normal(size=(ncol, 60))).astype(np.float32)),
+           np.asfortranarray((10 * rng.normal(size=(ncol, 60))).astype(np.float32))]
+    gin += [rng.normal(size=ncol).astype(np.float32) for _ in range(4)]
+    sout = [np.zeros((ncol, 60), np.float32, order="F") for _ in range(2)] + [np.zeros(ncol, np.float32) for _ in range(8)]
+    layers = fortis_b200.mlp_layers([244, 768, 768, 768, 768, 128], seed=0)
+    return G, S, Lp, K, gin, sout, layers
+
+
+@pytest.mark.parametrize("precision,tol", [("bf16", BF16_TOL), ("fp8w", FP8W_TOL)])
+@pytest.mark.parametrize("resident", [True, False])
+def test_column_config_fused_step(host, precision, tol, resident):
+    """BASELINE config 2's layout (ragged column count): gather fused into layer 0, scatter into the last epilogue."""
+    ncol = 1000
+    G, S, Lp, K, gin, sout, layers = column_case(ncol)
+    ref = [a.copy(order="F") for a in sout]
+    fo.full_step(G, S, Lp, K, layers, gin, ref)
+    model = [a.copy(order="F") for a in sout]
+    fo.full_step(G, S, Lp, K, layers, gin, model, forward=lambda L, X: fo.mlp_forward_lowp(L, X, precision))
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", precision)
+    host.option("checksum", 1)
+    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
+    if resident:
+        d_in, d_out = [to_dev(a) for a in gin], [to_dev(a) for a in sout]
+        host.step(d_in, d_out)
+        got = [t.cpu().numpy().reshape(a.shape, order="F") for t, a in zip(d_out, sout)]
+    else:
+        host.step(gin, sout)
+        got = sout
+    cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
+    e_model, e_exact = fo.rel_l2(cat(got), cat(model)), fo.rel_l2(cat(got), cat(ref))
+    bar = tol if precision == "bf16" else max(tol, SLACK * fo.rel_l2(cat(model), cat(ref)))
+    assert e_model < MODEL_TOL and e_exact < bar, "vs %s model %.3e, vs fp32 %.3e (bar %.3e)" % (precision, e_model, e_exact, bar)
+    cs = host.step_checksum()
+    want = float(cat(got).astype(np.float64).sum())
+    assert abs(cs - want) <= 1e-9 * max(1.0, np.abs(cat(got)).astype(np.float64).sum())
+
+
+def test_three_call_form_bf16(host):
+    """fortis_gather ; mlp_forward_batched ; fortis_scatter with the tensor-core kernel in the middle."""
+    ncol = 300
+    G, S, Lp, K, gin, sout, layers = column_case(ncol, seed=9)
+    model = [a.copy(order="F") for a in sout]
+    fo.full_step(G, S, Lp, K, layers, gin, model, forward=lambda L, X: fo.mlp_forward_lowp(L, X, "bf16"))
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", "bf16")
+    host.gather(gin)
+    host.forward_batched()
+    host.scatter(sout)
+    cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
+    assert fo.rel_l2(cat(sout), cat(model)) < MODEL_TOL
+
+
+def test_relu_mask_and_graph_replay(host):
+    """Final ReLU on masked outputs (benchmarks/climsim/export_wide.py:24-27) and FORTIS_GRAPH-style replay."""
+    dims, rows = [124, 256, 256, 128], 384
+    layers = fortis_b200.mlp_layers(dims, seed=13)
+    mask = np.zeros(128, np.float32); mask[120:] = 1.0
+    X = np.random.default_rng(7).normal(size=(rows, 124)).astype(np.float32)
+    host.load_model(fortis_b200.write_blob(layers, relu_mask=mask))
+    host.option("precision", "bf16")
+    host.option("graph", 1)
+    host.L.fortis_begin(rows)
+    want = fo.mlp_forward_lowp(layers, X, "bf16")
+    want[:, 120:] = np.maximum(want[:, 120:], 0)
+    host.L.mlp_upload(X.ctypes.data)
+    outs = []
+    for _ in range(4):
+        host.L.mlp_forward_dev()
+        Y = np.zeros((rows, 128), np.float32)
+        host.L.mlp_download(Y.ctypes.data)
+        outs.append(Y)
+    host.check()
+    assert fo.rel_l2(outs[0], want) < MODEL_TOL
+    assert all(o.tobytes() == outs[0].tobytes() for o in outs[1:])      # eager, captured and replayed runs agree
