@@ -98,6 +98,9 @@ struct PlanDev {
   std::vector<char> on_dev;
   void* vec_dev[kMaxVecs] = {};
   int *slot_head = nullptr, *store_next = nullptr;   // scatter: stores indexed by model output
+  Access* store_by_slot = nullptr;                   // scatter: one store target per model output (fast path)
+  bool fast = false;                                 // fp32 only, no expressions / scalars, <= 2 stride classes
+  long long cls[2][3] = {{0, 0, 0}, {0, 0, 0}};
 };
 
 struct Session {
@@ -157,7 +160,7 @@ void free_plan(PlanDev& P) {
     if (P.reg[i] && P.reg[i] != (const void*)1) { cudaHostUnregister((void*)P.reg[i]); cudaGetLastError(); }
   for (void* p : P.stage) pool_free(p);
   for (void*& v : P.vec_dev) { pool_free(v); v = nullptr; }
-  pool_free(P.hdr); pool_free(P.items); pool_free(P.slot_head); pool_free(P.store_next);
+  pool_free(P.hdr); pool_free(P.items); pool_free(P.slot_head); pool_free(P.store_next); pool_free(P.store_by_slot);
   P = PlanDev();
 }
 
@@ -207,6 +210,27 @@ void upload_plan(PlanDev& P) {
     P.store_next = (int*)pool_alloc((long)(next.size() * 4));
     cudaMemcpy(P.slot_head, head.data(), head.size() * 4, cudaMemcpyHostToDevice);
     cudaMemcpy(P.store_next, next.data(), next.size() * 4, cudaMemcpyHostToDevice);
+  }
+  // fast-path eligibility and stride classes
+  {
+    std::vector<Access> acc;
+    if (!P.h.is_scatter) acc = P.h.slots; else for (auto& t : P.h.stores) acc.push_back(t.a);
+    bool ok = P.h.prog.nops == 0 && P.h.scalars.empty() && !acc.empty() && P.h.arrays.size() < 0x7F;
+    int ncls = 0;
+    for (auto& a : acc) {
+      if (a.elt != 0 || a.off0 < 0 || a.off0 >= (1LL << 32)) { ok = false; break; }
+      int c = -1;
+      for (int i = 0; i < ncls; i++) if (P.cls[i][0] == a.si && P.cls[i][1] == a.sj && P.cls[i][2] == a.sk) c = i;
+      if (c < 0) { if (ncls == 2) { ok = false; break; } P.cls[ncls][0] = a.si; P.cls[ncls][1] = a.sj; P.cls[ncls][2] = a.sk; ncls++; }
+    }
+    if (P.h.is_scatter && ok) {
+      std::vector<Access> by(P.h.n > 0 ? P.h.n : 1);
+      for (auto& b : by) { std::memset(&b, 0, sizeof b); b.array = -1; }
+      for (auto& t : P.h.stores) { if (by[t.slot].array >= 0) ok = false; by[t.slot] = t.a; }
+      P.store_by_slot = (Access*)pool_alloc((long)(by.size() * sizeof(Access)));
+      cudaMemcpy(P.store_by_slot, by.data(), by.size() * sizeof(Access), cudaMemcpyHostToDevice);
+    }
+    P.fast = ok;
   }
   const size_t na = P.h.arrays.size();
   P.stage.assign(na, nullptr); P.stage_elems.assign(na, 0); P.reg.assign(na, nullptr); P.cur.assign(na, nullptr);
@@ -553,9 +577,11 @@ void run_step_kernels(const StepArgs& A) {
   const bool fused_gather = A.use_gather && s.fuse;
   if (s.precision != PREC_F32) {
     TcLaunch L{};
-    if (A.use_gather) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; } else L.X = s.din;
+    if (A.use_gather) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; L.fast_in = s.G.fast;
+                        std::memcpy(L.cin, s.G.cls, sizeof L.cin); } else L.X = s.din;
     if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS;
-                          L.slot_head = s.S.slot_head; L.store_next = s.S.store_next; }
+                          L.slot_head = s.S.slot_head; L.store_next = s.S.store_next; L.fast_out = s.S.fast;
+                          L.store_by_slot = s.S.store_by_slot; std::memcpy(L.cout, s.S.cls, sizeof L.cout); }
     L.Y = A.fuse_scatter ? nullptr : s.dout;
     L.g = g;
     ensure_aux(tc_grid(rows));

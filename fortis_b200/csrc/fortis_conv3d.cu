@@ -1,9 +1,247 @@
-// placeholder until the conv3d kernels land
+// conv3d (cross-correlation, stride 1, zero padding) as an implicit GEMM on the CUDA cores, fp32, with bias,
+// residual add and activation fused into the epilogue; plus the network driver for stacks of such layers.
+//
+// Replaces the reference's cuDNN lowering fortis_conv3d (runtime/fortis_rt.c:128-156: descriptors rebuilt every
+// call, heuristic algorithm, workspace from the pool, bias / activation / residual as further kernels:
+// compiler/FortisFuse.cpp:626-655, 687-760) and its library-free direct kernels (runtime/fortis_fft.cu:91-201).
+//
+// GEMM view: rows = output voxels (n, d, h, w), columns = output channels, reduction = taps x input channels.
+// A block owns 64 voxels x 64 channels; per (tap, 16 input channels) slice the activations (gathered with the
+// padding applied) and the weights are staged in shared memory; each of the 256 threads accumulates 4 x 4 outputs.
+// Element strides of x and y are parameters, so the same kernel serves NDHWC networks and the NCDHW single-layer
+// entry of the memref ABI.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <string>
+#include <vector>
+
 #include "fortis_kernels.h"
 #include "fortis_model.h"
+
 namespace fortis {
-ConvModel* conv_model_create(const ModelHost&, int, cudaStream_t, std::string* err) { if (err) *err = "conv3d kernel not built"; return nullptr; }
-void conv_model_destroy(ConvModel*) {}
-bool conv_forward(ConvModel*, const float*, float*, int, int, int, int, cudaStream_t, std::string* err) { if (err) *err = "conv3d kernel not built"; return false; }
-bool conv3d_ncdhw(const float*, const float*, float*, int, int, int, int, int, int, int, int, cudaStream_t, std::string* err) { if (err) *err = "conv3d kernel not built"; return false; }
+
+namespace {
+
+struct ConvGeom {
+  int N, D, H, W, C, F, K, pad;
+  int Do, Ho, Wo;
+  long long xs_n, xs_d, xs_h, xs_w, xs_c;     // element strides of x
+  long long ys_n, ys_d, ys_h, ys_w, ys_c;     // element strides of y (and of the residual)
+};
+
+constexpr int CBM = 64, CBN = 64, CBK = 16;
+
+__global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict__ x, const float* __restrict__ wt,   // wt [tap][C][F]
+                                                         const float* __restrict__ bias, const float* __restrict__ residual,
+                                                         float* __restrict__ y, ConvGeom g, int act, float slope) {
+  __shared__ float As[CBK][CBM + 4];
+  __shared__ float Ws[CBK][CBN + 4];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const long long nvox = (long long)g.N * g.Do * g.Ho * g.Wo;
+  const long long m0 = (long long)blockIdx.x * CBM;
+  const int f0 = blockIdx.y * CBN;
+  // the voxel this thread loads for the A tile (one voxel, 4 input channels per slice)
+  const int lv = tid & 63, lc = (tid >> 6) * 4;
+  const long long vox = m0 + lv;
+  int on = 0, od = 0, oh = 0, ow = 0;
+  const bool vlive = vox < nvox;
+  if (vlive) {
+    long long t = vox;
+    ow = (int)(t % g.Wo); t /= g.Wo;
+    oh = (int)(t % g.Ho); t /= g.Ho;
+    od = (int)(t % g.Do); on = (int)(t / g.Do);
+  }
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  const int ntaps = g.K * g.K * g.K;
+  for (int tap = 0; tap < ntaps; tap++) {
+    const int kd = tap / (g.K * g.K), kh = (tap / g.K) % g.K, kw = tap % g.K;
+    const int id = od + kd - g.pad, ih = oh + kh - g.pad, iw = ow + kw - g.pad;
+    const bool inb = vlive && id >= 0 && id < g.D && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+    const float* xp = x + (long long)on * g.xs_n + (long long)id * g.xs_d + (long long)ih * g.xs_h + (long long)iw * g.xs_w;
+    for (int c0 = 0; c0 < g.C; c0 += CBK) {
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int c = c0 + lc + e;
+        As[lc + e][lv] = (inb && c < g.C) ? __ldg(xp + (long long)c * g.xs_c) : 0.f;
+      }
+      {
+        const int wr = tid >> 4, wc = (tid & 15) * 4;       // 16 cin rows x 64 couts, 4 couts per thread
+        const int c = c0 + wr;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const int f = f0 + wc + e;
+          Ws[wr][wc + e] = (c < g.C && f < g.F) ? __ldg(wt + ((long long)tap * g.C + c) * g.F + f) : 0.f;
+        }
+      }
+      __syncthreads();
+#pragma unroll
+      for (int k = 0; k < CBK; k++) {
+        const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+        const float4 w = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+        const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const long long v = m0 + ty * 4 + i;
+    if (v >= nvox) continue;
+    long long t = v;
+    const int w_ = (int)(t % g.Wo); t /= g.Wo;
+    const int h_ = (int)(t % g.Ho); t /= g.Ho;
+    const int d_ = (int)(t % g.Do); const int n_ = (int)(t / g.Do);
+    const long long yo = (long long)n_ * g.ys_n + (long long)d_ * g.ys_d + (long long)h_ * g.ys_h + (long long)w_ * g.ys_w;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int f = f0 + tx * 4 + j;
+      if (f >= g.F) continue;
+      float o = acc[i][j] + (bias ? bias[f] : 0.f);
+      if (residual) o += residual[yo + (long long)f * g.ys_c];
+      if (act == ACT_RELU) o = fmaxf(o, 0.f);
+      else if (act == ACT_LEAKY) o = o > 0.f ? o : o * slope;
+      y[yo + (long long)f * g.ys_c] = o;
+    }
+  }
 }
+
+void launch_conv(const float* x, const float* wt, const float* bias, const float* residual, float* y, const ConvGeom& g, int act,
+                 float slope, cudaStream_t s) {
+  const long long nvox = (long long)g.N * g.Do * g.Ho * g.Wo;
+  if (nvox <= 0) return;
+  dim3 grid((unsigned)((nvox + CBM - 1) / CBM), (unsigned)((g.F + CBN - 1) / CBN));
+  conv3d_f32_kernel<<<grid, 256, 0, s>>>(x, wt, bias, residual, y, g, act, slope);
+}
+
+// torch layout (F, C, K, K, K) -> [tap][C][F]
+std::vector<float> repack_weights(const float* w, int F, int C, int K) {
+  const int taps = K * K * K;
+  std::vector<float> out((size_t)taps * C * F);
+  for (int f = 0; f < F; f++)
+    for (int c = 0; c < C; c++)
+      for (int t = 0; t < taps; t++) out[((size_t)t * C + c) * F + f] = w[((size_t)f * C + c) * taps + t];
+  return out;
+}
+
+}  // namespace
+
+struct ConvModel {
+  std::vector<LayerHost> meta;          // shapes and flags (weights dropped after upload)
+  std::vector<float*> wt, bias;
+  float *buf[3] = {nullptr, nullptr, nullptr};
+  long long buf_elems = 0;
+};
+
+void conv_model_destroy(ConvModel* m) {
+  if (!m) return;
+  for (float* p : m->wt) cudaFree(p);
+  for (float* p : m->bias) cudaFree(p);
+  for (float* p : m->buf) cudaFree(p);
+  delete m;
+}
+
+ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
+  (void)s;
+  if (precision != PREC_F32) { if (err) *err = "conv3d networks run in fp32 only"; return nullptr; }
+  ConvModel* m = new ConvModel();
+  for (auto& L : M.layers) {
+    LayerHost meta = L;
+    meta.W.clear(); meta.b.clear();
+    m->meta.push_back(meta);
+    std::vector<float> wt = repack_weights(L.W.data(), L.cout, L.cin, L.ksize);
+    float *dw = nullptr, *db = nullptr;
+    if (cudaMalloc(&dw, wt.size() * 4) != cudaSuccess || cudaMalloc(&db, L.b.size() * 4) != cudaSuccess) {
+      if (err) *err = "out of device memory for conv weights";
+      conv_model_destroy(m);
+      return nullptr;
+    }
+    cudaMemcpy(dw, wt.data(), wt.size() * 4, cudaMemcpyHostToDevice);
+    cudaMemcpy(db, L.b.data(), L.b.size() * 4, cudaMemcpyHostToDevice);
+    m->wt.push_back(dw); m->bias.push_back(db);
+  }
+  return m;
+}
+
+// x (N, D, H, W, Cin) -> y (N, D, H, W, Cout); every layer keeps the spatial extent (pad = K / 2)
+bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err) {
+  const long long nvox = (long long)N * D * H * W;
+  if (nvox <= 0) { if (err) *err = "conv3d model: set the input extent (option conv_shape = N,D,H,W)"; return false; }
+  int cmax = 1;
+  for (auto& L : m->meta) {
+    if (L.pad * 2 + 1 != L.ksize) { if (err) *err = "conv3d model layers must keep the spatial extent (pad = K / 2)"; return false; }
+    cmax = L.cout > cmax ? L.cout : cmax;
+  }
+  if (m->buf_elems < nvox * cmax) {
+    for (float*& p : m->buf) { cudaFree(p); p = nullptr; }
+    for (float*& p : m->buf)
+      if (cudaMalloc(&p, (size_t)nvox * cmax * 4) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
+    m->buf_elems = nvox * cmax;
+  }
+  const float* src = x;
+  const float* skip = nullptr;
+  int skip_buf = -1;
+  const int nl = (int)m->meta.size();
+  for (int l = 0; l < nl; l++) {
+    const LayerHost& L = m->meta[l];
+    float* dst = y;
+    int dst_buf = -1;
+    if (l != nl - 1) {
+      for (int b = 0; b < 3; b++)
+        if (m->buf[b] != src && b != skip_buf) { dst = m->buf[b]; dst_buf = b; break; }
+    }
+    ConvGeom g;
+    g.N = N; g.D = D; g.H = H; g.W = W; g.C = L.cin; g.F = L.cout; g.K = L.ksize; g.pad = L.pad;
+    g.Do = D; g.Ho = H; g.Wo = W;
+    g.xs_c = 1; g.xs_w = L.cin; g.xs_h = (long long)W * L.cin; g.xs_d = (long long)H * W * L.cin; g.xs_n = (long long)D * H * W * L.cin;
+    g.ys_c = 1; g.ys_w = L.cout; g.ys_h = (long long)W * L.cout; g.ys_d = (long long)H * W * L.cout; g.ys_n = (long long)D * H * W * L.cout;
+    const float* res = (L.flags & LFLAG_ADD_SKIP) ? skip : nullptr;
+    if ((L.flags & LFLAG_ADD_SKIP) && !skip) { if (err) *err = "conv3d model: a layer adds a skip that was never saved"; return false; }
+    launch_conv(src, m->wt[l], m->bias[l], res, dst, g, L.act, L.slope, s);
+    if (L.flags & LFLAG_SAVE_SKIP) { skip = dst; skip_buf = dst_buf; }
+    src = dst;
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { if (err) *err = std::string("conv3d launch: ") + cudaGetErrorString(e); return false; }
+  return true;
+}
+
+// single layer, NCDHW fp32, weights in the torch layout on the device (memref ABI of runtime/fortis_rt.c:128-131)
+bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, int K, int pad,
+                  cudaStream_t s, std::string* err) {
+  // weights are constants of the caller: repack each distinct (pointer, shape) once, as the reference caches its
+  // transposed GEMM weights (runtime/fortis_rt.c:55-66)
+  struct Cached { const float* w; int F, C, K; float* wt; };
+  static std::vector<Cached> cache;
+  float* wt = nullptr;
+  for (auto& c : cache) if (c.w == w && c.F == F && c.C == C && c.K == K) wt = c.wt;
+  if (!wt) {
+    const size_t n = (size_t)F * C * K * K * K;
+    std::vector<float> hw(n);
+    cudaStreamSynchronize(s);
+    if (cudaMemcpy(hw.data(), w, n * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { if (err) *err = "cannot read the conv weights"; return false; }
+    std::vector<float> r = repack_weights(hw.data(), F, C, K);
+    if (cudaMalloc(&wt, n * 4) != cudaSuccess) { if (err) *err = "out of device memory for conv weights"; return false; }
+    cudaMemcpy(wt, r.data(), n * 4, cudaMemcpyHostToDevice);
+    if (cache.size() < 64) cache.push_back({w, F, C, K, wt});
+  }
+  ConvGeom g;
+  g.N = N; g.D = D; g.H = H; g.W = W; g.C = C; g.F = F; g.K = K; g.pad = pad;
+  g.Do = D + 2 * pad - K + 1; g.Ho = H + 2 * pad - K + 1; g.Wo = W + 2 * pad - K + 1;
+  g.xs_w = 1; g.xs_h = W; g.xs_d = (long long)H * W; g.xs_c = (long long)D * H * W; g.xs_n = (long long)C * D * H * W;
+  g.ys_w = 1; g.ys_h = g.Wo; g.ys_d = (long long)g.Ho * g.Wo; g.ys_c = (long long)g.Do * g.Ho * g.Wo; g.ys_n = (long long)F * g.Do * g.Ho * g.Wo;
+  launch_conv(x, wt, nullptr, nullptr, y, g, ACT_NONE, 0.f, s);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { if (err) *err = std::string("conv3d launch: ") + cudaGetErrorString(e); return false; }
+  return true;
+}
+
+}  // namespace fortis

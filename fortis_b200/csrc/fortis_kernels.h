@@ -62,6 +62,10 @@ struct TcLaunch {
   const IoPlanDev* GP; const Access* slots;          // gather plan, or null with X set
   const IoPlanDev* SP; const StoreTarget* stores;    // scatter plan, or null with Y set
   const int* slot_head; const int* store_next;       // per model output: first store (-1: none) and the chain
+  // fast I/O (all accesses fp32, no lifted expressions, at most two stride classes): see fortis_mlp_tc.cu
+  int fast_in, fast_out;
+  long long cin[2][3], cout[2][3];                   // (si, sj, sk) per class
+  const Access* store_by_slot;                       // [n_out], array < 0 where an output is not stored
   ArrayTable TG, TS;
   RowGeom g;
   const float* X;                                    // (rows, n_in) when there is no gather plan

@@ -29,6 +29,8 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -54,22 +56,27 @@ constexpr int kThreads = kEpiThreads + 64;  // + TMA warp + MMA warp
 constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
 constexpr int kBarBytes = 256;
-constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + 1024;   // + slack for 1024-byte alignment
+constexpr int kFastIn = 256, kFastOut = 128;          // widest model input / output the fast I/O tables hold
+constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5; // uint32 offset + uint8 code per slot / store
+constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + kTabBytes;   // the base must be 1024-byte aligned
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol0 = 384;
 constexpr uint32_t kWaitLimit = 1u << 24;   // polls of try_wait before giving up (each poll may block briefly)
 
 // status codes (which wait gave up)
-enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5 };
+enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6 };
 
 struct TcLayer {
   int K, N;                // padded: K multiple of 128, N multiple of 64 (hidden: multiple of 128)
   int n_real;              // unpadded output width
   int act;
-  float slope;
+  float slope;             // branch-free activation: act(v) = max(v, v * slope); none -> 1, ReLU -> 0, LeakyReLU -> slope
   const float* bias;       // [N] padded with zeros
   const float* scale;      // [N] per-output-channel dequantisation scale (fp8 weights) or null
 };
+
+// Stride class of a fast gather / scatter: element offset of a row = ci*si + cj*sj + kk*sk
+struct StrideClass { long long si, sj, sk; };
 
 struct TcParams {
   CUtensorMap maps[kMaxLayers];
@@ -90,6 +97,12 @@ struct TcParams {
   long long nrows;
   double* partials;
   int* status;
+  long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
+  // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
+  // (array, class, constant offset) triples are unpacked into shared memory once per CTA
+  int fast_in, fast_out;
+  StrideClass cin[2], cout[2];
+  const Access* store_by_slot;           // [n_out] store target per model output (array < 0: none), fast_out only
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -104,7 +117,9 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -116,37 +131,53 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // bounded wait: returns false (and raises the abort flag, records `code`) when the limit is reached
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (*abort_flag) return false;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   for (uint32_t i = 0; i < kWaitLimit; i++) {
+    if (*abort_flag) return false;
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(status, 0, code);
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;          // the common case costs one instruction
+  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// The MMA and TMA warps run their loops with all 32 lanes (warp-uniform control flow) and let ONE elected lane issue
+// each asynchronous instruction.  Issuing from a divergent `if (lane == 0)` region instead costs ~100 cycles per
+// tcgen05.mma (operands have to be moved into uniform registers one by one), 3x the 32 cycles a 128x64x16 MMA takes.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
 }
 
 // D[tmem] (+)= A[tmem] . B[smem]^T, bf16 x bf16 -> fp32, M = 128, N = 64, K = 16
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+template <uint32_t IDESC>
+__device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc) {       // D += A.B
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC) : "memory");
+}
+template <uint32_t IDESC>
+__device__ __forceinline__ void tc_mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\telect.sync _|p, 0xffffffff;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+      "@p tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, q;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC), "r"(accumulate) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -190,20 +221,28 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t saddr) {
 // instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kChunkN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
 
-__device__ __forceinline__ float act_f(float v, int act, float slope) {
-  if (act == ACT_RELU) return fmaxf(v, 0.f);
-  if (act == ACT_LEAKY) return v > 0.f ? v : v * slope;
-  return v;
+__device__ __forceinline__ float act_f(float v, float slope) { return fmaxf(v, v * slope); }
+
+// cycle accounting for diagnostics: adds the time since *t to prof[slot] (CTA 0, one lane) and restarts the clock
+__device__ __forceinline__ void prof_add(long long* prof, int slot, long long* t, bool who) {
+#ifdef FORTIS_TC_PROFILE
+  if (prof && who) { const long long n = clock64(); atomicAdd((unsigned long long*)&prof[slot], (unsigned long long)(n - *t)); *t = n; }
+#else
+  (void)prof; (void)slot; (void)t; (void)who;
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------------------
+template <bool HAS_SCALE>
 __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t park = base;                                   // 8 x 16 KB parked chunks
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_u32(smem);                         // parked chunks: 8 x 16 KB at offset 0
+  if (base & 1023u) {                                           // the swizzled weight stages need 1024-byte alignment
+    if (threadIdx.x == 0) atomicCAS(P.status, 0, ST_SMEM_ALIGN);
+    return;
+  }
   const uint32_t ring = base + kParkBytes;                      // kStages x 16 KB
   const uint32_t bars = ring + kRingBytes;
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;            // [kStages] each
@@ -213,6 +252,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   // tmem base 144, abort flag 148, checksum scratch [160,224)
   uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 144);
   volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 148);
+  uint32_t* s_off = (uint32_t*)(smem + kParkBytes + kRingBytes + kBarBytes);          // [kFastIn] input slot offsets
+  uint32_t* o_off = s_off + kFastIn;                                                  // [kFastOut] store offsets
+  uint8_t* s_code = (uint8_t*)(o_off + kFastOut);                                     // array | class << 7, 0xFF: none
+  uint8_t* o_code = s_code + kFastIn;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long ntiles = (P.nrows + kTileM - 1) / kTileM;
@@ -224,6 +267,28 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (P.fast_in)
+    for (int q = threadIdx.x; q < kFastIn; q += kThreads) {
+      uint8_t code = 0xFF; uint32_t off = 0;
+      if (q < P.n_in) {
+        const Access a = P.slots[q];
+        code = (uint8_t)(a.array | ((a.si == P.cin[0].si && a.sj == P.cin[0].sj && a.sk == P.cin[0].sk) ? 0 : 0x80));
+        off = (uint32_t)a.off0;
+      }
+      s_code[q] = code; s_off[q] = off;
+    }
+  if (P.fast_out)
+    for (int n = threadIdx.x; n < kFastOut; n += kThreads) {
+      uint8_t code = 0xFF; uint32_t off = 0;
+      if (n < P.n_out && P.store_by_slot[n].array >= 0) {
+        const Access a = P.store_by_slot[n];
+        code = (uint8_t)(a.array | ((a.si == P.cout[0].si && a.sj == P.cout[0].sj && a.sk == P.cout[0].sk) ? 0 : 0x80));
+        off = (uint32_t)a.off0;
+      }
+      o_code[n] = code; o_off[n] = off;
+    }
+  if (warp == 8 && lane < P.nlayers)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&P.maps[lane])) : "memory");
   if (warp == 9) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -234,56 +299,68 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
-        for (int l = 0; l < P.nlayers; l++) {
-          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
-          for (int c = 0; c < nchunks; c++)
-            for (int kb = 0; kb < nkb; kb++, it++) {
-              const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-              mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY);
-              if (*abort_flag) break;
-              mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-              const uint32_t dst = ring + s * kStageBytes;
-              tma_load_2d(dst, &P.maps[l], kb * kStageK, c * kChunkN, bar_full + 8 * s);
-              tma_load_2d(dst + kStageBytes / 2, &P.maps[l], kb * kStageK + 64, c * kChunkN, bar_full + 8 * s);
-            }
-        }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0, acc_it = 0, a_it = 0;
-      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
-        for (int l = 0; l < P.nlayers; l++, a_it++) {
-          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
-          mbar_wait(bar_a_ready, a_it & 1, abort_flag, P.status, ST_A_READY);      // A of this layer is in TMEM
-          tc_fence_after();
-          for (int c = 0; c < nchunks; c++, acc_it++) {
-            const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-            mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
-            tc_fence_after();
-            const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
-            for (int kb = 0; kb < nkb; kb++, it++) {
-              const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-              mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
-              tc_fence_after();
-              if (!*abort_flag) {
-                const uint32_t sb = ring + s * kStageBytes;
-#pragma unroll
-                for (int j = 0; j < kStageK / 16; j++) {
-                  const uint64_t bd = make_b_desc(sb + (j >> 2) * (kStageBytes / 2) + (j & 3) * 32);
-                  tc_mma_ts(d_tmem, tmem + kb * (kStageK / 2) + j * 8, bd, kIdesc, (kb | j) ? 1u : 0u);
-                }
-              }
-              tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
-            }
-            tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
+    // ------------------------------------------------------------------ TMA producer (whole warp, one lane issues)
+    uint32_t s = 0, ph = 0;
+    const bool pw = blockIdx.x == 0 && lane == 0;
+    long long pt = clock64();
+    bool stop = false;
+    for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
+      for (int l = 0; l < P.nlayers && !stop; l++) {
+        const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+        const CUtensorMap* map = &P.maps[l];
+        for (int c = 0; c < nchunks && !stop; c++)
+          for (int kb = 0; kb < nkb; kb++) {
+            prof_add(P.prof, 17, &pt, pw);
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
+            prof_add(P.prof, 16, &pt, pw);
+            mbar_expect_tx(bar_full + 8 * s, kStageBytes);
+            const uint32_t dst = ring + s * kStageBytes;
+            tma_load_2d(dst, map, kb * kStageK, c * kChunkN, bar_full + 8 * s);
+            tma_load_2d(dst + kStageBytes / 2, map, kb * kStageK + 64, c * kChunkN, bar_full + 8 * s);
+            if (++s == kStages) { s = 0; ph ^= 1; }
           }
+      }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
+    uint32_t s = 0, ph = 0, acc_it = 0, a_it = 0;
+    const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
+    const bool pw = blockIdx.x == 0 && lane == 0;
+    long long pt = clock64();
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+      for (int l = 0; l < P.nlayers; l++, a_it++) {
+        const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+        prof_add(P.prof, 0, &pt, pw);
+        mbar_wait(bar_a_ready, a_it & 1, abort_flag, P.status, ST_A_READY);      // A of this layer is in TMEM
+        prof_add(P.prof, 1, &pt, pw);
+        tc_fence_after();
+        for (int c = 0; c < nchunks; c++, acc_it++) {
+          const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+          prof_add(P.prof, 0, &pt, pw);
+          mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
+          prof_add(P.prof, 2, &pt, pw);
+          tc_fence_after();
+          const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
+          for (int kb = 0; kb < nkb; kb++) {
+            prof_add(P.prof, 0, &pt, pw);
+            mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+            prof_add(P.prof, 3, &pt, pw);
+            tc_fence_after();
+            // descriptors of the stage's two 64-wide k sub-tiles; stepping k by 16 inside a 128-byte swizzle row
+            // adds 32 bytes = 2 to the (address >> 4) field
+            const uint32_t sb = ring + s * kStageBytes;
+            const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
+            const uint64_t bd1 = desc_hi | (uint64_t)(((sb + kStageBytes / 2) >> 4) & 0x3FFF);
+            const uint32_t a0 = tmem + kb * (kStageK / 2);
+            tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)kb);
+#pragma unroll
+            for (int j = 1; j < kStageK / 16; j++)
+              tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, (j < 4 ? bd0 : bd1) + (uint64_t)((j & 3) * 2));
+            tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
+            if (++s == kStages) { s = 0; ph ^= 1; }
+          }
+          tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
         }
-    }
+      }
   } else {
     // ------------------------------------------------------------------ row warps: gather, epilogues, scatter
     const int quad = warp & 3, half = warp >> 2;              // TMEM lane quadrant, which 32 of a chunk's 64 features
@@ -291,6 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
     uint32_t acc_it = 0;
     double csum = 0.0;
+    const bool pw = blockIdx.x == 0 && threadIdx.x == 0;
+    long long pt = clock64();
     uint32_t kept[(kMaxChunks - kSmemChunks) * 16];           // parked chunks 8..11 of this thread (bf16 pairs)
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const long long row = tile * kTileM + r;
@@ -300,57 +379,100 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       // ---- layer 0 input: this thread's half of the row, 32 features (16 packed columns) at a time
       {
         const int K0 = P.layer[0].K, per = K0 / 2;            // features per half
-        double sc[kMaxScalars];
-        if (live && P.GP && P.GP->nscalars) load_scalars(*P.GP, P.TG, ci, cj, kk, sc);
-        for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
-          uint32_t pk[16];
+        if (P.fast_in) {
+          // one position per stride class, then 32 independent loads per step: base[array] + offset + position
+          const long long pos0 = ci * P.cin[0].si + cj * P.cin[0].sj + kk * P.cin[0].sk;
+          const long long pos1 = ci * P.cin[1].si + cj * P.cin[1].sj + kk * P.cin[1].sk;
+          for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
+            float v[32];
 #pragma unroll
-          for (int j = 0; j < 16; j++) {
-            float v[2];
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-              const int q = q0 + 2 * j + e;
-              float x = 0.f;
-              if (live && q < P.n_in) {
-                x = P.GP ? gather_value(*P.GP, P.slots[q], P.TG, q, ci, cj, kk, sc) : __ldg(P.X + row * P.n_in + q);
-                if (P.in_div) x = __fdiv_rn(x, __ldg(P.in_div + q));
-              }
-              v[e] = x;
+            for (int j = 0; j < 32; j++) {
+              const uint32_t code = s_code[q0 + j];
+              v[j] = 0.f;
+              if (live && code != 0xFF)
+                v[j] = __ldg((const float*)P.TG.base[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? pos1 : pos0)));
             }
-            pk[j] = pack_bf16(v[0], v[1]);
+            if (P.in_div) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+            }
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+            tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
           }
-          tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
+        } else {
+          double sc[kMaxScalars];
+          if (live && P.GP && P.GP->nscalars) load_scalars(*P.GP, P.TG, ci, cj, kk, sc);
+          for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+              float v[2];
+#pragma unroll
+              for (int e = 0; e < 2; e++) {
+                const int q = q0 + 2 * j + e;
+                float x = 0.f;
+                if (live && q < P.n_in) {
+                  x = P.GP ? gather_value(*P.GP, P.slots[q], P.TG, q, ci, cj, kk, sc) : __ldg(P.X + row * P.n_in + q);
+                  if (P.in_div) x = __fdiv_rn(x, __ldg(P.in_div + q));
+                }
+                v[e] = x;
+              }
+              pk[j] = pack_bf16(v[0], v[1]);
+            }
+            tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
+          }
         }
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(bar_a_ready);
+        prof_add(P.prof, 9, &pt, pw);
       }
       for (int l = 0; l < P.nlayers; l++) {
         const TcLayer& L = P.layer[l];
         const int nchunks = L.N / kChunkN;
         const bool last = l == P.nlayers - 1;
+        const float slope = L.slope;
         if (!last) {
 #pragma unroll
           for (int c = 0; c < kMaxChunks; c++) {
             if (c < nchunks) {
               const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
               acc_it++;
+              const int n0 = c * kChunkN + half * 32;
+              // the 32 biases of this thread's features: warp-uniform 16-byte loads issued before the wait
+              float4 bq[8];
+#pragma unroll
+              for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
+              prof_add(P.prof, 11, &pt, pw);
               mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+              prof_add(P.prof, 10, &pt, pw);
               tc_fence_after();
               uint32_t a[32];
               tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
               tmem_ld_wait();
               tc_fence_before();
               mbar_arrive(bar_acc_empty + 8 * b);             // the MMA warp may refill this accumulator
-              const int n0 = c * kChunkN + half * 32;
+              if (HAS_SCALE) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                  const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+                  a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
+                  a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
+                  a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
+                  a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
+                }
+              }
               uint32_t pk[16];
 #pragma unroll
-              for (int j = 0; j < 16; j++) {
-                float v0 = __uint_as_float(a[2 * j]), v1 = __uint_as_float(a[2 * j + 1]);
-                if (L.scale) { v0 *= __ldg(L.scale + n0 + 2 * j); v1 *= __ldg(L.scale + n0 + 2 * j + 1); }
-                v0 = act_f(v0 + __ldg(L.bias + n0 + 2 * j), L.act, L.slope);
-                v1 = act_f(v1 + __ldg(L.bias + n0 + 2 * j + 1), L.act, L.slope);
-                pk[j] = pack_bf16(v0, v1);
+              for (int j = 0; j < 8; j++) {
+                const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
+                const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
+                const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
+                const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
+                pk[2 * j] = pack_bf16(v0, v1);
+                pk[2 * j + 1] = pack_bf16(v2, v3);
               }
               if (c < kSmemChunks) {
                 // [chunk][half][16-byte piece][row]: lanes are rows, so every store is conflict-free
@@ -366,6 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           }
           // every MMA of this layer has retired (its last accumulator was complete), so A may be overwritten:
           // move the parked chunks into the A columns and release the next layer
+          prof_add(P.prof, 11, &pt, pw);
 #pragma unroll
           for (int c = 0; c < kMaxChunks; c++) {
             if (c < nchunks) {
@@ -387,44 +510,82 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           tmem_st_wait();
           tc_fence_before();
           mbar_arrive(bar_a_ready);
+          prof_add(P.prof, 12, &pt, pw);
         } else {
           // ---- last layer: bias, output scaling / masks, then straight into the host arrays
           double sc[kMaxScalars];
-          if (live && P.SP && P.SP->nscalars) load_scalars(*P.SP, P.TS, ci, cj, kk, sc);
+          if (live && P.SP && !P.fast_out && P.SP->nscalars) load_scalars(*P.SP, P.TS, ci, cj, kk, sc);
+          const long long opos0 = ci * P.cout[0].si + cj * P.cout[0].sj + kk * P.cout[0].sk;
+          const long long opos1 = ci * P.cout[1].si + cj * P.cout[1].sj + kk * P.cout[1].sk;
           for (int c = 0; c < nchunks; c++) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
+            const int n0 = c * kChunkN + half * 32;
+            float4 bq[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
+            prof_add(P.prof, 13, &pt, pw);
             mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            prof_add(P.prof, 14, &pt, pw);
             tc_fence_after();
             uint32_t a[32];
             tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
             tmem_ld_wait();
             tc_fence_before();
             mbar_arrive(bar_acc_empty + 8 * b);
-            const int n0 = c * kChunkN + half * 32;
-            if (live) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
+              if (HAS_SCALE) sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+              v[4 * j] = act_f(__uint_as_float(a[4 * j]) * sq.x + bq[j].x, slope);
+              v[4 * j + 1] = act_f(__uint_as_float(a[4 * j + 1]) * sq.y + bq[j].y, slope);
+              v[4 * j + 2] = act_f(__uint_as_float(a[4 * j + 2]) * sq.z + bq[j].z, slope);
+              v[4 * j + 3] = act_f(__uint_as_float(a[4 * j + 3]) * sq.w + bq[j].w, slope);
+            }
+            if (P.out_mul || P.relu_mask) {
 #pragma unroll
               for (int j = 0; j < 32; j++) {
                 const int n = n0 + j;
                 if (n < P.n_out) {
-                  float v = __uint_as_float(a[j]);
-                  if (L.scale) v *= __ldg(L.scale + n);
-                  v = act_f(v + __ldg(L.bias + n), L.act, L.slope);
-                  if (P.out_mul) v *= __ldg(P.out_mul + n);
-                  if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v = fmaxf(v, 0.f);
-                  if (P.Y) P.Y[row * P.n_out + n] = v;
-                  if (P.SP) {
-                    for (int s = __ldg(P.slot_head + n); s >= 0; s = __ldg(P.store_next + s)) {
-                      const StoreTarget st = P.stores[s];
-                      const double o = scatter_value(*P.SP, P.TS, n, v, sc);
-                      store_elem(P.TS, st.a, access_offset(st.a, ci, cj, kk), o);
-                      csum += st.a.elt == 0 ? (double)(float)o : o;
-                    }
+                  if (P.out_mul) v[j] *= __ldg(P.out_mul + n);
+                  if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v[j] = fmaxf(v[j], 0.f);
+                }
+              }
+            }
+            if (live) {
+              if (P.Y) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
+              }
+              if (P.SP && P.fast_out) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                  const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
+                  if (code != 0xFF) {
+                    ((float*)P.TS.base[code & 0x7F])[(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
+                    csum += (double)v[j];
+                  }
+                }
+              } else if (P.SP) {
+#pragma unroll 1
+                for (int j = 0; j < 32; j++) {
+                  const int n = n0 + j;
+                  if (n >= P.n_out) break;
+                  float vj = 0.f;
+#pragma unroll
+                  for (int t = 0; t < 32; t++) if (t == j) vj = v[t];
+                  for (int s2 = __ldg(P.slot_head + n); s2 >= 0; s2 = __ldg(P.store_next + s2)) {
+                    const StoreTarget st = P.stores[s2];
+                    const double o = scatter_value(*P.SP, P.TS, n, vj, sc);
+                    store_elem(P.TS, st.a, access_offset(st.a, ci, cj, kk), o);
+                    csum += st.a.elt == 0 ? (double)(float)o : o;
                   }
                 }
               }
             }
           }
+          prof_add(P.prof, 13, &pt, pw);
         }
       }
     }
@@ -507,9 +668,7 @@ struct TcModel {
   float *in_div = nullptr, *out_mul = nullptr, *relu_mask = nullptr;
   TcLayer layer[kMaxLayers];
   CUtensorMap maps[kMaxLayers];
-  int *slot_head = nullptr, *store_next = nullptr;     // built per scatter plan by the caller
-  const StoreTarget* built_for = nullptr;
-  int built_n = 0;
+  bool has_scale = false;
 };
 
 bool tc_model_supported(const ModelHost& M, std::string* why) {
@@ -519,6 +678,7 @@ bool tc_model_supported(const ModelHost& M, std::string* why) {
   for (size_t l = 0; l < M.layers.size(); l++) {
     const LayerHost& L = M.layers[l];
     if (round_up(L.cin, kStageK) > kMaxK) return no("a layer input is wider than 768");
+    if (L.act == ACT_LEAKY && !(L.slope >= 0.f && L.slope <= 1.f)) return no("LeakyReLU slope outside [0, 1]");
     const int npad = l + 1 < M.layers.size() ? round_up(L.cout, kStageK) : round_up(L.cout, kChunkN);
     if (npad > kMaxK) return no("a layer output is wider than 768");
   }
@@ -538,7 +698,7 @@ void tc_model_destroy(TcModel* m) {
   for (void* p : m->w) cudaFree(p);
   for (float* p : m->bias) cudaFree(p);
   for (float* p : m->scale) cudaFree(p);
-  cudaFree(m->in_div); cudaFree(m->out_mul); cudaFree(m->relu_mask); cudaFree(m->slot_head); cudaFree(m->store_next);
+  cudaFree(m->in_div); cudaFree(m->out_mul); cudaFree(m->relu_mask);
   delete m;
 }
 
@@ -583,7 +743,8 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     }
     m->scale.push_back(ds);
     TcLayer& T = m->layer[l];
-    T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.slope = L.slope; T.bias = db; T.scale = ds;
+    T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds;
+    T.slope = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;      // act(v) = max(v, v * slope)
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     const cuuint32_t box[2] = {64, (cuuint32_t)kChunkN};
@@ -600,8 +761,10 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     return d;
   };
   m->in_div = up(M.in_div); m->out_mul = up(M.out_mul); m->relu_mask = up(M.relu_mask);
-  if (cudaFuncSetAttribute(mlp_tc_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+  if (cudaFuncSetAttribute(mlp_tc_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
     return fail("cannot reserve " + std::to_string(kSmemBytes) + " bytes of shared memory for the tensor-core kernel");
+  m->has_scale = precision == PREC_FP8W;
   return m;
 }
 
@@ -617,10 +780,32 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   P.SP = L.SP; P.stores = L.stores; P.TS = L.TS; P.Y = L.Y;
   P.slot_head = L.slot_head; P.store_next = L.store_next;
   P.g = L.g; P.nrows = nrows; P.partials = L.partials; P.status = L.status;
+  P.fast_in = L.fast_in && m->n_in <= kFastIn; P.fast_out = L.fast_out && m->n_out <= kFastOut;
+  for (int i = 0; i < 2; i++) {
+    P.cin[i] = StrideClass{L.cin[i][0], L.cin[i][1], L.cin[i][2]};
+    P.cout[i] = StrideClass{L.cout[i][0], L.cout[i][1], L.cout[i][2]};
+  }
+  P.store_by_slot = L.store_by_slot;
   if (!P.GP && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (P.SP && (!P.slot_head || !P.store_next)) { if (err) *err = "tensor-core step: scatter index missing"; return false; }
   const int grid = tc_grid(nrows);
-  mlp_tc_fused_kernel<<<grid, kThreads, kSmemBytes, s>>>(P);
+  static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
+  static long long* dprof = nullptr;
+  if (want_prof) {
+    if (!dprof) cudaMalloc(&dprof, 32 * sizeof(long long));
+    cudaMemsetAsync(dprof, 0, 32 * sizeof(long long), s);
+    P.prof = dprof;
+  }
+  if (m->has_scale) mlp_tc_fused_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(P);
+  else mlp_tc_fused_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  if (want_prof) {
+    long long h[32];
+    cudaStreamSynchronize(s);
+    cudaMemcpy(h, dprof, sizeof h, cudaMemcpyDeviceToHost);
+    std::fprintf(stderr, "tc prof (cycles, CTA 0): mma issue %lld | wait a_ready %lld acc_empty %lld full %lld || rows: gather %lld | hidden wait %lld work %lld "
+                 "transfer %lld | last wait %lld work %lld || tma wait-empty %lld issue %lld\n",
+                 h[0], h[1], h[2], h[3], h[9], h[10], h[11], h[12], h[14], h[13], h[16], h[17]);
+  }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("tensor-core kernel launch: ") + cudaGetErrorString(e); return false; }
   return true;

@@ -1,0 +1,72 @@
+"""conv3d path (BASELINE config 4's layer types) against the oracle, through the C ABI."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+import fortis_b200
+from oracle import fortis_oracle as fo
+
+FP32_TOL = 1e-5
+
+
+@pytest.fixture()
+def host():
+    h = fortis_b200.Host()
+    h.reset()
+    yield h
+    h.reset()
+
+
+@pytest.mark.parametrize("shape", [(2, 9, 7, 5), (1, 33, 33, 33)])
+def test_superres_net_small(host, shape):
+    """Conv3d 3->W k3 p1 + LeakyReLU(0.2); residual blocks [conv, LeakyReLU, conv, +skip]; Conv3d W->3 (NDHWC)."""
+    N, D, H, W = shape
+    width, blocks = (16, 2) if shape[1] < 20 else (64, 1)
+    layers = fortis_b200.conv_layers(3, width, 3, nblocks=blocks, seed=6)
+    for L in layers:                       # non-zero biases so that the bias path is exercised
+        L["b"] = (np.random.default_rng(1).normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = np.random.default_rng(5).normal(size=(N, D, H, W, 3)).astype(np.float32)
+    want = fo.convnet_forward(layers, x)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("conv_shape", "%d,%d,%d,%d" % shape)
+    y = np.zeros((N, D, H, W, 3), np.float32)
+    host.forward(x, y)
+    assert fo.rel_l2(y, want) < FP32_TOL
+
+
+def test_conv_probe_stamp_through_memref_entry(host, golden_dir):
+    """The reference's conv probe (frontend/export_conv.py; README stamp 9617.28) through fortis_conv3d's memref ABI:
+    NCDHW fp32, the bias and LeakyReLU(0.1) applied afterwards as the compiled program does in its epilogue kernel."""
+    Z = np.load(os.path.join(golden_dir, "stamps.npz"))
+    x = torch.from_numpy(Z["conv_x"].reshape(1, 3, 16, 16, 16).copy()).cuda()
+    w = torch.from_numpy(Z["conv_W"].copy()).cuda()
+    y = torch.zeros((1, 8, 16, 16, 16), dtype=torch.float32, device="cuda")
+    L = host.L
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    for fn in (L.fortis_conv3d, L.fortis_conv3d_direct):
+        fn.argtypes = [vp, vp, cl] + [cl] * 10 + [vp, vp, cl] + [cl] * 10 + [vp, vp, cl] + [cl] * 10 + [cl] * 18
+        fn.restype = None
+        y.zero_()
+        fn(x.data_ptr(), x.data_ptr(), 0, 1, 3, 16, 16, 16, 3 * 4096, 4096, 256, 16, 1,
+           w.data_ptr(), w.data_ptr(), 0, 8, 3, 3, 3, 3, 81, 27, 9, 3, 1,
+           y.data_ptr(), y.data_ptr(), 0, 1, 8, 16, 16, 16, 8 * 4096, 4096, 256, 16, 1,
+           1, 3, 16, 16, 16, 8, 3, 3, 3, 16, 16, 16, 1, 1, 1, 1, 1, 1)
+        host.sync()
+        out = y.cpu().numpy() + Z["conv_b"].reshape(1, 8, 1, 1, 1)
+        out = np.where(out > 0, out, out * np.float32(0.1))
+        cs = float(out.astype(np.float64).sum())
+        assert abs(cs - 9617.28) / 9617.28 < 3e-5
+        assert np.allclose(out.ravel()[:4], Z["conv_y4"], rtol=1e-5, atol=1e-6)
+    # stride 2 is refused with a message and leaves y untouched (runtime/fortis_fft.cu:135)
+    y.fill_(-7.0)
+    L.fortis_conv3d_direct(x.data_ptr(), x.data_ptr(), 0, 1, 3, 16, 16, 16, 3 * 4096, 4096, 256, 16, 1,
+                           w.data_ptr(), w.data_ptr(), 0, 8, 3, 3, 3, 3, 81, 27, 9, 3, 1,
+                           y.data_ptr(), y.data_ptr(), 0, 1, 8, 16, 16, 16, 8 * 4096, 4096, 256, 16, 1,
+                           1, 3, 16, 16, 16, 8, 3, 3, 3, 16, 16, 16, 2, 2, 2, 1, 1, 1)
+    host.sync()
+    assert float(y.min()) == -7.0 and float(y.max()) == -7.0

@@ -129,6 +129,9 @@ def test_descriptor_cases_bit_exact(host, golden_dir, name, resident):
         assert a.tobytes(order="F") == b.tobytes(order="F")
 
 
+_REF_PINNED = []   # the reference's gsetup pins its arrays for the life of the process and never unpins them
+
+
 def test_reference_generated_kernels_agree(host, golden_dir):
     """Second checker: the reference's own generated ZB gather / scatter kernels (oracle/_ref), run on this GPU."""
     so = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libfortis_ref_zb.so")
@@ -146,6 +149,7 @@ def test_reference_generated_kernels_agree(host, golden_dir):
     Y = (np.random.default_rng(99).random((71040, 3)) - 0.5).astype(np.float32)
     assert ref.ref_upload_output(p(Y)) == 0
     sin = zb_scatter_arrays(gin)
+    _REF_PINNED.extend(gin + sin)          # keep the pinned addresses from being reused by later allocations
     ora = [a.copy(order="F") for a in sin]
     for k in range(1, 16):
         ref.fortis_scatter(ctypes.c_int(k), *[p(a) for a in sin])
