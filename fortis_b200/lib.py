@@ -39,6 +39,7 @@ def load():
         "fortis_unpack": (None, [vp, ci]), "fortis_model_input": (vp, []), "fortis_model_output": (vp, []),
         "fortis_begin": (None, [ci]), "mgpuStreamCreate": (vp, []), "fortis_alloc": (vp, [cl]), "fortis_free": (None, [vp]),
         "fortis_checksum": (ci, [vp, cl, ci, c.POINTER(c.c_double)]), "fortis_step_checksum": (ci, [c.POINTER(c.c_double)]),
+        "fortis_checksum_noalloc": (ci, [vp, cl, ci, vp, vp]),
         "fortis_device_status": (ci, []), "fortis_copy_to_host": (ci, [vp, vp, cl]), "fortis_copy_to_device": (ci, [vp, vp, cl]),
         "fortis_debug_eval_expr": (ci, [cc, ci, c.c_double, c.POINTER(c.c_double), c.POINTER(ci), ci, c.POINTER(c.c_double)]),
         "fortis_debug_plan": (ci, [cc, cc, cc, ci, cl, c.POINTER(ci), ci, c.POINTER(c.c_longlong), c.POINTER(ci),

@@ -139,6 +139,17 @@ int fortis_copy_to_device(void* dev, const void* src, long nbytes);
 
 /* fp64 sum of n elements (elt 0 = float, 1 = double) of a device or host array, summed in a fixed order */
 int fortis_checksum(const void* data, long n, int elt, double* out);
+/* No counterpart in the reference.  The same fp64 sum for callers that cannot allocate device memory: hosts that
+ * give their whole GPU memory budget to pools sized at start-up, and code between latency-critical launches, where
+ * cudaMalloc's device synchronisation would stall the step.  dev_data and dev_out are DEVICE pointers supplied by the
+ * caller, `stream` is the caller's cudaStream_t (0 = default stream); the result is written to *dev_out in stream
+ * order and nothing is synchronised.  The block partials live in a 32 KB array inside the library image, so n is
+ * limited to 2^28 elements (return -2 and a message beyond that) and the call performs no cudaMalloc / cudaFree and
+ * uses no pool.  The first call on each device resolves the array's device address (a set-up step: make that call
+ * before any stream capture).  All calls share the array: calls that can overlap on the GPU race on it.
+ * Returns 0, or a negative code with a message on stderr. */
+int fortis_checksum_noalloc(const void* dev_data, long n, int elt, double* dev_out, void* stream);
+
 /* fp64 sum of everything the fused steps scattered since the last call (needs option "checksum" = "1") */
 int fortis_step_checksum(double* out);
 /* device status word of the tensor-core kernel: 0, or the code of a bounded wait that gave up */
