@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FLOP_PER_COL = {"column": 2 * (244 * 768 + 3 * 768 * 768 + 768 * 128), "stencil": 2 * (27 * 20 + 20 * 20 + 20 * 3),
-                "toy": 2 * (64 * 256 + 256 * 256 + 256 * 64)}
+                "toy": 2 * (64 * 256 + 256 * 256 + 256 * 64), "conv": 2 * 27 * (3 * 64 + 12 * 64 * 64 + 64 * 3)}
 BYTES_PER_COL = {"column": 4 * (244 + 128), "stencil": 24, "toy": 4 * 128}
 
 
@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="fortis_b200", choices=["fortis_b200", "reference"])
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32", "fp8w"])
-    ap.add_argument("--workload", default="column", choices=["column", "column_c5", "stencil", "toy"])
+    ap.add_argument("--workload", default="column", choices=["column", "column_c5", "stencil", "toy", "conv"])
     ap.add_argument("--ncol", type=int, default=0, help="override the per-rank column count (column workloads)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -77,6 +77,14 @@ def make_workload(name, rank, ncol_override=0):
         layers = fortis_b200.mlp_layers([27, 20, 20, 3], seed=4, init="uniform", act="relu", bias="uniform")
         return dict(G=G, S=S, Lp=Lp, K=K, gin=gin, sout=sout, layers=layers, units=nx * ny * nz, kind="stencil",
                     label="ocean stencil MLP, 1440x1080x4 points, 27->20->20->3")
+    if name == "conv":
+        shape = (8, 33, 33, 33)
+        rng = np.random.default_rng(5 + rank)
+        x = rng.standard_normal(shape + (3,), dtype=np.float32)
+        y = np.zeros(shape + (3,), np.float32)
+        layers = fortis_b200.conv_layers(3, 64, 3, nblocks=6, seed=6)
+        return dict(G=None, S=None, Lp=None, K=None, gin=[x], sout=[y], layers=layers, units=int(np.prod(shape)), kind="conv",
+                    shape=shape, label="conv3d super-resolution net, 8 x 33^3 x 3 NDHWC, 3->64, 6 residual blocks, 64->3")
     ncol = 4096
     G, S, Lp, K = fo.identity_descriptors(64, 64, ncol)
     rng = np.random.default_rng(rank)
@@ -240,9 +248,13 @@ def main():
     prec = args.precision
     h = fortis_b200.Host()
     h.reset()
-    h.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"], kdist=wl["K"])
+    is_conv = wl["kind"] == "conv"
+    if not is_conv:
+        h.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"], kdist=wl["K"])
     h.load_model(fortis_b200.write_blob(wl["layers"]))
     h.option("precision", prec)
+    if is_conv:
+        h.option("conv_shape", "%d,%d,%d,%d" % wl["shape"])
     h.option("checksum", 1)
     h.option("async", 1)
     stream = torch.cuda.ExternalStream(h.stream())
@@ -279,12 +291,20 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    total_ms, per = timed(lambda: h.step(d_in, d_out), args.steps, max(3, args.warmup))
+    if is_conv:
+        h.L.mlp_upload(wl["gin"][0].ctypes.data)           # input resident in HBM; every step runs the whole network
+        step_fn = lambda: h.L.mlp_forward_dev()
+    else:
+        step_fn = lambda: h.step(d_in, d_out)
+    total_ms, per = timed(step_fn, args.steps, max(3, args.warmup))
     clocks = sampler.stop() if sampler else None
     status = h.L.fortis_device_status()
     if status != 0:
         raise SystemExit("device status %d: a bounded wait in the tensor-core kernel gave up" % status)
-    cs_local = h.step_checksum()
+    cs_local = h.step_checksum() if not is_conv else 0.0
+    if is_conv:
+        h.L.mlp_download(wl["sout"][0].ctypes.data)
+        cs_local = float(wl["sout"][0].astype(np.float64).sum())
     units = wl["units"] * world
     value = units * args.steps / (total_ms * 1e-3)
     kernel_ms = float(np.median(per))
@@ -294,7 +314,8 @@ def main():
         # host arrays: the library pins them once, then every step copies all inputs H2D and all outputs D2H
         h.option("async", 0)
         e_steps = max(3, min(args.steps, 20))
-        e_total, _ = timed(lambda: h.step(wl["gin"], wl["sout"]), e_steps, 3)
+        e_fn = (lambda: h.forward(wl["gin"][0], wl["sout"][0])) if is_conv else (lambda: h.step(wl["gin"], wl["sout"]))
+        e_total, _ = timed(e_fn, e_steps, 3)
         e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
                "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
     cs_global = cs_local
@@ -316,7 +337,7 @@ def main():
             roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": src}
         else:
             peak, src = (peaks.get("bf16_tflops"), "measured burst") if peaks.get("bf16_tflops") else (1590.0, "fallback")
-            ach = wl["units"] * FLOP_PER_COL["column" if kind == "column" else kind] / (kernel_ms * 1e-3) / 1e12
+            ach = wl["units"] * FLOP_PER_COL[kind] / (kernel_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": src}
         traffic = None
         try:
@@ -325,8 +346,8 @@ def main():
             pass
         roof["traffic"] = traffic
         roof["kernel_ms"] = kernel_ms
-        cpu = None if args.no_cpu else time_cpu(wl)
-        launches_per_step = 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
+        cpu = None if (args.no_cpu or is_conv) else time_cpu(wl)
+        launches_per_step = len(wl["layers"]) if is_conv else 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
         line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": {"bf16": "bf16", "fp32": "f32", "fp8w": "bf16 (fp8-e4m3 weights)"}[prec],

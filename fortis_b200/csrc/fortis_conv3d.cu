@@ -135,6 +135,7 @@ std::vector<float> repack_weights(const float* w, int F, int C, int K) {
 }  // namespace
 
 struct ConvModel {
+  ConvTcModel* tcm = nullptr;           // bf16 tensor-core network (precision bf16); the fields below serve fp32
   std::vector<LayerHost> meta;          // shapes and flags (weights dropped after upload)
   std::vector<float*> wt, bias;
   float *buf[3] = {nullptr, nullptr, nullptr};
@@ -143,6 +144,7 @@ struct ConvModel {
 
 void conv_model_destroy(ConvModel* m) {
   if (!m) return;
+  conv_tc_destroy(m->tcm);
   for (float* p : m->wt) cudaFree(p);
   for (float* p : m->bias) cudaFree(p);
   for (float* p : m->buf) cudaFree(p);
@@ -151,8 +153,14 @@ void conv_model_destroy(ConvModel* m) {
 
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
   (void)s;
-  if (precision != PREC_F32) { if (err) *err = "conv3d networks run in fp32 only"; return nullptr; }
+  if (precision == PREC_FP8W) { if (err) *err = "conv3d networks run in fp32 or bf16"; return nullptr; }
   ConvModel* m = new ConvModel();
+  if (precision == PREC_BF16) {
+    std::string why;
+    m->tcm = conv_tc_create(M, &why);
+    if (!m->tcm) { if (err) *err = "precision bf16 needs the tensor-core conv kernel, which cannot take this model: " + why; delete m; return nullptr; }
+    return m;
+  }
   for (auto& L : M.layers) {
     LayerHost meta = L;
     meta.W.clear(); meta.b.clear();
@@ -173,6 +181,7 @@ ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, 
 
 // x (N, D, H, W, Cin) -> y (N, D, H, W, Cout); every layer keeps the spatial extent (pad = K / 2)
 bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err) {
+  if (m->tcm) return conv_tc_forward(m->tcm, x, y, N, D, H, W, s, err);
   const long long nvox = (long long)N * D * H * W;
   if (nvox <= 0) { if (err) *err = "conv3d model: set the input extent (option conv_shape = N,D,H,W)"; return false; }
   int cmax = 1;

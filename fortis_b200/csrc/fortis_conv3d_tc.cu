@@ -1,0 +1,463 @@
+// conv3d 64 -> 64 channels, 3x3x3, stride 1, pad 1 as an implicit GEMM on tcgen05 tensor cores (bf16 operands, fp32
+// accumulation in tensor memory), with bias + residual add + LeakyReLU fused into the epilogue; plus the thin FFMA
+// kernels for the network's first (few channels in) and last (few channels out) layers and the bf16 network driver.
+//
+// Replaces fortis_conv3d -> cudnnConvolutionForward and the separate bias / activation / residual kernels the
+// reference chains behind it (runtime/fortis_rt.c:128-156, compiler/FortisFuse.cpp:626-655, 687-760).
+//
+// Layout: activations are bf16, channels-last, ZERO-PADDED in memory: [N][D+2][H+2][W+2][64], viewed as a matrix
+// [P rows][64 channels] (one 128-byte row per voxel).  With the border stored explicitly, the input rows a tap
+// (kd, kh, kw) needs for output rows p0..p0+127 are simply rows p0+shift..p0+shift+127 with
+// shift = (kd-1)(H+2)(W+2) + (kh-1)(W+2) + (kw-1): every tap is ONE plain 2-D TMA tile load, no im2col, no masks
+// (rows outside [0, P) are zero-filled by TMA).  Border rows of the output are computed and then written as zeros,
+// which keeps the padding intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work
+// at 33^3.
+//
+// Per 128-row tile: D[128 x 64] = sum over 27 taps of A_tap[128 x 64] . W_tap[64 x 64]^T, 4 MMAs (K = 16) per tap,
+// operands staged by TMA in an 8-deep ring of 24 KB stages (A tile 16 KB + W tile 8 KB, 128-byte swizzle), two
+// accumulators so that the epilogue of a tile overlaps the MMAs of the next.  Warp 0: TMA, warp 1: MMA, warps 2-5:
+// epilogue (thread = one voxel row, 64 channels).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "fortis_kernels.h"
+#include "fortis_model.h"
+#include "fortis_tc.cuh"
+
+namespace fortis {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kC = 64;                       // channels of the tensor-core layers
+constexpr int kTile = 128;                   // output rows per tile
+constexpr int kStageA = kTile * kC * 2;      // 16 KB
+constexpr int kStageW = kC * kC * 2;         // 8 KB
+constexpr int kStage = kStageA + kStageW;    // 24 KB
+constexpr int kStagesC = 8;
+constexpr int kConvThreads = 192;
+constexpr int kConvSmem = kStagesC * kStage + 256;
+constexpr uint32_t kConvIdesc = idesc_bf16(kTile, kC);
+enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_ALIGN = 16 };
+
+struct ConvTcParams {
+  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 128
+  CUtensorMap wmap;            // weights [27 * 64 (tap, cout)][64 cin] bf16, box 64 x 64
+  const float* bias;           // [64]
+  const __nv_bfloat16* skip;   // [P][64] or null
+  __nv_bfloat16* out;          // [P][64]
+  int D, H, W;                 // unpadded extent
+  long long P;                 // padded rows
+  float slope;                 // act(v) = max(v, v * slope)
+  int* status;
+};
+
+__global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid_constant__ ConvTcParams P) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t base = smem_u32(smem);
+  if (base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(P.status, 0, CST_ALIGN);
+    return;
+  }
+  const uint32_t bars = base + kStagesC * kStage;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStagesC, bar_acc_full = bars + 16 * kStagesC, bar_acc_empty = bar_acc_full + 16;
+  uint32_t* tmem_slot = (uint32_t*)(smem + kStagesC * kStage + 16 * kStagesC + 32);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long ntiles = (P.P + kTile - 1) / kTile;
+  const int Wp = P.W + 2, Hp = P.H + 2, Dp = P.D + 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStagesC; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0 && lane < 2)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(lane ? &P.wmap : &P.amap)) : "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer: per tile 27 stages, each the shifted activation tile and that tap's weight tile
+    uint32_t s = 0, ph = 0;
+    bool stop = false;
+    for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x) {
+      const long long p0 = tile * kTile;
+      for (int tap = 0; tap < 27; tap++) {
+        const int kd = tap / 9, kh = (tap / 3) % 3, kw = tap % 3;
+        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp + (kw - 1);
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
+        mbar_expect_tx(bar_full + 8 * s, kStage);
+        const uint32_t dst = base + s * kStage;
+        tma_load_2d(dst, &P.amap, 0, (int)(p0 + shift), bar_full + 8 * s);
+        tma_load_2d(dst + kStageA, &P.wmap, 0, tap * kC, bar_full + 8 * s);
+        if (++s == kStagesC) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    uint32_t s = 0, ph = 0, acc_it = 0;
+    const uint64_t desc_hi = make_kmajor_sw128_desc(0) & 0xFFFFFFFF00000000ull;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, acc_it++) {
+      const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+      mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY);
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + b * kC;
+      for (int tap = 0; tap < 27; tap++) {
+        mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
+        tc_fence_after();
+        const uint32_t sb = base + s * kStage;
+        const uint64_t ad = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
+        const uint64_t bd = desc_hi | (uint64_t)(((sb + kStageA) >> 4) & 0x3FFF);
+        tc_mma_ss<kConvIdesc>(d_tmem, ad, bd, (uint32_t)tap);
+#pragma unroll
+        for (int j = 1; j < kC / 16; j++) tc_mma_ss<kConvIdesc>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), 1u);
+        tc_commit(bar_empty + 8 * s);
+        if (++s == kStagesC) { s = 0; ph ^= 1; }
+      }
+      tc_commit(bar_acc_full + 8 * b);
+    }
+  } else {
+    // ---- epilogue: thread = one output row (voxel of the padded volume), 64 channels
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
+    float bias[kC];
+#pragma unroll
+    for (int j = 0; j < kC / 4; j++) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(P.bias) + j);
+      bias[4 * j] = q.x; bias[4 * j + 1] = q.y; bias[4 * j + 2] = q.z; bias[4 * j + 3] = q.w;
+    }
+    uint32_t acc_it = 0;
+    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, acc_it++) {
+      const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+      const long long p = tile * kTile + r;
+      bool interior = false;
+      if (p < P.P) {
+        const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), dp = (int)((p / ((long long)Wp * Hp)) % Dp);
+        interior = wp >= 1 && wp <= P.W && hp >= 1 && hp <= P.H && dp >= 1 && dp <= P.D;
+      }
+      // residual row, fetched while the MMAs of this tile are still running
+      uint4 sk[8];
+      const bool use_skip = P.skip != nullptr && interior;
+      if (use_skip) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + p * kC) + j);
+      }
+      mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL);
+      tc_fence_after();
+      uint32_t a0[32], a1[32];
+      tmem_ld32(lane_addr + b * kC, a0);
+      tmem_ld32(lane_addr + b * kC + 32, a1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty + 8 * b);
+      if (p < P.P) {
+        uint4 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; e++) {
+            const int c = 8 * j + e;
+            v[e] = __uint_as_float(c < 32 ? a0[c] : a1[c - 32]) + bias[c];
+          }
+          if (use_skip) {
+            const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[j]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[2 * e] += f.x; v[2 * e + 1] += f.y; }
+          }
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const float x0 = interior ? fmaxf(v[2 * e], v[2 * e] * P.slope) : 0.f;
+            const float x1 = interior ? fmaxf(v[2 * e + 1], v[2 * e + 1] * P.slope) : 0.f;
+            pk[e] = pack_bf16(x0, x1);
+          }
+          o[j] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(P.out + p * kC);
+#pragma unroll
+        for (int j = 0; j < 8; j++) dst[j] = o[j];
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0)
+    for (int i = 0; i < 2000; i++) __nanosleep(1000);        // let copies in flight land before the CTA gives its memory back
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+  }
+}
+
+// ---- first layer: fp32 NDHWC input with few channels -> padded bf16 [P][64]; thread = (voxel, 8 output channels)
+__global__ void __launch_bounds__(256) conv_in_kernel(const float* __restrict__ x, const float* __restrict__ wt,   // wt [27][C][64]
+                                                      const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                                      int N, int D, int H, int W, int C, float slope) {
+  extern __shared__ float sw[];                               // 27 * C * 64 weights
+  for (int i = threadIdx.x; i < 27 * C * kC; i += 256) sw[i] = wt[i];
+  __syncthreads();
+  const long long nvox = (long long)N * D * H * W;
+  const long long t = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long v = t >> 3;
+  const int g8 = (int)(t & 7) * 8;
+  if (v >= nvox) return;
+  const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; e++) acc[e] = bias[g8 + e];
+  for (int tap = 0; tap < 27; tap++) {
+    const int id = d_ + tap / 9 - 1, ih = h_ + (tap / 3) % 3 - 1, iw = w_ + tap % 3 - 1;
+    if (id < 0 || id >= D || ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+    const float* xp = x + ((((long long)n_ * D + id) * H + ih) * W + iw) * C;
+    for (int c = 0; c < C; c++) {
+      const float xv = __ldg(xp + c);
+      const float* wp = sw + (tap * C + c) * kC + g8;
+#pragma unroll
+      for (int e = 0; e < 8; e++) acc[e] = fmaf(xv, wp[e], acc[e]);
+    }
+  }
+  const long long p = (((long long)n_ * (D + 2) + d_ + 1) * (H + 2) + h_ + 1) * (W + 2) + w_ + 1;
+  uint32_t pk[4];
+#pragma unroll
+  for (int e = 0; e < 4; e++) pk[e] = pack_bf16(fmaxf(acc[2 * e], acc[2 * e] * slope), fmaxf(acc[2 * e + 1], acc[2 * e + 1] * slope));
+  *reinterpret_cast<uint4*>(out + p * kC + g8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+}
+
+// ---- last layer: padded bf16 [P][64] -> fp32 NDHWC with few channels; thread = voxel
+template <int F>
+__global__ void __launch_bounds__(128) conv_out_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ wt,   // wt [27][64][F]
+                                                       const float* __restrict__ bias, float* __restrict__ y,
+                                                       int N, int D, int H, int W, float slope) {
+  __shared__ float sw[27 * kC * F];
+  for (int i = threadIdx.x; i < 27 * kC * F; i += 128) sw[i] = wt[i];
+  __syncthreads();
+  const long long nvox = (long long)N * D * H * W;
+  const long long v = (long long)blockIdx.x * 128 + threadIdx.x;
+  if (v >= nvox) return;
+  const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
+  float acc[F];
+#pragma unroll
+  for (int f = 0; f < F; f++) acc[f] = bias[f];
+  for (int tap = 0; tap < 27; tap++) {
+    const long long p = (((long long)n_ * (D + 2) + d_ + tap / 9) * (H + 2) + h_ + (tap / 3) % 3) * (W + 2) + w_ + tap % 3;
+    const uint4* row = reinterpret_cast<const uint4*>(in + p * kC);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const uint4 q = __ldg(row + j);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float2 xv = __bfloat1622float2(h2[e]);
+        const float* wp = sw + (tap * kC + 8 * j + 2 * e) * F;
+#pragma unroll
+        for (int f = 0; f < F; f++) acc[f] = fmaf(xv.x, wp[f], fmaf(xv.y, wp[F + f], acc[f]));
+      }
+    }
+  }
+#pragma unroll
+  for (int f = 0; f < F; f++) y[v * F + f] = fmaxf(acc[f], acc[f] * slope);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn conv_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+bool make_map(CUtensorMap* m, void* base, long long rows, int box_rows) {
+  EncodeTiledFn enc = conv_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)kC, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)kC * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kC, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+uint16_t to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+float slope_of(const LayerHost& L) { return L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope; }
+
+}  // namespace
+
+struct ConvTcModel {
+  std::vector<LayerHost> meta;
+  float* w_in = nullptr; float* b_in = nullptr;            // first layer, fp32 [27][C][64]
+  float* w_out = nullptr; float* b_out = nullptr;          // last layer, fp32 [27][64][F]
+  std::vector<void*> w_mid; std::vector<float*> b_mid;     // 64 -> 64 layers: bf16 [27*64][64]
+  std::vector<CUtensorMap> wmaps;
+  __nv_bfloat16* buf[3] = {nullptr, nullptr, nullptr};
+  CUtensorMap amaps[3];
+  long long P = 0;
+  int shape[4] = {0, 0, 0, 0};
+  int* status = nullptr;
+};
+
+bool conv_tc_supported(const ModelHost& M, std::string* why) {
+  auto no = [&](const char* w) { if (why) *why = w; return false; };
+  const int nl = (int)M.layers.size();
+  if (nl < 3) return no("the tensor-core conv path needs a first, at least one 64->64 and a last layer");
+  for (int l = 0; l < nl; l++) {
+    const LayerHost& L = M.layers[l];
+    if (L.kind != LAYER_CONV3D || L.ksize != 3 || L.pad != 1) return no("only 3x3x3 pad-1 convolutions");
+    if (L.act == ACT_LEAKY && !(L.slope >= 0.f && L.slope <= 1.f)) return no("LeakyReLU slope outside [0, 1]");
+    if (l == 0 && (L.cout != kC || L.cin > 6 || (L.flags & LFLAG_ADD_SKIP))) return no("first layer must be 1..6 channels -> 64");
+    if (l == nl - 1 && (L.cin != kC || (L.cout != 1 && L.cout != 2 && L.cout != 3 && L.cout != 4) || (L.flags & (LFLAG_ADD_SKIP | LFLAG_SAVE_SKIP))))
+      return no("last layer must be 64 -> 1..4 channels");
+    if (l > 0 && l < nl - 1 && (L.cin != kC || L.cout != kC)) return no("middle layers must be 64 -> 64");
+  }
+  return true;
+}
+
+void conv_tc_destroy(ConvTcModel* m) {
+  if (!m) return;
+  cudaFree(m->w_in); cudaFree(m->b_in); cudaFree(m->w_out); cudaFree(m->b_out);
+  for (void* p : m->w_mid) cudaFree(p);
+  for (float* p : m->b_mid) cudaFree(p);
+  for (auto& p : m->buf) cudaFree(p);
+  cudaFree(m->status);
+  delete m;
+}
+
+ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
+  std::string why;
+  if (!conv_tc_supported(M, &why)) { if (err) *err = why; return nullptr; }
+  ConvTcModel* m = new ConvTcModel();
+  auto fail = [&](const std::string& w) { if (err) *err = w; conv_tc_destroy(m); return (ConvTcModel*)nullptr; };
+  const int nl = (int)M.layers.size();
+  auto upload = [&](const void* h, size_t bytes) -> void* {
+    void* d = nullptr;
+    if (cudaMalloc(&d, bytes) != cudaSuccess) return nullptr;
+    cudaMemcpy(d, h, bytes, cudaMemcpyHostToDevice);
+    return d;
+  };
+  for (int l = 0; l < nl; l++) {
+    const LayerHost& L = M.layers[l];
+    LayerHost meta = L; meta.W.clear(); meta.b.clear();
+    m->meta.push_back(meta);
+    if (l == 0 || l == nl - 1) {
+      std::vector<float> wt((size_t)27 * L.cin * L.cout);          // [tap][cin][cout]
+      for (int f = 0; f < L.cout; f++)
+        for (int c = 0; c < L.cin; c++)
+          for (int t = 0; t < 27; t++) wt[((size_t)t * L.cin + c) * L.cout + f] = L.W[((size_t)f * L.cin + c) * 27 + t];
+      float* dw = (float*)upload(wt.data(), wt.size() * 4);
+      float* db = (float*)upload(L.b.data(), L.b.size() * 4);
+      if (!dw || !db) return fail("out of device memory for conv weights");
+      if (l == 0) { m->w_in = dw; m->b_in = db; } else { m->w_out = dw; m->b_out = db; }
+    } else {
+      std::vector<uint16_t> wb((size_t)27 * kC * kC);              // [tap][cout][cin], cin contiguous (K-major B operand)
+      for (int f = 0; f < kC; f++)
+        for (int c = 0; c < kC; c++)
+          for (int t = 0; t < 27; t++) wb[((size_t)t * kC + f) * kC + c] = to_bf16(L.W[((size_t)f * kC + c) * 27 + t]);
+      void* dw = upload(wb.data(), wb.size() * 2);
+      float* db = (float*)upload(L.b.data(), L.b.size() * 4);
+      if (!dw || !db) return fail("out of device memory for conv weights");
+      m->w_mid.push_back(dw); m->b_mid.push_back(db);
+      CUtensorMap map;
+      if (!make_map(&map, dw, 27 * kC, kC)) return fail("cuTensorMapEncodeTiled failed for conv weights");
+      m->wmaps.push_back(map);
+    }
+  }
+  if (cudaMalloc(&m->status, sizeof(int)) != cudaSuccess) return fail("out of device memory");
+  cudaMemset(m->status, 0, sizeof(int));
+  if (cudaFuncSetAttribute(conv3d_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess)
+    return fail("cannot reserve shared memory for the tensor-core conv kernel");
+  return m;
+}
+
+bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err) {
+  const long long nvox = (long long)N * D * H * W;
+  if (nvox <= 0) { if (err) *err = "conv3d model: set the input extent (option conv_shape = N,D,H,W)"; return false; }
+  const long long P = (long long)N * (D + 2) * (H + 2) * (W + 2);
+  if (P >= (1LL << 31) - 4096) { if (err) *err = "conv3d model: volume too large for 32-bit TMA row coordinates"; return false; }
+  if (m->P != P || m->shape[0] != N || m->shape[1] != D || m->shape[2] != H || m->shape[3] != W) {
+    for (auto& p : m->buf) { cudaFree(p); p = nullptr; }
+    for (int b = 0; b < 3; b++) {
+      if (cudaMalloc(&m->buf[b], (size_t)P * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
+      cudaMemsetAsync(m->buf[b], 0, (size_t)P * kC * 2, s);        // the border must be zero before the first layer writes the interior
+      if (!make_map(&m->amaps[b], m->buf[b], P, kTile)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
+    }
+    m->P = P; m->shape[0] = N; m->shape[1] = D; m->shape[2] = H; m->shape[3] = W;
+  }
+  const int nl = (int)m->meta.size();
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // first layer
+  {
+    const LayerHost& L = m->meta[0];
+    const long long threads = nvox * 8;
+    const size_t smem = (size_t)27 * L.cin * kC * 4;
+    conv_in_kernel<<<(unsigned)((threads + 255) / 256), 256, smem, s>>>(x, m->w_in, m->b_in, m->buf[0], N, D, H, W, L.cin, slope_of(L));
+  }
+  int cur = 0, skip = (m->meta[0].flags & LFLAG_SAVE_SKIP) ? 0 : -1;
+  for (int l = 1; l < nl - 1; l++) {
+    const LayerHost& L = m->meta[l];
+    int dst = -1;
+    for (int b = 0; b < 3; b++) if (b != cur && b != skip) { dst = b; break; }
+    if ((L.flags & LFLAG_ADD_SKIP) && skip < 0) { if (err) *err = "conv3d model: a layer adds a skip that was never saved"; return false; }
+    ConvTcParams P_;
+    std::memset(&P_, 0, sizeof P_);
+    P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l - 1]; P_.bias = m->b_mid[l - 1];
+    P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] : nullptr;
+    P_.out = m->buf[dst]; P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status;
+    const long long ntiles = (P + kTile - 1) / kTile;
+    const int grid = (int)(ntiles < sms ? ntiles : sms);
+    conv3d_tc_kernel<<<grid, kConvThreads, kConvSmem, s>>>(P_);
+    if (L.flags & LFLAG_SAVE_SKIP) skip = dst;
+    cur = dst;
+  }
+  {
+    const LayerHost& L = m->meta[nl - 1];
+    const unsigned grid = (unsigned)((nvox + 127) / 128);
+    const float sl = slope_of(L);
+    switch (L.cout) {
+      case 1: conv_out_kernel<1><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      case 2: conv_out_kernel<2><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      case 3: conv_out_kernel<3><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      default: conv_out_kernel<4><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+    }
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(e); return false; }
+  return true;
+}
+
+int conv_tc_status(ConvTcModel* m) {
+  int v = 0;
+  if (m && m->status) cudaMemcpy(&v, m->status, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+}  // namespace fortis

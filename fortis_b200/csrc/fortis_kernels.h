@@ -86,6 +86,14 @@ bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, i
 bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, int K, int pad,
                   cudaStream_t s, std::string* err);
 
+// tensor-core conv network (fortis_conv3d_tc.cu): bf16 activations in a zero-padded channels-last volume
+struct ConvTcModel;
+bool conv_tc_supported(const ModelHost& M, std::string* why);
+ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err);
+void conv_tc_destroy(ConvTcModel* m);
+bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
+int conv_tc_status(ConvTcModel* m);
+
 void launch_checksum(const void* data, long long n, int elt, double* partials, double* out, int accumulate, cudaStream_t s);
 void launch_fold(const double* partials, int n, double* out, int accumulate, cudaStream_t s);
 

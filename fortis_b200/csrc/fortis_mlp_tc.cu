@@ -37,6 +37,7 @@
 #include "fortis_device.cuh"
 #include "fortis_kernels.h"
 #include "fortis_model.h"
+#include "fortis_tc.cuh"
 
 namespace fortis {
 
@@ -61,7 +62,6 @@ constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5; // uint32 offset + uint8 c
 constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + kTabBytes;   // the base must be 1024-byte aligned
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol0 = 384;
-constexpr uint32_t kWaitLimit = 1u << 24;   // polls of try_wait before giving up (each poll may block briefly)
 
 // status codes (which wait gave up)
 enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6 };
@@ -105,107 +105,7 @@ struct TcParams {
   const Access* store_by_slot;           // [n_out] store target per model output (array < 0: none), fast_out only
 };
 
-// ---------------------------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
-      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// bounded wait: returns false (and raises the abort flag, records `code`) when the limit is reached
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t i = 0; i < kWaitLimit; i++) {
-    if (*abort_flag) return false;
-    if (mbar_try_wait(bar, parity)) return true;
-  }
-  *abort_flag = 1;
-  atomicCAS(status, 0, code);
-  return false;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;          // the common case costs one instruction
-  return mbar_wait_slow(bar, parity, abort_flag, status, code);
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
-      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// The MMA and TMA warps run their loops with all 32 lanes (warp-uniform control flow) and let ONE elected lane issue
-// each asynchronous instruction.  Issuing from a divergent `if (lane == 0)` region instead costs ~100 cycles per
-// tcgen05.mma (operands have to be moved into uniform registers one by one), 3x the 32 cycles a 128x64x16 MMA takes.
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
-}
-
-// D[tmem] (+)= A[tmem] . B[smem]^T, bf16 x bf16 -> fp32, M = 128, N = 64, K = 16
-template <uint32_t IDESC>
-__device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc) {       // D += A.B
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 1;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC) : "memory");
-}
-template <uint32_t IDESC>
-__device__ __forceinline__ void tc_mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\telect.sync _|p, 0xffffffff;\n\tsetp.ne.b32 q, %4, 0;\n\t"
-      "@p tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, q;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC), "r"(accumulate) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);     // .x = lo -> low 16 bits = lower k index
-  return *reinterpret_cast<const uint32_t*>(&v);
-}
+using namespace tc;
 
 // shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 B apart, 8-row groups 1024 B apart
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t saddr) {

@@ -516,6 +516,30 @@ def convnet_forward(layers: Sequence[Dict], x: np.ndarray, dtype=np.float32) -> 
     return h
 
 
+def convnet_forward_lowp(layers: Sequence[Dict], x: np.ndarray) -> np.ndarray:
+    """Model of the bf16 tensor-core conv network: the first layer (few channels in) and the last (few channels
+    out) are computed in fp32 with fp32 weights; the 64->64 layers take bf16 activations and bf16 weights with wide
+    accumulation; every intermediate activation (including the remembered skip) is stored as bf16."""
+    n = len(layers)
+    h = np.asarray(x, dtype=np.float32)
+    skip = None
+    for l, L in enumerate(layers):
+        if l == 0 or l == n - 1:
+            y = conv3d_ndhwc(h.astype(np.float64), np.asarray(L["W"], np.float64), None, L.get("pad", 1), np.float64)
+        else:
+            y = conv3d_ndhwc(h.astype(np.float64), round_bf16(L["W"]).astype(np.float64), None, L.get("pad", 1), np.float64)
+        y = y.astype(np.float32) + np.asarray(L["b"], np.float32)
+        if L.get("add"):
+            y = y + skip
+        y = act_apply(y, L.get("act", "none"), L.get("slope", 0.0)).astype(np.float32)
+        if l < n - 1:
+            y = round_bf16(y)
+        if L.get("save"):
+            skip = y
+        h = y
+    return h
+
+
 def rel_l2(y, ref) -> float:
     y = np.asarray(y, dtype=np.float64).ravel()
     ref = np.asarray(ref, dtype=np.float64).ravel()

@@ -39,6 +39,35 @@ def test_superres_net_small(host, shape):
     assert fo.rel_l2(y, want) < FP32_TOL
 
 
+@pytest.mark.parametrize("shape,blocks", [((2, 9, 7, 5), 2), ((1, 33, 33, 33), 1), ((2, 16, 12, 20), 6)])
+def test_superres_net_bf16_tensor_cores(host, shape, blocks):
+    """The same network on the tcgen05 implicit-GEMM kernel (64 -> 64 layers) with bf16 activations.  Checked against
+    the oracle's model of that arithmetic (tight) and against the fp32 oracle (BASELINE's bf16 bar, 5e-3, or what
+    bf16 storage of 2 * blocks + 1 activations costs by itself if that is more)."""
+    N, D, H, W = shape
+    layers = fortis_b200.conv_layers(3, 64, 3, nblocks=blocks, seed=6)
+    for L in layers:
+        L["b"] = (np.random.default_rng(1).normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = np.random.default_rng(5).normal(size=(N, D, H, W, 3)).astype(np.float32)
+    model = fo.convnet_forward_lowp(layers, x)
+    exact = fo.convnet_forward(layers, x)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", "bf16")
+    host.option("conv_shape", "%d,%d,%d,%d" % shape)
+    y = np.zeros((N, D, H, W, 3), np.float32)
+    host.forward(x, y)
+    y2 = np.zeros_like(y)
+    host.forward(x, y2)                                      # second call reuses the padded buffers
+    assert y2.tobytes() == y.tobytes()
+    e_model, e_exact = fo.rel_l2(y, model), fo.rel_l2(y, exact)
+    bar = max(5e-3, 1.1 * fo.rel_l2(model, exact))
+    # A deep residual stack amplifies rounding decorrelation: merely accumulating the MODEL in fp32 instead of fp64
+    # moves its 6-block output by 5e-3 (4e-4 at 2 blocks, 3e-5 at 1), so the tight model check is for shallow stacks.
+    model_bar = 2e-3 if blocks <= 2 else bar
+    assert e_model < model_bar and e_exact < bar, "vs bf16 model %.3e, vs fp32 %.3e (bar %.3e)" % (e_model, e_exact, bar)
+    assert host.L.fortis_device_status() == 0
+
+
 def test_conv_probe_stamp_through_memref_entry(host, golden_dir):
     """The reference's conv probe (frontend/export_conv.py; README stamp 9617.28) through fortis_conv3d's memref ABI:
     NCDHW fp32, the bias and LeakyReLU(0.1) applied afterwards as the compiled program does in its epilogue kernel."""
