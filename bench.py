@@ -139,8 +139,8 @@ def cpu_step_fn(wl, sample_units):
     from oracle import build as ob
     from oracle import cport
     lib = ctypes.CDLL(ob.build_port(verbose=False))
-    lib.oracle_max_threads.restype = ctypes.c_int
-    threads = lib.oracle_max_threads()
+    # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which is not what a CPU baseline wants)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     from oracle import fortis_oracle as fo
     G, S, Lp, K = wl["G"], wl["S"], wl["Lp"], wl["K"]
     P = fo.loop_params(Lp, K)
@@ -177,7 +177,7 @@ def cpu_step_fn(wl, sample_units):
     def step():
         lib.oracle_step(ctypes.c_long(count), 1, P["ni"], len(G["slots"]), inp, ia, io, isi, isj, isk,
                         len(S["stores"]), outp, oa, oo, osi, osj, osk, PL["n"], PL["dims"], PL["Wp"], PL["bp"], PL["act"],
-                        PL["slope"], 0, ctypes.byref(cs))
+                        PL["slope"], threads, ctypes.byref(cs))
         return count
     return step, threads
 
@@ -346,7 +346,7 @@ def main():
             pass
         roof["traffic"] = traffic
         roof["kernel_ms"] = kernel_ms
-        cpu = None if (args.no_cpu or is_conv) else time_cpu(wl)
+        cpu = None if (args.no_cpu or is_conv or world > 1) else time_cpu(wl)      # the CPU baseline is an N = 1 figure
         launches_per_step = len(wl["layers"]) if is_conv else 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
         line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",

@@ -32,7 +32,8 @@ def build(force=False, verbose=False):
         hdr_newest = max(os.path.getmtime(p) for p in _deps() if p.endswith((".h", ".cuh")))
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(srcp), hdr_newest):
             return obj
-        cmd = ["nvcc"] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", srcp, "-o", obj]
+        extra = os.environ.get("FORTIS_NVCC_FLAGS", "").split()       # e.g. -DFORTIS_TC_PROFILE for the cycle counters
+        cmd = ["nvcc"] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", srcp, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode:
             sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)

@@ -576,20 +576,28 @@ void run_step_kernels(const StepArgs& A) {
   }
   const bool fused_gather = A.use_gather && s.fuse;
   if (s.precision != PREC_F32) {
+    // The tensor-core kernel fuses the gather / scatter when the descriptor is in its table-driven class (fp32
+    // arrays, no lifted expressions or scalars, at most two stride classes, <= 256 inputs / <= 128 outputs);
+    // other descriptors run the bit-exact standalone gather / scatter kernels around it.
     TcLaunch L{};
-    if (A.use_gather) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; L.fast_in = s.G.fast;
-                        std::memcpy(L.cin, s.G.cls, sizeof L.cin); } else L.X = s.din;
-    if (A.fuse_scatter) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS;
-                          L.slot_head = s.S.slot_head; L.store_next = s.S.store_next; L.fast_out = s.S.fast;
-                          L.store_by_slot = s.S.store_by_slot; std::memcpy(L.cout, s.S.cls, sizeof L.cout); }
-    L.Y = A.fuse_scatter ? nullptr : s.dout;
+    const bool fuse_in = A.use_gather && s.fuse && s.G.fast && s.model.n_in() <= 256;
+    const bool fuse_out = A.fuse_scatter && s.fuse && s.S.fast && s.model.n_out() <= 128;
+    if (fuse_in) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; L.fast_in = 1; std::memcpy(L.cin, s.G.cls, sizeof L.cin); }
+    else {
+      if (A.use_gather) launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, A.TG, g, s.din, st);
+      L.X = s.din;
+    }
+    if (fuse_out) { L.SP = s.S.hdr; L.stores = (const StoreTarget*)s.S.items; L.TS = A.TS; L.fast_out = 1;
+                    L.store_by_slot = s.S.store_by_slot; std::memcpy(L.cout, s.S.cls, sizeof L.cout); }
+    L.Y = fuse_out ? nullptr : s.dout;
     L.g = g;
     ensure_aux(tc_grid(rows));
-    L.partials = (A.fuse_scatter && s.want_checksum) ? s.d_partials : nullptr;
+    L.partials = (fuse_out && s.want_checksum) ? s.d_partials : nullptr;
     L.status = s.d_status;
     std::string err;
     if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
     if (L.partials) launch_fold(s.d_partials, tc_grid(rows), s.d_sum, 1, st);
+    if (A.fuse_scatter && !fuse_out) launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, A.TS, g, s.dout, st);
     return;
   }
   if (fused_gather && s.small_ok) {

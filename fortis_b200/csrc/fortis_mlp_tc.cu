@@ -10,7 +10,8 @@
 //   * A (the layer's input activations, bf16) lives in TENSOR MEMORY: lane = row, two K values per 32-bit column
 //     (K <= 768 -> 384 columns).  The MMAs take A from TMEM and B from shared memory, so shared-memory read
 //     bandwidth is spent on the weights only.
-//   * W streams from L2 through a ring of 16 KB TMA stages (64 features x 128 k, 128-byte swizzle, no multicast).
+//   * W streams from L2 through a ring of 32 KB TMA stages (64 features x 256 k, 128-byte swizzle, one 3-D tile
+//     load per stage, no multicast).
 //   * D: two 64-column fp32 accumulators in TMEM; the epilogue of chunk c overlaps the MMAs of chunk c+1.
 //   * The epilogue (8 warps; thread = one row x 32 features) adds bias, applies the activation, rounds to bf16 and
 //     parks the chunk: chunks 0-7 in shared memory, chunks 8-11 in registers (A is still being read by later
@@ -18,8 +19,9 @@
 //     written into the A columns with tcgen05.st and the next layer starts.
 //   * Layer 0's A is produced by the same threads straight from the host's Fortran arrays (thread = row, so every
 //     slot is a coalesced load); the last layer's epilogue stores straight into the host arrays and accumulates
-//     the fp64 checksum.
-// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 6 x 16 KB weight ring.
+//     the fp64 checksum.  This fusion is table-driven and covers fp32 arrays without lifted expressions; any other
+//     descriptor is served by the standalone gather / scatter kernels writing X / reading Y around this kernel.
+// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 3 x 32 KB weight ring.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word, raises a CTA-wide
 // abort flag that turns all later waits into no-ops, and the CTA still frees its tensor memory and returns.
@@ -45,9 +47,10 @@ namespace {
 
 constexpr int kTileM = 128;
 constexpr int kChunkN = 64;                 // output features per accumulator
-constexpr int kStageK = 128;                // k extent of one weight stage
-constexpr int kStageBytes = kChunkN * kStageK * 2;   // 16 KB
-constexpr int kStages = 6;
+constexpr int kStageK = 256;                // k extent of one weight stage: four 64-wide swizzled sub-tiles, ONE TMA
+constexpr int kStageBytes = kChunkN * kStageK * 2;   // 32 KB
+constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 KB
+constexpr int kStages = 3;
 constexpr int kSmemChunks = 8;              // parked chunks held in shared memory; the rest in registers
 constexpr int kMaxChunks = 12;              // 768 / 64
 constexpr int kMaxK = 768;
@@ -58,7 +61,7 @@ constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
 constexpr int kBarBytes = 256;
 constexpr int kFastIn = 256, kFastOut = 128;          // widest model input / output the fast I/O tables hold
-constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5; // uint32 offset + uint8 code per slot / store
+constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5 + 2 * kMaxArrays * 8;   // uint32 offset + uint8 code per slot / store, array bases
 constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + kTabBytes;   // the base must be 1024-byte aligned
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol0 = 384;
@@ -67,7 +70,7 @@ constexpr uint32_t kAccCol0 = 384;
 enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6 };
 
 struct TcLayer {
-  int K, N;                // padded: K multiple of 128, N multiple of 64 (hidden: multiple of 128)
+  int K, N;                // padded: K multiple of 256, N multiple of 64 (hidden: multiple of 256)
   int n_real;              // unpadded output width
   int act;
   float slope;             // branch-free activation: act(v) = max(v, v * slope); none -> 1, ReLU -> 0, LeakyReLU -> slope
@@ -125,11 +128,9 @@ __device__ __forceinline__ float act_f(float v, float slope) { return fmaxf(v, v
 
 // cycle accounting for diagnostics: adds the time since *t to prof[slot] (CTA 0, one lane) and restarts the clock
 __device__ __forceinline__ void prof_add(long long* prof, int slot, long long* t, bool who) {
-#ifdef FORTIS_TC_PROFILE
+  // always compiled (one well-predicted branch per call when prof is null): compiling it out makes the optimiser
+  // restructure the role loops and nvcc's front end then runs for tens of minutes on this kernel
   if (prof && who) { const long long n = clock64(); atomicAdd((unsigned long long*)&prof[slot], (unsigned long long)(n - *t)); *t = n; }
-#else
-  (void)prof; (void)slot; (void)t; (void)who;
-#endif
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -156,6 +157,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   uint32_t* o_off = s_off + kFastIn;                                                  // [kFastOut] store offsets
   uint8_t* s_code = (uint8_t*)(o_off + kFastOut);                                     // array | class << 7, 0xFF: none
   uint8_t* o_code = s_code + kFastIn;
+  // array base pointers of the fast paths, copied out of the kernel parameters so that the unrolled load / store
+  // loops index shared memory (indexing the parameter block dynamically makes nvcc's front end crawl)
+  const float** s_base_in = (const float**)(o_code + kFastOut);
+  float** s_base_out = (float**)(s_base_in + kMaxArrays);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long ntiles = (P.nrows + kTileM - 1) / kTileM;
@@ -166,6 +171,10 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     mbar_init(bar_a_ready, kEpiThreads);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x < kMaxArrays) {
+    s_base_in[threadIdx.x] = (const float*)P.TG.base[threadIdx.x];
+    s_base_out[threadIdx.x] = (float*)P.TS.base[threadIdx.x];
   }
   if (P.fast_in)
     for (int q = threadIdx.x; q < kFastIn; q += kThreads) {
@@ -215,8 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             prof_add(P.prof, 16, &pt, pw);
             mbar_expect_tx(bar_full + 8 * s, kStageBytes);
             const uint32_t dst = ring + s * kStageBytes;
-            tma_load_2d(dst, map, kb * kStageK, c * kChunkN, bar_full + 8 * s);
-            tma_load_2d(dst + kStageBytes / 2, map, kb * kStageK + 64, c * kChunkN, bar_full + 8 * s);
+            tma_load_3d(dst, map, 0, c * kChunkN, kb * (kStageK / 64), bar_full + 8 * s);
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
       }
@@ -245,16 +253,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
             prof_add(P.prof, 3, &pt, pw);
             tc_fence_after();
-            // descriptors of the stage's two 64-wide k sub-tiles; stepping k by 16 inside a 128-byte swizzle row
-            // adds 32 bytes = 2 to the (address >> 4) field
+            // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
+            // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
             const uint32_t sb = ring + s * kStageBytes;
             const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
-            const uint64_t bd1 = desc_hi | (uint64_t)(((sb + kStageBytes / 2) >> 4) & 0x3FFF);
             const uint32_t a0 = tmem + kb * (kStageK / 2);
             tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)kb);
 #pragma unroll
             for (int j = 1; j < kStageK / 16; j++)
-              tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, (j < 4 ? bd0 : bd1) + (uint64_t)((j & 3) * 2));
+              tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
             tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
             if (++s == kStages) { s = 0; ph ^= 1; }
           }
@@ -290,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               const uint32_t code = s_code[q0 + j];
               v[j] = 0.f;
               if (live && code != 0xFF)
-                v[j] = __ldg((const float*)P.TG.base[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? pos1 : pos0)));
+                v[j] = __ldg(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? pos1 : pos0)));
             }
             if (P.in_div) {
 #pragma unroll
@@ -302,25 +309,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
           }
         } else {
-          double sc[kMaxScalars];
-          if (live && P.GP && P.GP->nscalars) load_scalars(*P.GP, P.TG, ci, cj, kk, sc);
+          // input already materialised as X (rows, n_in): array-form calls, and descriptors the fast tables cannot
+          // express (lifted expressions, f64 arrays, scalars), for which the standalone gather kernel ran first
           for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = (live && q0 + j < P.n_in) ? __ldg(P.X + row * P.n_in + q0 + j) : 0.f;
+            if (P.in_div) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+            }
             uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-              float v[2];
-#pragma unroll
-              for (int e = 0; e < 2; e++) {
-                const int q = q0 + 2 * j + e;
-                float x = 0.f;
-                if (live && q < P.n_in) {
-                  x = P.GP ? gather_value(*P.GP, P.slots[q], P.TG, q, ci, cj, kk, sc) : __ldg(P.X + row * P.n_in + q);
-                  if (P.in_div) x = __fdiv_rn(x, __ldg(P.in_div + q));
-                }
-                v[e] = x;
-              }
-              pk[j] = pack_bf16(v[0], v[1]);
-            }
+            for (int j = 0; j < 16; j++) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
             tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
           }
         }
@@ -335,75 +336,86 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         const bool last = l == P.nlayers - 1;
         const float slope = L.slope;
         if (!last) {
+          // epilogue of one chunk: accumulator -> (x scale) + bias -> activation -> 16 packed bf16 pairs
+          auto chunk_epilogue = [&](int c, uint32_t (&pk)[16]) {
+            const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+            acc_it++;
+            const int n0 = c * kChunkN + half * 32;
+            // the 32 biases of this thread's features: warp-uniform 16-byte loads issued before the wait
+            float4 bq[8];
 #pragma unroll
-          for (int c = 0; c < kMaxChunks; c++) {
-            if (c < nchunks) {
-              const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-              acc_it++;
-              const int n0 = c * kChunkN + half * 32;
-              // the 32 biases of this thread's features: warp-uniform 16-byte loads issued before the wait
-              float4 bq[8];
-#pragma unroll
-              for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
-              prof_add(P.prof, 11, &pt, pw);
-              mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
-              prof_add(P.prof, 10, &pt, pw);
-              tc_fence_after();
-              uint32_t a[32];
-              tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
-              tmem_ld_wait();
-              tc_fence_before();
-              mbar_arrive(bar_acc_empty + 8 * b);             // the MMA warp may refill this accumulator
-              if (HAS_SCALE) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                  const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
-                  a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
-                  a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
-                  a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
-                  a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
-                }
-              }
-              uint32_t pk[16];
+            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
+            prof_add(P.prof, 11, &pt, pw);
+            mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            prof_add(P.prof, 10, &pt, pw);
+            tc_fence_after();
+            uint32_t a[32];
+            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty + 8 * b);             // the MMA warp may refill this accumulator
+            if (HAS_SCALE) {
 #pragma unroll
               for (int j = 0; j < 8; j++) {
-                const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
-                const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
-                const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
-                const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
-                pk[2 * j] = pack_bf16(v0, v1);
-                pk[2 * j + 1] = pack_bf16(v2, v3);
+                const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+                a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
+                a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
+                a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
+                a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
               }
-              if (c < kSmemChunks) {
-                // [chunk][half][16-byte piece][row]: lanes are rows, so every store is conflict-free
-                uint8_t* dst = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+            }
 #pragma unroll
-                for (int p = 0; p < 4; p++)
-                  *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
-              } else {
+            for (int j = 0; j < 8; j++) {
+              const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
+              const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
+              const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
+              const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
+              pk[2 * j] = pack_bf16(v0, v1);
+              pk[2 * j + 1] = pack_bf16(v2, v3);
+            }
+          };
+          // chunks parked in shared memory: a rolled loop (the address depends on c only arithmetically)
+          const int nsm = nchunks < kSmemChunks ? nchunks : kSmemChunks;
+#pragma unroll 1
+          for (int c = 0; c < nsm; c++) {
+            uint32_t pk[16];
+            chunk_epilogue(c, pk);
+            // [chunk][half][16-byte piece][row]: lanes are rows, so every store is conflict-free
+            uint8_t* dst = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
-                for (int j = 0; j < 16; j++) kept[(c >= kSmemChunks ? c - kSmemChunks : 0) * 16 + j] = pk[j];
-              }
+            for (int p = 0; p < 4; p++)
+              *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
+          }
+          // chunks parked in registers: unrolled so that `kept` is indexed statically
+#pragma unroll
+          for (int c = kSmemChunks; c < kMaxChunks; c++) {
+            if (c < nchunks) {
+              uint32_t pk[16];
+              chunk_epilogue(c, pk);
+#pragma unroll
+              for (int j = 0; j < 16; j++) kept[(c - kSmemChunks) * 16 + j] = pk[j];
             }
           }
           // every MMA of this layer has retired (its last accumulator was complete), so A may be overwritten:
           // move the parked chunks into the A columns and release the next layer
           prof_add(P.prof, 11, &pt, pw);
+#pragma unroll 1
+          for (int c = 0; c < nsm; c++) {
+            uint32_t pk[16];
+            const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
-          for (int c = 0; c < kMaxChunks; c++) {
+            for (int p = 0; p < 4; p++) {
+              const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
+              pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
+            }
+            tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
+          }
+#pragma unroll
+          for (int c = kSmemChunks; c < kMaxChunks; c++) {
             if (c < nchunks) {
               uint32_t pk[16];
-              if (c < kSmemChunks) {
-                const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
-                for (int p = 0; p < 4; p++) {
-                  const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
-                  pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; j++) pk[j] = kept[(c >= kSmemChunks ? c - kSmemChunks : 0) * 16 + j];
-              }
+              for (int j = 0; j < 16; j++) pk[j] = kept[(c - kSmemChunks) * 16 + j];
               tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
             }
           }
@@ -413,8 +425,6 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           prof_add(P.prof, 12, &pt, pw);
         } else {
           // ---- last layer: bias, output scaling / masks, then straight into the host arrays
-          double sc[kMaxScalars];
-          if (live && P.SP && !P.fast_out && P.SP->nscalars) load_scalars(*P.SP, P.TS, ci, cj, kk, sc);
           const long long opos0 = ci * P.cout[0].si + cj * P.cout[0].sj + kk * P.cout[0].sk;
           const long long opos1 = ci * P.cout[1].si + cj * P.cout[1].sj + kk * P.cout[1].sk;
           for (int c = 0; c < nchunks; c++) {
@@ -458,28 +468,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
                 for (int j = 0; j < 32; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
               }
-              if (P.SP && P.fast_out) {
+              if (P.fast_out) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                   const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
                   if (code != 0xFF) {
-                    ((float*)P.TS.base[code & 0x7F])[(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
+                    s_base_out[code & 0x7F][(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
                     csum += (double)v[j];
-                  }
-                }
-              } else if (P.SP) {
-#pragma unroll 1
-                for (int j = 0; j < 32; j++) {
-                  const int n = n0 + j;
-                  if (n >= P.n_out) break;
-                  float vj = 0.f;
-#pragma unroll
-                  for (int t = 0; t < 32; t++) if (t == j) vj = v[t];
-                  for (int s2 = __ldg(P.slot_head + n); s2 >= 0; s2 = __ldg(P.store_next + s2)) {
-                    const StoreTarget st = P.stores[s2];
-                    const double o = scatter_value(*P.SP, P.TS, n, vj, sc);
-                    store_elem(P.TS, st.a, access_offset(st.a, ci, cj, kk), o);
-                    csum += st.a.elt == 0 ? (double)(float)o : o;
                   }
                 }
               }
@@ -645,11 +640,13 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     TcLayer& T = m->layer[l];
     T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds;
     T.slope = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;      // act(v) = max(v, v * slope)
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)kChunkN};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(&m->maps[l], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    // W[N][K] viewed as [K/64][N][64]: one box of {64 k, 64 rows, 4 k-blocks} lands in shared memory as four
+    // consecutive 64 x 64 sub-tiles, each in the 128-byte-swizzled K-major layout the MMA descriptor expects
+    const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)kChunkN, (cuuint32_t)(kStageK / 64)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = enc(&m->maps[l], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
   }
@@ -686,8 +683,8 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
     P.cout[i] = StrideClass{L.cout[i][0], L.cout[i][1], L.cout[i][2]};
   }
   P.store_by_slot = L.store_by_slot;
-  if (!P.GP && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
-  if (P.SP && (!P.slot_head || !P.store_next)) { if (err) *err = "tensor-core step: scatter index missing"; return false; }
+  if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
+  if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(nrows);
   static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
   static long long* dprof = nullptr;
