@@ -13,9 +13,12 @@
 // which keeps the padding intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work
 // at 33^3.
 //
-// Per 128-row tile: D[128 x 64] = sum over 27 taps of A_tap[128 x 64] . W_tap[64 x 64]^T, 4 MMAs (K = 16) per tap,
-// operands staged by TMA in an 8-deep ring of 24 KB stages (A tile 16 KB + W tile 8 KB, 128-byte swizzle), two
-// accumulators so that the epilogue of a tile overlaps the MMAs of the next.  Warp 0: TMA, warp 1: MMA, warps 2-5:
+// Per 128-row tile: D[128 x 64] = sum over 27 taps of A_tap[128 x 64] . W_tap[64 x 64]^T, 4 MMAs (K = 16) per tap.
+// The three kw taps of one (kd, kh) read the same activation rows shifted by one, so ONE 130-row tile is staged per
+// (kd, kh) and the three taps address it through descriptors whose start moves by 128 bytes (the kernel is bound
+// by the L2 -> shared-memory stream, and this cuts it from 648 KB to 366 KB per tile).  Ring of 5 stages of 41 KB
+// (activation tile + the three weight tiles, 128-byte swizzle); two accumulators so that the epilogue of a tile
+// overlaps the MMAs of the next.  Warp 0: TMA, warp 1: MMA, warps 2-5:
 // epilogue (thread = one voxel row, 64 channels).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -38,18 +41,20 @@ namespace {
 
 constexpr int kC = 64;                       // channels of the tensor-core layers
 constexpr int kTile = 128;                   // output rows per tile
-constexpr int kStageA = kTile * kC * 2;      // 16 KB
-constexpr int kStageW = kC * kC * 2;         // 8 KB
-constexpr int kStage = kStageA + kStageW;    // 24 KB
-constexpr int kStagesC = 8;
+constexpr int kRowsA = kTile + 2;            // the three kw taps of one (kd, kh) read rows p0-1 .. p0+128 of the same tile
+constexpr int kBytesA = kRowsA * kC * 2;     // 16,640 B landed by TMA
+constexpr int kStageA = 17 * 1024;           // region reserved for it (1024-byte multiple keeps the weights aligned)
+constexpr int kStageW = 3 * kC * kC * 2;     // 24 KB: the three kw weight tiles, consecutive rows of the weight matrix
+constexpr int kStage = kStageA + kStageW;    // 41 KB
+constexpr int kStagesC = 5;
 constexpr int kConvThreads = 192;
 constexpr int kConvSmem = kStagesC * kStage + 256;
 constexpr uint32_t kConvIdesc = idesc_bf16(kTile, kC);
 enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_ALIGN = 16 };
 
 struct ConvTcParams {
-  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 128
-  CUtensorMap wmap;            // weights [27 * 64 (tap, cout)][64 cin] bf16, box 64 x 64
+  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 130
+  CUtensorMap wmap;            // weights [27 * 64 (tap, cout)][64 cin] bf16, box 64 x 192
   const float* bias;           // [64]
   const __nv_bfloat16* skip;   // [P][64] or null
   __nv_bfloat16* out;          // [P][64]
@@ -97,14 +102,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     bool stop = false;
     for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x) {
       const long long p0 = tile * kTile;
-      for (int tap = 0; tap < 27; tap++) {
-        const int kd = tap / 9, kh = (tap / 3) % 3, kw = tap % 3;
-        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp + (kw - 1);
+      for (int g = 0; g < 9; g++) {                               // (kd, kh) groups: one activation tile serves kw = 0, 1, 2
+        const int kd = g / 3, kh = g % 3;
+        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp - 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
-        mbar_expect_tx(bar_full + 8 * s, kStage);
+        mbar_expect_tx(bar_full + 8 * s, kBytesA + kStageW);
         const uint32_t dst = base + s * kStage;
         tma_load_2d(dst, &P.amap, 0, (int)(p0 + shift), bar_full + 8 * s);
-        tma_load_2d(dst + kStageA, &P.wmap, 0, tap * kC, bar_full + 8 * s);
+        tma_load_2d(dst + kStageA, &P.wmap, 0, g * 3 * kC, bar_full + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
       }
     }
@@ -117,15 +122,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY);
       tc_fence_after();
       const uint32_t d_tmem = tmem + b * kC;
-      for (int tap = 0; tap < 27; tap++) {
+      for (int g = 0; g < 9; g++) {
         mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
         tc_fence_after();
         const uint32_t sb = base + s * kStage;
         const uint64_t ad = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
         const uint64_t bd = desc_hi | (uint64_t)(((sb + kStageA) >> 4) & 0x3FFF);
-        tc_mma_ss<kConvIdesc>(d_tmem, ad, bd, (uint32_t)tap);
 #pragma unroll
-        for (int j = 1; j < kC / 16; j++) tc_mma_ss<kConvIdesc>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), 1u);
+        for (int kw = 0; kw < 3; kw++) {
+          // tap kw reads the tile shifted down by kw rows: the start address moves by kw * 128 bytes; the 128-byte
+          // swizzle is a function of the shared-memory address itself, so the shifted view stays consistent with
+          // what TMA wrote
+          const uint64_t adk = ad + (uint64_t)(kw * 8);
+          const uint64_t bdk = bd + (uint64_t)(kw * (kC * kC * 2 >> 4));
+#pragma unroll
+          for (int j = 0; j < kC / 16; j++)
+            tc_mma_ss<kConvIdesc>(d_tmem, adk + (uint64_t)(j * 2), bdk + (uint64_t)(j * 2), (uint32_t)(g | kw | j));
+        }
         tc_commit(bar_empty + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
       }
@@ -386,7 +399,7 @@ ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
       if (!dw || !db) return fail("out of device memory for conv weights");
       m->w_mid.push_back(dw); m->b_mid.push_back(db);
       CUtensorMap map;
-      if (!make_map(&map, dw, 27 * kC, kC)) return fail("cuTensorMapEncodeTiled failed for conv weights");
+      if (!make_map(&map, dw, 27 * kC, 3 * kC)) return fail("cuTensorMapEncodeTiled failed for conv weights");
       m->wmaps.push_back(map);
     }
   }
@@ -407,7 +420,7 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     for (int b = 0; b < 3; b++) {
       if (cudaMalloc(&m->buf[b], (size_t)P * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
       cudaMemsetAsync(m->buf[b], 0, (size_t)P * kC * 2, s);        // the border must be zero before the first layer writes the interior
-      if (!make_map(&m->amaps[b], m->buf[b], P, kTile)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
+      if (!make_map(&m->amaps[b], m->buf[b], P, kRowsA)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
     }
     m->P = P; m->shape[0] = N; m->shape[1] = D; m->shape[2] = H; m->shape[3] = W;
   }
