@@ -36,8 +36,8 @@ BYTES_PER_COL = {"column": 4 * (244 + 128), "stencil": 24, "toy": 4 * 128}
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="fortis_b200", choices=["fortis_b200", "reference"])
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32", "fp8w"])
     ap.add_argument("--workload", default="column", choices=["column", "column_c5", "stencil", "toy", "conv"])
@@ -190,10 +190,15 @@ def time_cpu(wl, target_s=12.0):
     rate = n / dt
     sample = int(min(wl["units"], max(probe_units, rate * target_s)))
     step, threads = cpu_step_fn(wl, sample)
-    t0 = time.perf_counter(); n = step(); dt = time.perf_counter() - t0
-    return dict(value=n / dt, unit="columns/s", cores=threads, kind="port",
-                sample="%d of %d columns of the same workload, one pass, %.1f s; C port of the reference's native "
-                       "Fortran forward (no Fortran compiler in the image), OpenMP over columns" % (n, wl["units"], dt))
+    done, passes, t0 = 0, 0, time.perf_counter()
+    while True:                                   # whole passes over the sample until about target_s of CPU work
+        done += step(); passes += 1
+        dt = time.perf_counter() - t0
+        if dt >= target_s or passes >= 64:
+            break
+    return dict(value=done / dt, unit="columns/s", cores=threads, kind="port",
+                sample="%d of %d columns of the same workload x %d passes, %.1f s; C port of the reference's native "
+                       "Fortran forward (no Fortran compiler in the image), OpenMP over columns" % (done // passes, wl["units"], passes, dt))
 
 
 def run_reference(args):
@@ -255,6 +260,7 @@ def main():
     h.option("precision", prec)
     if is_conv:
         h.option("conv_shape", "%d,%d,%d,%d" % wl["shape"])
+        h.option("graph", 1)                               # FORTIS_GRAPH: the 14 launches of a step replay as one graph
     h.option("checksum", 1)
     h.option("async", 1)
     stream = torch.cuda.ExternalStream(h.stream())

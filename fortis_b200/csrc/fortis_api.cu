@@ -1266,6 +1266,7 @@ int fortis_device_status(void) {
   int v = 0;
   cudaStreamSynchronize(stream());
   cudaMemcpy(&v, s.d_status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (v == 0 && s.conv) v = conv_model_status(s.conv);
   return v;
   FORTIS_CATCH(return -1)
 }

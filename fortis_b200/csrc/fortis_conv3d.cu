@@ -151,6 +151,8 @@ void conv_model_destroy(ConvModel* m) {
   delete m;
 }
 
+int conv_model_status(ConvModel* m) { return m && m->tcm ? conv_tc_status(m->tcm) : 0; }
+
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
   (void)s;
   if (precision == PREC_FP8W) { if (err) *err = "conv3d networks run in fp32 or bf16"; return nullptr; }

@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
   }
 }
 
-// ---- first layer: fp32 NDHWC input with few channels -> padded bf16 [P][64]; thread = (voxel, 8 output channels)
+// ---- first layer: fp32 NDHWC input with few channels -> padded bf16 [P][64]; thread = (voxel, 8 output channels).
+// Persistent blocks: the 27 * C * 64 weights are staged in shared memory once per block, not once per 32 voxels.
 __global__ void __launch_bounds__(256) conv_in_kernel(const float* __restrict__ x, const float* __restrict__ wt,   // wt [27][C][64]
                                                       const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
                                                       int N, int D, int H, int W, int C, float slope) {
@@ -228,65 +229,94 @@ __global__ void __launch_bounds__(256) conv_in_kernel(const float* __restrict__ 
   for (int i = threadIdx.x; i < 27 * C * kC; i += 256) sw[i] = wt[i];
   __syncthreads();
   const long long nvox = (long long)N * D * H * W;
-  const long long t = (long long)blockIdx.x * 256 + threadIdx.x;
-  const long long v = t >> 3;
-  const int g8 = (int)(t & 7) * 8;
-  if (v >= nvox) return;
-  const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
-  float acc[8];
+  const int g8 = (threadIdx.x & 7) * 8;
+  float b8[8];
 #pragma unroll
-  for (int e = 0; e < 8; e++) acc[e] = bias[g8 + e];
-  for (int tap = 0; tap < 27; tap++) {
-    const int id = d_ + tap / 9 - 1, ih = h_ + (tap / 3) % 3 - 1, iw = w_ + tap % 3 - 1;
-    if (id < 0 || id >= D || ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
-    const float* xp = x + ((((long long)n_ * D + id) * H + ih) * W + iw) * C;
-    for (int c = 0; c < C; c++) {
-      const float xv = __ldg(xp + c);
-      const float* wp = sw + (tap * C + c) * kC + g8;
+  for (int e = 0; e < 8; e++) b8[e] = bias[g8 + e];
+  for (long long v = (long long)blockIdx.x * 32 + (threadIdx.x >> 3); v < nvox; v += (long long)gridDim.x * 32) {
+    const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
+    float acc[8];
 #pragma unroll
-      for (int e = 0; e < 8; e++) acc[e] = fmaf(xv, wp[e], acc[e]);
+    for (int e = 0; e < 8; e++) acc[e] = b8[e];
+    for (int tap = 0; tap < 27; tap++) {
+      const int id = d_ + tap / 9 - 1, ih = h_ + (tap / 3) % 3 - 1, iw = w_ + tap % 3 - 1;
+      if (id < 0 || id >= D || ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
+      const float* xp = x + ((((long long)n_ * D + id) * H + ih) * W + iw) * C;
+      for (int c = 0; c < C; c++) {
+        const float xv = __ldg(xp + c);
+        const float4 w0 = *reinterpret_cast<const float4*>(sw + (tap * C + c) * kC + g8);
+        const float4 w1 = *reinterpret_cast<const float4*>(sw + (tap * C + c) * kC + g8 + 4);
+        acc[0] = fmaf(xv, w0.x, acc[0]); acc[1] = fmaf(xv, w0.y, acc[1]); acc[2] = fmaf(xv, w0.z, acc[2]); acc[3] = fmaf(xv, w0.w, acc[3]);
+        acc[4] = fmaf(xv, w1.x, acc[4]); acc[5] = fmaf(xv, w1.y, acc[5]); acc[6] = fmaf(xv, w1.z, acc[6]); acc[7] = fmaf(xv, w1.w, acc[7]);
+      }
     }
-  }
-  const long long p = (((long long)n_ * (D + 2) + d_ + 1) * (H + 2) + h_ + 1) * (W + 2) + w_ + 1;
-  uint32_t pk[4];
+    const long long p = (((long long)n_ * (D + 2) + d_ + 1) * (H + 2) + h_ + 1) * (W + 2) + w_ + 1;
+    uint32_t pk[4];
 #pragma unroll
-  for (int e = 0; e < 4; e++) pk[e] = pack_bf16(fmaxf(acc[2 * e], acc[2 * e] * slope), fmaxf(acc[2 * e + 1], acc[2 * e + 1] * slope));
-  *reinterpret_cast<uint4*>(out + p * kC + g8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    for (int e = 0; e < 4; e++) pk[e] = pack_bf16(fmaxf(acc[2 * e], acc[2 * e] * slope), fmaxf(acc[2 * e + 1], acc[2 * e + 1] * slope));
+    *reinterpret_cast<uint4*>(out + p * kC + g8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
 }
 
-// ---- last layer: padded bf16 [P][64] -> fp32 NDHWC with few channels; thread = voxel
+// ---- last layer: padded bf16 [P][64] -> fp32 NDHWC with few channels.  A warp owns 4 voxels at a time; lane l holds
+// input channels 2l and 2l+1, so every tap is one coalesced 128-byte row read per voxel and the lane's 2 x F weights
+// of that tap come from shared memory once for the 4 voxels; the F sums are finished with a shuffle tree.
 template <int F>
-__global__ void __launch_bounds__(128) conv_out_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ wt,   // wt [27][64][F]
+__global__ void __launch_bounds__(256) conv_out_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ wt,   // wt [27][64][F]
                                                        const float* __restrict__ bias, float* __restrict__ y,
                                                        int N, int D, int H, int W, float slope) {
   __shared__ float sw[27 * kC * F];
-  for (int i = threadIdx.x; i < 27 * kC * F; i += 128) sw[i] = wt[i];
+  for (int i = threadIdx.x; i < 27 * kC * F; i += 256) sw[i] = wt[i];
   __syncthreads();
   const long long nvox = (long long)N * D * H * W;
-  const long long v = (long long)blockIdx.x * 128 + threadIdx.x;
-  if (v >= nvox) return;
-  const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
-  float acc[F];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long wstride = (long long)gridDim.x * 8 * 4;
+  for (long long v0 = ((long long)blockIdx.x * 8 + warp) * 4; v0 < nvox; v0 += wstride) {
+    long long prow[4];
 #pragma unroll
-  for (int f = 0; f < F; f++) acc[f] = bias[f];
-  for (int tap = 0; tap < 27; tap++) {
-    const long long p = (((long long)n_ * (D + 2) + d_ + tap / 9) * (H + 2) + h_ + (tap / 3) % 3) * (W + 2) + w_ + tap % 3;
-    const uint4* row = reinterpret_cast<const uint4*>(in + p * kC);
+    for (int i = 0; i < 4; i++) {
+      const long long v = v0 + i < nvox ? v0 + i : nvox - 1;
+      const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
+      prow[i] = (((long long)n_ * (D + 2) + d_) * (H + 2) + h_) * (W + 2) + w_;      // tap (0,0,0) of this voxel
+    }
+    float acc[4][F];
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-      const uint4 q = __ldg(row + j);
-      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&q);
+    for (int i = 0; i < 4; i++)
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const float2 xv = __bfloat1622float2(h2[e]);
-        const float* wp = sw + (tap * kC + 8 * j + 2 * e) * F;
+      for (int f = 0; f < F; f++) acc[i][f] = 0.f;
+    for (int tap = 0; tap < 27; tap++) {
+      const long long toff = ((long long)(tap / 9) * (H + 2) + (tap / 3) % 3) * (W + 2) + tap % 3;
+      float w0[F], w1[F];
 #pragma unroll
-        for (int f = 0; f < F; f++) acc[f] = fmaf(xv.x, wp[f], fmaf(xv.y, wp[F + f], acc[f]));
+      for (int f = 0; f < F; f++) { w0[f] = sw[(tap * kC + 2 * lane) * F + f]; w1[f] = sw[(tap * kC + 2 * lane + 1) * F + f]; }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(in + (prow[i] + toff) * kC + 2 * lane);
+        const float2 xv = __bfloat1622float2(h2);
+#pragma unroll
+        for (int f = 0; f < F; f++) acc[i][f] = fmaf(xv.x, w0[f], fmaf(xv.y, w1[f], acc[i][f]));
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int f = 0; f < F; f++) {
+        float t = acc[i][f];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        acc[i][f] = t;
+      }
+    if (lane < 4 && v0 + lane < nvox) {
+#pragma unroll
+      for (int f = 0; f < F; f++) {
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) if (i == lane) o = acc[i][f];
+        o += bias[f];
+        y[(v0 + lane) * F + f] = fmaxf(o, o * slope);
       }
     }
   }
-#pragma unroll
-  for (int f = 0; f < F; f++) y[v * F + f] = fmaxf(acc[f], acc[f] * slope);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -430,9 +460,9 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   // first layer
   {
     const LayerHost& L = m->meta[0];
-    const long long threads = nvox * 8;
     const size_t smem = (size_t)27 * L.cin * kC * 4;
-    conv_in_kernel<<<(unsigned)((threads + 255) / 256), 256, smem, s>>>(x, m->w_in, m->b_in, m->buf[0], N, D, H, W, L.cin, slope_of(L));
+    const long long blocks = (nvox + 31) / 32;
+    conv_in_kernel<<<(unsigned)(blocks < sms * 4 ? blocks : sms * 4), 256, smem, s>>>(x, m->w_in, m->b_in, m->buf[0], N, D, H, W, L.cin, slope_of(L));
   }
   int cur = 0, skip = (m->meta[0].flags & LFLAG_SAVE_SKIP) ? 0 : -1;
   for (int l = 1; l < nl - 1; l++) {
@@ -453,13 +483,14 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   }
   {
     const LayerHost& L = m->meta[nl - 1];
-    const unsigned grid = (unsigned)((nvox + 127) / 128);
+    const long long blocks = (nvox + 31) / 32;
+    const unsigned grid = (unsigned)(blocks < sms * 4 ? blocks : sms * 4);
     const float sl = slope_of(L);
     switch (L.cout) {
-      case 1: conv_out_kernel<1><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      case 2: conv_out_kernel<2><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      case 3: conv_out_kernel<3><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      default: conv_out_kernel<4><<<grid, 128, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      case 1: conv_out_kernel<1><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      case 2: conv_out_kernel<2><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      case 3: conv_out_kernel<3><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
+      default: conv_out_kernel<4><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
     }
   }
   const cudaError_t e = cudaGetLastError();

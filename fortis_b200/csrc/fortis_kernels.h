@@ -80,6 +80,7 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
 struct ConvModel;
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
 void conv_model_destroy(ConvModel* m);
+int conv_model_status(ConvModel* m);        // 0, or the code of a bounded wait that gave up in the tensor-core conv kernel
 // x (N,D,H,W,Cin) fp32 NDHWC on the device -> y (N,D,H,W,Cout)
 bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 // single layer, NCDHW fp32 (the memref ABI of runtime/fortis_rt.c:128-131)
