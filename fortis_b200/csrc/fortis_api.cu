@@ -143,7 +143,11 @@ struct Session {
 };
 Session* g_S = nullptr;
 Session& S() {
-  if (!g_S) g_S = new Session();
+  if (!g_S) {
+    g_S = new Session();
+    // option environment variables apply however the descriptors and the model arrive
+    if (std::getenv("FORTIS_GRAPH")) g_S->graph = true;                              // driver/fortis_shim.py:84
+  }
   return *g_S;
 }
 
@@ -249,7 +253,6 @@ void load_env_config() {
   }
   if (!s.have_model) { const char* m = std::getenv("FORTIS_MODEL"); if (m && *m) fortis_load_model(m); }
   if (const char* p = std::getenv("FORTIS_PRECISION")) fortis_set_option("precision", p);
-  if (std::getenv("FORTIS_GRAPH")) s.graph = true;                  // driver/fortis_shim.py:84
   if (const char* b = std::getenv("FORTIS_BATCH")) if (s.begin_count < 0) s.begin_count = std::atoll(b);
 }
 

@@ -11,7 +11,8 @@ class FortisError(RuntimeError):
 
 
 def lib_path():
-    return os.path.join(HERE, "libfortis_b200.so")
+    """The in-tree library; FORTIS_B200_LIB names another build of it (A/B comparisons)."""
+    return os.environ.get("FORTIS_B200_LIB") or os.path.join(HERE, "libfortis_b200.so")
 
 
 def load():

@@ -1,9 +1,9 @@
 #!/usr/bin/env python3
 """Generate the golden fixtures under tests/golden/ from the reference checkout.
 
-Run in a container that has the reference at /root/reference (it is NOT needed to run the tests):
+Run where a checkout of the reference (sanatgp/Fortis) is available (it is NOT needed to run the tests):
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [path-to-reference-checkout]
 
 What it does
   1. Copies the reference's checked-in layout descriptors for the MOM6 Zanna-Bolton host (data, not code):
