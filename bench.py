@@ -353,7 +353,7 @@ def main():
         roof["traffic"] = traffic
         roof["kernel_ms"] = kernel_ms
         cpu = None if (args.no_cpu or is_conv or world > 1) else time_cpu(wl)      # the CPU baseline is an N = 1 figure
-        launches_per_step = len(wl["layers"]) if is_conv else 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
+        launches_per_step = (len(wl["layers"]) + (1 if prec != "fp32" else 0)) if is_conv else 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
         line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
                 "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": {"bf16": "bf16", "fp32": "f32", "fp8w": "bf16 (fp8-e4m3 weights)"}[prec],

@@ -1,6 +1,8 @@
-// conv3d 64 -> 64 channels, 3x3x3, stride 1, pad 1 as an implicit GEMM on tcgen05 tensor cores (bf16 operands, fp32
-// accumulation in tensor memory), with bias + residual add + LeakyReLU fused into the epilogue; plus the thin FFMA
-// kernels for the network's first (few channels in) and last (few channels out) layers and the bf16 network driver.
+// conv3d 3x3x3, stride 1, pad 1 as an implicit GEMM on tcgen05 tensor cores (bf16 operands, fp32 accumulation in
+// tensor memory), with bias + residual add + LeakyReLU fused into the epilogue, and the bf16 network driver.  Three
+// instantiations of one kernel: 64 -> 64 channels (the body of the network), few -> 64 (first layer: only the first
+// 16-wide k step of every tap is issued) and 64 -> few (last layer: N = 16 MMAs, fp32 NDHWC output straight from the
+// accumulator).
 //
 // Replaces fortis_conv3d -> cudnnConvolutionForward and the separate bias / activation / residual kernels the
 // reference chains behind it (runtime/fortis_rt.c:128-156, compiler/FortisFuse.cpp:626-655, 687-760).
@@ -20,6 +22,11 @@
 // (activation tile + the three weight tiles, 128-byte swizzle); two accumulators so that the epilogue of a tile
 // overlaps the MMAs of the next.  Warp 0: TMA, warp 1: MMA, warps 2-5:
 // epilogue (thread = one voxel row, 64 channels).
+//
+// First layer: the fp32 NDHWC input is packed into its own padded bf16 volume with channels >= Cin zero, and the
+// weights are padded the same way, so the layer is the same shifted-tile GEMM with one k step per tap instead of
+// four.  Last layer: the weights are padded to 16 output channels; the epilogue adds the bias, applies the
+// activation and writes the real channels of interior voxels as fp32.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -49,22 +56,30 @@ constexpr int kStage = kStageA + kStageW;    // 41 KB
 constexpr int kStagesC = 5;
 constexpr int kConvThreads = 192;
 constexpr int kConvSmem = kStagesC * kStage + 256;
-constexpr uint32_t kConvIdesc = idesc_bf16(kTile, kC);
+template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(kTile, NOUT); };
+constexpr int kEdgeC = 16;                   // first layer: input channels kept; last layer: output channels computed
 enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_ALIGN = 16 };
 
 struct ConvTcParams {
   CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 130
   CUtensorMap wmap;            // weights [27 * 64 (tap, cout)][64 cin] bf16, box 64 x 192
-  const float* bias;           // [64]
+  const float* bias;           // [64] (zero beyond the layer's real outputs)
   const __nv_bfloat16* skip;   // [P][64] or null
   __nv_bfloat16* out;          // [P][64]
+  float* y;                    // last layer: fp32 [N*D*H*W][F]
+  int F;                       // last layer: real output channels (<= 16)
   int D, H, W;                 // unpadded extent
   long long P;                 // padded rows
   float slope;                 // act(v) = max(v, v * slope)
   int* status;
 };
 
+// KSTEPS: 16-wide k steps issued per tap (4 = all 64 input channels, 1 = only the first 16);  NOUT: output channels
+// of the MMA (weight rows staged per tap);  LAST: write fp32 NDHWC instead of the padded bf16 volume
+template <int KSTEPS, int NOUT, bool LAST>
 __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid_constant__ ConvTcParams P) {
+  constexpr uint32_t kIdescN = ConvIdesc<NOUT>::value;
+  constexpr int kBytesW = 3 * NOUT * kC * 2;                      // the three kw weight tiles of one (kd, kh)
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);
   if (base & 1023u) {
@@ -106,10 +121,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
         const int kd = g / 3, kh = g % 3;
         const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp - 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
-        mbar_expect_tx(bar_full + 8 * s, kBytesA + kStageW);
+        mbar_expect_tx(bar_full + 8 * s, kBytesA + kBytesW);
         const uint32_t dst = base + s * kStage;
         tma_load_2d(dst, &P.amap, 0, (int)(p0 + shift), bar_full + 8 * s);
-        tma_load_2d(dst + kStageA, &P.wmap, 0, g * 3 * kC, bar_full + 8 * s);
+        tma_load_2d(dst + kStageA, &P.wmap, 0, g * 3 * NOUT, bar_full + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
       }
     }
@@ -134,10 +149,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
           // swizzle is a function of the shared-memory address itself, so the shifted view stays consistent with
           // what TMA wrote
           const uint64_t adk = ad + (uint64_t)(kw * 8);
-          const uint64_t bdk = bd + (uint64_t)(kw * (kC * kC * 2 >> 4));
+          const uint64_t bdk = bd + (uint64_t)(kw * (NOUT * kC * 2 >> 4));
 #pragma unroll
-          for (int j = 0; j < kC / 16; j++)
-            tc_mma_ss<kConvIdesc>(d_tmem, adk + (uint64_t)(j * 2), bdk + (uint64_t)(j * 2), (uint32_t)(g | kw | j));
+          for (int j = 0; j < KSTEPS; j++)
+            tc_mma_ss<kIdescN>(d_tmem, adk + (uint64_t)(j * 2), bdk + (uint64_t)(j * 2), (uint32_t)(g | kw | j));
         }
         tc_commit(bar_empty + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
@@ -166,13 +181,29 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       }
       // residual row, fetched while the MMAs of this tile are still running
       uint4 sk[8];
-      const bool use_skip = P.skip != nullptr && interior;
+      const bool use_skip = !LAST && P.skip != nullptr && interior;
       if (use_skip) {
 #pragma unroll
         for (int j = 0; j < 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + p * kC) + j);
       }
       mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL);
       tc_fence_after();
+      if (LAST) {
+        uint32_t a[32];                                            // columns >= NOUT are not part of this layer
+        tmem_ld32(lane_addr + b * kC, a);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(bar_acc_empty + 8 * b);
+        if (interior) {
+          const long long n_ = p / ((long long)Wp * Hp * Dp);
+          const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), dp = (int)((p / ((long long)Wp * Hp)) % Dp);
+          float* dst = P.y + ((((n_ * P.D + dp - 1) * P.H + hp - 1) * P.W) + wp - 1) * P.F;
+#pragma unroll
+          for (int f = 0; f < NOUT; f++)
+            if (f < P.F) { const float v = __uint_as_float(a[f]) + bias[f]; dst[f] = fmaxf(v, v * P.slope); }
+        }
+        continue;
+      }
       uint32_t a0[32], a1[32];
       tmem_ld32(lane_addr + b * kC, a0);
       tmem_ld32(lane_addr + b * kC + 32, a1);
@@ -220,102 +251,24 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
   }
 }
 
-// ---- first layer: fp32 NDHWC input with few channels -> padded bf16 [P][64]; thread = (voxel, 8 output channels).
-// Persistent blocks: the 27 * C * 64 weights are staged in shared memory once per block, not once per 32 voxels.
-__global__ void __launch_bounds__(256) conv_in_kernel(const float* __restrict__ x, const float* __restrict__ wt,   // wt [27][C][64]
-                                                      const float* __restrict__ bias, __nv_bfloat16* __restrict__ out,
-                                                      int N, int D, int H, int W, int C, float slope) {
-  extern __shared__ float sw[];                               // 27 * C * 64 weights
-  for (int i = threadIdx.x; i < 27 * C * kC; i += 256) sw[i] = wt[i];
-  __syncthreads();
+// ---- network input: fp32 NDHWC with C <= 16 channels -> the first 16 channels (32 bytes) of the padded bf16 rows; the
+// border rows and the channels beyond 16 of this buffer are never written (zero from allocation; the first layer's
+// MMAs read only the first 16 channels)
+__global__ void __launch_bounds__(256) conv_pack_input_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                              int N, int D, int H, int W, int C) {
   const long long nvox = (long long)N * D * H * W;
-  const int g8 = (threadIdx.x & 7) * 8;
-  float b8[8];
-#pragma unroll
-  for (int e = 0; e < 8; e++) b8[e] = bias[g8 + e];
-  for (long long v = (long long)blockIdx.x * 32 + (threadIdx.x >> 3); v < nvox; v += (long long)gridDim.x * 32) {
+  for (long long v = (long long)blockIdx.x * 256 + threadIdx.x; v < nvox; v += (long long)gridDim.x * 256) {
     const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
-    float acc[8];
-#pragma unroll
-    for (int e = 0; e < 8; e++) acc[e] = b8[e];
-    for (int tap = 0; tap < 27; tap++) {
-      const int id = d_ + tap / 9 - 1, ih = h_ + (tap / 3) % 3 - 1, iw = w_ + tap % 3 - 1;
-      if (id < 0 || id >= D || ih < 0 || ih >= H || iw < 0 || iw >= W) continue;
-      const float* xp = x + ((((long long)n_ * D + id) * H + ih) * W + iw) * C;
-      for (int c = 0; c < C; c++) {
-        const float xv = __ldg(xp + c);
-        const float4 w0 = *reinterpret_cast<const float4*>(sw + (tap * C + c) * kC + g8);
-        const float4 w1 = *reinterpret_cast<const float4*>(sw + (tap * C + c) * kC + g8 + 4);
-        acc[0] = fmaf(xv, w0.x, acc[0]); acc[1] = fmaf(xv, w0.y, acc[1]); acc[2] = fmaf(xv, w0.z, acc[2]); acc[3] = fmaf(xv, w0.w, acc[3]);
-        acc[4] = fmaf(xv, w1.x, acc[4]); acc[5] = fmaf(xv, w1.y, acc[5]); acc[6] = fmaf(xv, w1.z, acc[6]); acc[7] = fmaf(xv, w1.w, acc[7]);
-      }
-    }
     const long long p = (((long long)n_ * (D + 2) + d_ + 1) * (H + 2) + h_ + 1) * (W + 2) + w_ + 1;
-    uint32_t pk[4];
+    float f[16];
 #pragma unroll
-    for (int e = 0; e < 4; e++) pk[e] = pack_bf16(fmaxf(acc[2 * e], acc[2 * e] * slope), fmaxf(acc[2 * e + 1], acc[2 * e + 1] * slope));
-    *reinterpret_cast<uint4*>(out + p * kC + g8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-  }
-}
-
-// ---- last layer: padded bf16 [P][64] -> fp32 NDHWC with few channels.  A warp owns 4 voxels at a time; lane l holds
-// input channels 2l and 2l+1, so every tap is one coalesced 128-byte row read per voxel and the lane's 2 x F weights
-// of that tap come from shared memory once for the 4 voxels; the F sums are finished with a shuffle tree.
-template <int F>
-__global__ void __launch_bounds__(256) conv_out_kernel(const __nv_bfloat16* __restrict__ in, const float* __restrict__ wt,   // wt [27][64][F]
-                                                       const float* __restrict__ bias, float* __restrict__ y,
-                                                       int N, int D, int H, int W, float slope) {
-  __shared__ float sw[27 * kC * F];
-  for (int i = threadIdx.x; i < 27 * kC * F; i += 256) sw[i] = wt[i];
-  __syncthreads();
-  const long long nvox = (long long)N * D * H * W;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long wstride = (long long)gridDim.x * 8 * 4;
-  for (long long v0 = ((long long)blockIdx.x * 8 + warp) * 4; v0 < nvox; v0 += wstride) {
-    long long prow[4];
+    for (int c = 0; c < 16; c++) f[c] = c < C ? __ldg(x + v * C + c) : 0.f;
+    uint32_t pk[8];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const long long v = v0 + i < nvox ? v0 + i : nvox - 1;
-      const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
-      prow[i] = (((long long)n_ * (D + 2) + d_) * (H + 2) + h_) * (W + 2) + w_;      // tap (0,0,0) of this voxel
-    }
-    float acc[4][F];
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-#pragma unroll
-      for (int f = 0; f < F; f++) acc[i][f] = 0.f;
-    for (int tap = 0; tap < 27; tap++) {
-      const long long toff = ((long long)(tap / 9) * (H + 2) + (tap / 3) % 3) * (W + 2) + tap % 3;
-      float w0[F], w1[F];
-#pragma unroll
-      for (int f = 0; f < F; f++) { w0[f] = sw[(tap * kC + 2 * lane) * F + f]; w1[f] = sw[(tap * kC + 2 * lane + 1) * F + f]; }
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(in + (prow[i] + toff) * kC + 2 * lane);
-        const float2 xv = __bfloat1622float2(h2);
-#pragma unroll
-        for (int f = 0; f < F; f++) acc[i][f] = fmaf(xv.x, w0[f], fmaf(xv.y, w1[f], acc[i][f]));
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-#pragma unroll
-      for (int f = 0; f < F; f++) {
-        float t = acc[i][f];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-        acc[i][f] = t;
-      }
-    if (lane < 4 && v0 + lane < nvox) {
-#pragma unroll
-      for (int f = 0; f < F; f++) {
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) if (i == lane) o = acc[i][f];
-        o += bias[f];
-        y[(v0 + lane) * F + f] = fmaxf(o, o * slope);
-      }
-    }
+    for (int e = 0; e < 8; e++) pk[e] = pack_bf16(f[2 * e], f[2 * e + 1]);
+    uint4* dst = reinterpret_cast<uint4*>(out + p * kC);
+    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
   }
 }
 
@@ -357,12 +310,10 @@ float slope_of(const LayerHost& L) { return L.act == ACT_NONE ? 1.f : L.act == A
 
 struct ConvTcModel {
   std::vector<LayerHost> meta;
-  float* w_in = nullptr; float* b_in = nullptr;            // first layer, fp32 [27][C][64]
-  float* w_out = nullptr; float* b_out = nullptr;          // last layer, fp32 [27][64][F]
-  std::vector<void*> w_mid; std::vector<float*> b_mid;     // 64 -> 64 layers: bf16 [27*64][64]
+  std::vector<void*> w; std::vector<float*> b;             // per layer: bf16 [27 * rows][64] (rows = 64, last layer 16), fp32 bias [64]
   std::vector<CUtensorMap> wmaps;
-  __nv_bfloat16* buf[3] = {nullptr, nullptr, nullptr};
-  CUtensorMap amaps[3];
+  __nv_bfloat16* buf[4] = {nullptr, nullptr, nullptr, nullptr};   // three rotating activation volumes + the packed input
+  CUtensorMap amaps[4];
   long long P = 0;
   int shape[4] = {0, 0, 0, 0};
   int* status = nullptr;
@@ -376,9 +327,9 @@ bool conv_tc_supported(const ModelHost& M, std::string* why) {
     const LayerHost& L = M.layers[l];
     if (L.kind != LAYER_CONV3D || L.ksize != 3 || L.pad != 1) return no("only 3x3x3 pad-1 convolutions");
     if (L.act == ACT_LEAKY && !(L.slope >= 0.f && L.slope <= 1.f)) return no("LeakyReLU slope outside [0, 1]");
-    if (l == 0 && (L.cout != kC || L.cin > 6 || (L.flags & LFLAG_ADD_SKIP))) return no("first layer must be 1..6 channels -> 64");
-    if (l == nl - 1 && (L.cin != kC || (L.cout != 1 && L.cout != 2 && L.cout != 3 && L.cout != 4) || (L.flags & (LFLAG_ADD_SKIP | LFLAG_SAVE_SKIP))))
-      return no("last layer must be 64 -> 1..4 channels");
+    if (l == 0 && (L.cout != kC || L.cin < 1 || L.cin > kEdgeC || (L.flags & LFLAG_ADD_SKIP))) return no("first layer must be 1..16 channels -> 64");
+    if (l == nl - 1 && (L.cin != kC || L.cout < 1 || L.cout > kEdgeC || (L.flags & (LFLAG_ADD_SKIP | LFLAG_SAVE_SKIP))))
+      return no("last layer must be 64 -> 1..16 channels");
     if (l > 0 && l < nl - 1 && (L.cin != kC || L.cout != kC)) return no("middle layers must be 64 -> 64");
   }
   return true;
@@ -386,9 +337,8 @@ bool conv_tc_supported(const ModelHost& M, std::string* why) {
 
 void conv_tc_destroy(ConvTcModel* m) {
   if (!m) return;
-  cudaFree(m->w_in); cudaFree(m->b_in); cudaFree(m->w_out); cudaFree(m->b_out);
-  for (void* p : m->w_mid) cudaFree(p);
-  for (float* p : m->b_mid) cudaFree(p);
+  for (void* p : m->w) cudaFree(p);
+  for (float* p : m->b) cudaFree(p);
   for (auto& p : m->buf) cudaFree(p);
   cudaFree(m->status);
   delete m;
@@ -410,32 +360,27 @@ ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
     const LayerHost& L = M.layers[l];
     LayerHost meta = L; meta.W.clear(); meta.b.clear();
     m->meta.push_back(meta);
-    if (l == 0 || l == nl - 1) {
-      std::vector<float> wt((size_t)27 * L.cin * L.cout);          // [tap][cin][cout]
-      for (int f = 0; f < L.cout; f++)
-        for (int c = 0; c < L.cin; c++)
-          for (int t = 0; t < 27; t++) wt[((size_t)t * L.cin + c) * L.cout + f] = L.W[((size_t)f * L.cin + c) * 27 + t];
-      float* dw = (float*)upload(wt.data(), wt.size() * 4);
-      float* db = (float*)upload(L.b.data(), L.b.size() * 4);
-      if (!dw || !db) return fail("out of device memory for conv weights");
-      if (l == 0) { m->w_in = dw; m->b_in = db; } else { m->w_out = dw; m->b_out = db; }
-    } else {
-      std::vector<uint16_t> wb((size_t)27 * kC * kC);              // [tap][cout][cin], cin contiguous (K-major B operand)
-      for (int f = 0; f < kC; f++)
-        for (int c = 0; c < kC; c++)
-          for (int t = 0; t < 27; t++) wb[((size_t)t * kC + f) * kC + c] = to_bf16(L.W[((size_t)f * kC + c) * 27 + t]);
-      void* dw = upload(wb.data(), wb.size() * 2);
-      float* db = (float*)upload(L.b.data(), L.b.size() * 4);
-      if (!dw || !db) return fail("out of device memory for conv weights");
-      m->w_mid.push_back(dw); m->b_mid.push_back(db);
-      CUtensorMap map;
-      if (!make_map(&map, dw, 27 * kC, 3 * kC)) return fail("cuTensorMapEncodeTiled failed for conv weights");
-      m->wmaps.push_back(map);
-    }
+    // [tap][cout][cin] with cin contiguous (K-major B operand), zero where the layer has no channel
+    const int rows = l == nl - 1 ? kEdgeC : kC;
+    std::vector<uint16_t> wb((size_t)27 * rows * kC, 0);
+    for (int f = 0; f < L.cout; f++)
+      for (int c = 0; c < L.cin; c++)
+        for (int t = 0; t < 27; t++) wb[((size_t)t * rows + f) * kC + c] = to_bf16(L.W[((size_t)f * L.cin + c) * 27 + t]);
+    std::vector<float> bias(kC, 0.f);
+    for (int f = 0; f < L.cout; f++) bias[f] = L.b[f];
+    void* dw = upload(wb.data(), wb.size() * 2);
+    float* db = (float*)upload(bias.data(), bias.size() * 4);
+    if (!dw || !db) return fail("out of device memory for conv weights");
+    m->w.push_back(dw); m->b.push_back(db);
+    CUtensorMap map;
+    if (!make_map(&map, dw, 27 * rows, 3 * rows)) return fail("cuTensorMapEncodeTiled failed for conv weights");
+    m->wmaps.push_back(map);
   }
   if (cudaMalloc(&m->status, sizeof(int)) != cudaSuccess) return fail("out of device memory");
   cudaMemset(m->status, 0, sizeof(int));
-  if (cudaFuncSetAttribute(conv3d_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess)
+  if (cudaFuncSetAttribute(conv3d_tc_kernel<4, kC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<1, kC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<4, kEdgeC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess)
     return fail("cannot reserve shared memory for the tensor-core conv kernel");
   return m;
 }
@@ -447,7 +392,7 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   if (P >= (1LL << 31) - 4096) { if (err) *err = "conv3d model: volume too large for 32-bit TMA row coordinates"; return false; }
   if (m->P != P || m->shape[0] != N || m->shape[1] != D || m->shape[2] != H || m->shape[3] != W) {
     for (auto& p : m->buf) { cudaFree(p); p = nullptr; }
-    for (int b = 0; b < 3; b++) {
+    for (int b = 0; b < 4; b++) {
       if (cudaMalloc(&m->buf[b], (size_t)P * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
       cudaMemsetAsync(m->buf[b], 0, (size_t)P * kC * 2, s);        // the border must be zero before the first layer writes the interior
       if (!make_map(&m->amaps[b], m->buf[b], P, kRowsA)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
@@ -457,41 +402,29 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   const int nl = (int)m->meta.size();
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // first layer
   {
-    const LayerHost& L = m->meta[0];
-    const size_t smem = (size_t)27 * L.cin * kC * 4;
-    const long long blocks = (nvox + 31) / 32;
-    conv_in_kernel<<<(unsigned)(blocks < sms * 4 ? blocks : sms * 4), 256, smem, s>>>(x, m->w_in, m->b_in, m->buf[0], N, D, H, W, L.cin, slope_of(L));
+    const long long blocks = (nvox + 255) / 256;
+    conv_pack_input_kernel<<<(unsigned)(blocks < sms * 8 ? blocks : sms * 8), 256, 0, s>>>(x, m->buf[3], N, D, H, W, m->meta[0].cin);
   }
-  int cur = 0, skip = (m->meta[0].flags & LFLAG_SAVE_SKIP) ? 0 : -1;
-  for (int l = 1; l < nl - 1; l++) {
+  const long long ntiles = (P + kTile - 1) / kTile;
+  const int grid = (int)(ntiles < sms ? ntiles : sms);
+  int cur = 3, skip = -1;
+  for (int l = 0; l < nl; l++) {
     const LayerHost& L = m->meta[l];
     int dst = -1;
     for (int b = 0; b < 3; b++) if (b != cur && b != skip) { dst = b; break; }
     if ((L.flags & LFLAG_ADD_SKIP) && skip < 0) { if (err) *err = "conv3d model: a layer adds a skip that was never saved"; return false; }
     ConvTcParams P_;
     std::memset(&P_, 0, sizeof P_);
-    P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l - 1]; P_.bias = m->b_mid[l - 1];
+    P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l]; P_.bias = m->b[l];
     P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] : nullptr;
-    P_.out = m->buf[dst]; P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status;
-    const long long ntiles = (P + kTile - 1) / kTile;
-    const int grid = (int)(ntiles < sms ? ntiles : sms);
-    conv3d_tc_kernel<<<grid, kConvThreads, kConvSmem, s>>>(P_);
+    P_.out = m->buf[dst]; P_.y = y; P_.F = L.cout;
+    P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status;
+    if (l == nl - 1) conv3d_tc_kernel<4, kEdgeC, true><<<grid, kConvThreads, kConvSmem, s>>>(P_);
+    else if (l == 0) conv3d_tc_kernel<1, kC, false><<<grid, kConvThreads, kConvSmem, s>>>(P_);
+    else conv3d_tc_kernel<4, kC, false><<<grid, kConvThreads, kConvSmem, s>>>(P_);
     if (L.flags & LFLAG_SAVE_SKIP) skip = dst;
     cur = dst;
-  }
-  {
-    const LayerHost& L = m->meta[nl - 1];
-    const long long blocks = (nvox + 31) / 32;
-    const unsigned grid = (unsigned)(blocks < sms * 4 ? blocks : sms * 4);
-    const float sl = slope_of(L);
-    switch (L.cout) {
-      case 1: conv_out_kernel<1><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      case 2: conv_out_kernel<2><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      case 3: conv_out_kernel<3><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-      default: conv_out_kernel<4><<<grid, 256, 0, s>>>(m->buf[cur], m->w_out, m->b_out, y, N, D, H, W, sl); break;
-    }
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(e); return false; }

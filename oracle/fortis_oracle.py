@@ -517,17 +517,14 @@ def convnet_forward(layers: Sequence[Dict], x: np.ndarray, dtype=np.float32) -> 
 
 
 def convnet_forward_lowp(layers: Sequence[Dict], x: np.ndarray) -> np.ndarray:
-    """Model of the bf16 tensor-core conv network: the first layer (few channels in) and the last (few channels
-    out) are computed in fp32 with fp32 weights; the 64->64 layers take bf16 activations and bf16 weights with wide
-    accumulation; every intermediate activation (including the remembered skip) is stored as bf16."""
+    """Model of the bf16 tensor-core conv network: the input and every layer's weights are rounded to bf16, products
+    are accumulated wide, bias / skip / activation are applied in fp32, and every intermediate activation (including
+    the remembered skip) is stored as bf16; the last layer's output stays fp32."""
     n = len(layers)
-    h = np.asarray(x, dtype=np.float32)
+    h = round_bf16(np.asarray(x, dtype=np.float32))
     skip = None
     for l, L in enumerate(layers):
-        if l == 0 or l == n - 1:
-            y = conv3d_ndhwc(h.astype(np.float64), np.asarray(L["W"], np.float64), None, L.get("pad", 1), np.float64)
-        else:
-            y = conv3d_ndhwc(h.astype(np.float64), round_bf16(L["W"]).astype(np.float64), None, L.get("pad", 1), np.float64)
+        y = conv3d_ndhwc(h.astype(np.float64), round_bf16(L["W"]).astype(np.float64), None, L.get("pad", 1), np.float64)
         y = y.astype(np.float32) + np.asarray(L["b"], np.float32)
         if L.get("add"):
             y = y + skip
