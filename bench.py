@@ -44,6 +44,7 @@ def parse():
     ap.add_argument("--ncol", type=int, default=0, help="override the per-rank column count (column workloads)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-incumbent", action="store_true")
     return ap.parse_args()
 
 
@@ -234,6 +235,51 @@ def run_reference(args):
 # -----------------------------------------------------------------------------------------------------------------
 # GPU arm
 # -----------------------------------------------------------------------------------------------------------------
+# the library path the reference's runtime takes on a GPU, for comparison (column workloads): materialise X with a
+# gather, one cuBLAS SGEMM per layer with a separate bias / activation pass, scatter Y (runtime/fortis_rt.c:87-100,
+# compiler/FortisFuse.cpp:587-655).  torch's fp32 matmul with TF32 off is that SGEMM.  Reported beside the result;
+# never part of `value`.
+# -----------------------------------------------------------------------------------------------------------------
+def time_incumbent(torch, wl, d_in, d_out, flush, steps=10):
+    torch.backends.cuda.matmul.allow_tf32 = False
+    ncol = wl["units"]
+    W = [torch.from_numpy(L["W"]).cuda() for L in wl["layers"]]
+    B = [torch.from_numpy(L["b"]).cuda() for L in wl["layers"]]
+    views_in = [a.view(-1, ncol).t() for a in d_in]                # Fortran (ncol, nlev) -> (ncol, nlev) strided views
+    outs = [a.view(-1, ncol).t() for a in d_out]
+
+    def step():
+        x = torch.cat(views_in, dim=1).contiguous()                # the gather kernel's X
+        for l, L in enumerate(wl["layers"]):
+            x = torch.addmm(B[l], x, W[l].t())
+            if L["act"] == "leaky":
+                x = torch.nn.functional.leaky_relu(x, L["slope"])
+            elif L["act"] == "relu":
+                x = torch.relu(x)
+        o = 0
+        for v in outs:                                             # the scatter kernel
+            v.copy_(x[:, o:o + v.shape[1]])
+            o += v.shape[1]
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    ms = []
+    for _ in range(steps):
+        flush.fill_(1)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        step()
+        e.record()
+        torch.cuda.synchronize()
+        ms.append(s.elapsed_time(e))
+    med = float(np.median(ms))
+    return {"value": ncol / (med * 1e-3), "unit": "columns/s", "ms_per_step": med,
+            "what": "torch fp32: gather (cat) -> cuBLAS SGEMM + bias + activation per layer -> scatter (copy); library kernels, comparison only"}
+
+
+# -----------------------------------------------------------------------------------------------------------------
 def main():
     args = parse()
     if args.impl == "reference":
@@ -324,6 +370,9 @@ def main():
         e_total, _ = timed(e_fn, e_steps, 3)
         e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
                "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
+    incumbent = None
+    if wl["kind"] == "column" and world == 1 and not args.no_incumbent and wl["units"] <= 1 << 18:
+        incumbent = time_incumbent(torch, wl, d_in, d_out, flush)
     cs_global = cs_local
     if dist is not None:
         t = torch.tensor([cs_local], dtype=torch.float64, device="cuda")
@@ -361,7 +410,7 @@ def main():
                 "config": {"workload": wl["label"], "columns_per_gpu": wl["units"], "precision": prec, "l2": "flushed between timed steps (256 MB write)",
                            "parallelism": "contiguous column block per rank, no data-path collective"},
                 "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "roofline": roof, "cpu_baseline": cpu,
-                "clocks": clocks, "checksum": cs_global}
+                "incumbent_gpu_library_path": incumbent, "clocks": clocks, "checksum": cs_global}
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -47,22 +48,22 @@ using namespace tc;
 namespace {
 
 constexpr int kC = 64;                       // channels of the tensor-core layers
-constexpr int kTile = 128;                   // output rows per tile
-constexpr int kRowsA = kTile + 2;            // the three kw taps of one (kd, kh) read rows p0-1 .. p0+128 of the same tile
-constexpr int kBytesA = kRowsA * kC * 2;     // 16,640 B landed by TMA
-constexpr int kStageA = 17 * 1024;           // region reserved for it (1024-byte multiple keeps the weights aligned)
-constexpr int kStageW = 3 * kC * kC * 2;     // 24 KB: the three kw weight tiles, consecutive rows of the weight matrix
-constexpr int kStage = kStageA + kStageW;    // 41 KB
-constexpr int kStagesC = 5;
+constexpr int kTile = 128;                   // rows computed per tile (the MMA's M)
+constexpr int kWarpOut = 30;                 // rows written per epilogue warp: its first and last computed rows only feed their neighbours
+constexpr int kTileOut = 4 * kWarpOut;       // rows written per tile; a tile is four 32-row boxes whose rows overlap by two
+constexpr int kStageA = kTile * kC * 2;      // 16 KB: one activation tile (a ring stage)
+constexpr int kResW = 9 * 96 * kC * 2;       // 108 KB: this CTA's half of all 27 weight tiles, resident for the whole kernel
+constexpr int kStagesC = 7;
 constexpr int kConvThreads = 192;
-constexpr int kConvSmem = kStagesC * kStage + 256;
-template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(kTile, NOUT); };
+constexpr int kConvSmem = kResW + kStagesC * kStageA + 256;
+constexpr int kAccStride = 256;              // TMEM columns between the two accumulators (each 3 * NOUT wide)
+template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT); };   // the pair's M = 256
 constexpr int kEdgeC = 16;                   // first layer: input channels kept; last layer: output channels computed
-enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_ALIGN = 16 };
+enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_WEIGHTS = 15, CST_ALIGN = 16 };
 
 struct ConvTcParams {
-  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 130
-  CUtensorMap wmap;            // weights [27 * 64 (tap, cout)][64 cin] bf16, box 64 x 192
+  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 32
+  CUtensorMap wmap;            // weights [27 * NOUT (tap, cout)][64 cin] bf16, box 64 x 3 NOUT
   const float* bias;           // [64] (zero beyond the layer's real outputs)
   const __nv_bfloat16* skip;   // [P][64] or null
   __nv_bfloat16* out;          // [P][64]
@@ -72,172 +73,227 @@ struct ConvTcParams {
   long long P;                 // padded rows
   float slope;                 // act(v) = max(v, v * slope)
   int* status;
+  long long* prof;             // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
 };
 
-// KSTEPS: 16-wide k steps issued per tap (4 = all 64 input channels, 1 = only the first 16);  NOUT: output channels
-// of the MMA (weight rows staged per tap);  LAST: write fp32 NDHWC instead of the padded bf16 volume
+// cycle accounting for diagnostics: adds the time since *t to prof[slot] (CTA 0, one lane) and restarts the clock
+__device__ __forceinline__ void cprof_add(long long* prof, int slot, long long* t, bool who) {
+  if (prof && who) { const long long n = clock64(); atomicAdd((unsigned long long*)&prof[slot], (unsigned long long)(n - *t)); *t = n; }
+}
+
+// KSTEPS: 16-wide k steps issued per (kd, kh) group (4 = all 64 input channels, 1 = only the first 16);  NOUT: output
+// channels (weight rows per tap);  LAST: write fp32 NDHWC instead of the padded bf16 volume.
+// Launched as clusters of two CTAs (cta_group::2): the leader's MMA warp issues for both.
 template <int KSTEPS, int NOUT, bool LAST>
 __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid_constant__ ConvTcParams P) {
-  constexpr uint32_t kIdescN = ConvIdesc<NOUT>::value;
-  constexpr int kBytesW = 3 * NOUT * kC * 2;                      // the three kw weight tiles of one (kd, kh)
+  constexpr uint32_t kIdescN = ConvIdesc<NOUT>::value;            // M = 256 (128 rows per CTA), N = 3 * NOUT
+  constexpr int kHalfRows = 3 * NOUT / 2;                         // weight rows of one (kd, kh) group held by each CTA
+  constexpr int kHalfBytes = kHalfRows * kC * 2;                  // 12 KB (3 KB for the last layer)
   extern __shared__ __align__(1024) uint8_t smem[];
-  const uint32_t base = smem_u32(smem);
-  if (base & 1023u) {
+  const uint32_t base = smem_u32(smem);                           // resident weights at offset 0
+  if (base & 1023u) {                                             // same in both CTAs of a pair: both leave
     if (threadIdx.x == 0) atomicCAS(P.status, 0, CST_ALIGN);
     return;
   }
-  const uint32_t bars = base + kStagesC * kStage;
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStagesC, bar_acc_full = bars + 16 * kStagesC, bar_acc_empty = bar_acc_full + 16;
-  uint32_t* tmem_slot = (uint32_t*)(smem + kStagesC * kStage + 16 * kStagesC + 32);
-  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  const uint32_t ring = base + kResW;
+  const uint32_t bars = ring + kStagesC * kStageA;
+  // barrier block (256 B): full [0,56) empty [56,112) acc_full [112,128) acc_empty [128,144) weights [144,152)
+  // tmem base 160, abort flag 164
+  const uint32_t bar_full = bars, bar_empty = bars + 56, bar_acc_full = bars + 112, bar_acc_empty = bars + 128, bar_w = bars + 144;
+  uint8_t* barp = smem + kResW + kStagesC * kStageA;
+  uint32_t* tmem_slot = (uint32_t*)(barp + 160);
+  volatile int* abort_flag = (volatile int*)(barp + 164);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long ntiles = (P.P + kTile - 1) / kTile;
+  const uint32_t crank = cluster_ctarank();
+  const long long ntiles = (P.P + kTileOut - 1) / kTileOut;
+  const long long npairs = (ntiles + 1) / 2;                       // a pair works on tiles 2 t and 2 t + 1
+  const long long pair0 = blockIdx.x >> 1, pair_step = gridDim.x >> 1;
   const int Wp = P.W + 2, Hp = P.H + 2, Dp = P.D + 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesC; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128); }
+    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 8); }   // 4 epilogue warps per CTA
+    mbar_init(bar_w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0 && lane < 2)
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(lane ? &P.wmap : &P.amap)) : "memory");
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(128u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();                      // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
-    // ---- TMA producer: per tile 27 stages, each the shifted activation tile and that tap's weight tile
+    // ---- TMA producer (one per CTA): this CTA's half of the weights once, then per tile 9 activation tiles.
+    //      Completion of both CTAs' copies is counted on the LEADER's barriers, which the leader arms for both.
+    const uint32_t full0 = map_to_cta(bar_full, 0), w0 = map_to_cta(bar_w, 0);
+    if (crank == 0) mbar_expect_tx(bar_w, 2 * 9 * kHalfBytes);
+#pragma unroll 1
+    for (int g = 0; g < 9; g++)
+      tma_load_2d_pair(base + g * kHalfBytes, &P.wmap, 0, g * 3 * NOUT + (int)crank * kHalfRows, w0);
     uint32_t s = 0, ph = 0;
     bool stop = false;
-    for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x) {
-      const long long p0 = tile * kTile;
-      for (int g = 0; g < 9; g++) {                               // (kd, kh) groups: one activation tile serves kw = 0, 1, 2
+    const bool pw = blockIdx.x == 0 && lane == 0;
+    long long pt = clock64();
+    for (long long tp = pair0; tp < npairs && !stop; tp += pair_step) {
+      const long long q0 = (2 * tp + crank) * kTileOut - 1;       // first computed row of this CTA's tile (warp w: q0 + 30 w ...)
+      for (int g = 0; g < 9; g++) {
         const int kd = g / 3, kh = g % 3;
-        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp - 1;
+        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp;
+        cprof_add(P.prof, 7, &pt, pw);
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
-        mbar_expect_tx(bar_full + 8 * s, kBytesA + kBytesW);
-        const uint32_t dst = base + s * kStage;
-        tma_load_2d(dst, &P.amap, 0, (int)(p0 + shift), bar_full + 8 * s);
-        tma_load_2d(dst + kStageA, &P.wmap, 0, g * 3 * NOUT, bar_full + 8 * s);
+        cprof_add(P.prof, 6, &pt, pw);
+        if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kStageA);
+#pragma unroll
+        for (int w = 0; w < 4; w++)                                // 32 rows per epilogue warp
+          tma_load_2d_pair(ring + s * kStageA + w * (kStageA / 4), &P.amap, 0, (int)(q0 + shift + kWarpOut * w), full0 + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer
-    uint32_t s = 0, ph = 0, acc_it = 0;
-    const uint64_t desc_hi = make_kmajor_sw128_desc(0) & 0xFFFFFFFF00000000ull;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, acc_it++) {
-      const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-      mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY);
-      tc_fence_after();
-      const uint32_t d_tmem = tmem + b * kC;
-      for (int g = 0; g < 9; g++) {
-        mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
+    if (crank == 0) {
+      // ---- MMA issuer (leader only): per (kd, kh) group KSTEPS MMAs of M = 256, N = 3 * NOUT; accumulator column
+      //      block kw holds sum over groups of X[row + shift(kd, kh)] . W(kd, kh, kw), still to be shifted by kw - 1 rows
+      uint32_t s = 0, ph = 0, acc_it = 0;
+      const uint64_t desc_hi = make_kmajor_sw128_desc(0) & 0xFFFFFFFF00000000ull;
+      const bool pw = blockIdx.x == 0 && lane == 0;
+      long long pt = clock64();
+      mbar_wait(bar_w, 0, abort_flag, P.status, CST_WEIGHTS);
+      cprof_add(P.prof, 3, &pt, pw);
+      for (long long tp = pair0; tp < npairs; tp += pair_step, acc_it++) {
+        const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+        cprof_add(P.prof, 2, &pt, pw);
+        mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY);
+        cprof_add(P.prof, 0, &pt, pw);
         tc_fence_after();
-        const uint32_t sb = base + s * kStage;
-        const uint64_t ad = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
-        const uint64_t bd = desc_hi | (uint64_t)(((sb + kStageA) >> 4) & 0x3FFF);
-#pragma unroll
-        for (int kw = 0; kw < 3; kw++) {
-          // tap kw reads the tile shifted down by kw rows: the start address moves by kw * 128 bytes; the 128-byte
-          // swizzle is a function of the shared-memory address itself, so the shifted view stays consistent with
-          // what TMA wrote
-          const uint64_t adk = ad + (uint64_t)(kw * 8);
-          const uint64_t bdk = bd + (uint64_t)(kw * (NOUT * kC * 2 >> 4));
+        const uint32_t d_tmem = tmem + b * kAccStride;
+        for (int g = 0; g < 9; g++) {
+          cprof_add(P.prof, 2, &pt, pw);
+          mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
+          cprof_add(P.prof, 1, &pt, pw);
+          tc_fence_after();
+          const uint64_t ad = desc_hi | (uint64_t)(((ring + s * kStageA) >> 4) & 0x3FFF);
+          const uint64_t bd = desc_hi | (uint64_t)(((base + g * kHalfBytes) >> 4) & 0x3FFF);
 #pragma unroll
           for (int j = 0; j < KSTEPS; j++)
-            tc_mma_ss<kIdescN>(d_tmem, adk + (uint64_t)(j * 2), bdk + (uint64_t)(j * 2), (uint32_t)(g | kw | j));
+            tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(g | j));
+          tc_commit_pair(bar_empty + 8 * s);                      // frees this stage in both CTAs
+          if (++s == kStagesC) { s = 0; ph ^= 1; }
         }
-        tc_commit(bar_empty + 8 * s);
-        if (++s == kStagesC) { s = 0; ph ^= 1; }
+        tc_commit_pair(bar_acc_full + 8 * b);                     // both CTAs' epilogues
       }
-      tc_commit(bar_acc_full + 8 * b);
     }
   } else {
-    // ---- epilogue: thread = one output row (voxel of the padded volume), 64 channels
+    // ---- epilogue: thread = one computed row (voxel of the padded volume);
+    //      out[row] = acc_kw0[row - 1] + acc_kw1[row] + acc_kw2[row + 1], the neighbours by warp shuffle: each warp's 32
+    //      computed rows overlap the next warp's by two, so lanes 1..30 have both neighbours in their own warp
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    float bias[kC];
+    constexpr int CH = NOUT >= 32 ? 32 : 16;                       // channels per pass
+    float bias[NOUT];
 #pragma unroll
-    for (int j = 0; j < kC / 4; j++) {
+    for (int j = 0; j < NOUT / 4; j++) {
       const float4 q = __ldg(reinterpret_cast<const float4*>(P.bias) + j);
       bias[4 * j] = q.x; bias[4 * j + 1] = q.y; bias[4 * j + 2] = q.z; bias[4 * j + 3] = q.w;
     }
+    const uint32_t arr_acc_empty = map_to_cta(bar_acc_empty, 0);   // the leader's barrier
+    const bool pw = blockIdx.x == 0 && threadIdx.x == 64;
+    long long pt = clock64();
+    const uint32_t uW = (uint32_t)Wp, uH = (uint32_t)Hp, uD = (uint32_t)Dp;
+    // row of this thread in tile pair tp_ and whether it is written / an interior voxel (P < 2^31: 32-bit arithmetic)
+    auto locate = [&](long long tp_, uint32_t& p_, bool& writes_, bool& interior_, uint32_t& wp_, uint32_t& hp_, uint32_t& dp_, uint32_t& n_) {
+      const long long pl = (2 * tp_ + crank) * kTileOut + kWarpOut * quad + lane - 1;
+      writes_ = tp_ < npairs && lane >= 1 && lane <= kWarpOut && pl < P.P;
+      p_ = writes_ ? (uint32_t)pl : 0u;
+      const uint32_t t1 = p_ / uW, t2 = t1 / uH;
+      wp_ = p_ - t1 * uW; hp_ = t1 - t2 * uH; n_ = t2 / uD; dp_ = t2 - n_ * uD;
+      interior_ = writes_ && wp_ >= 1 && wp_ <= (uint32_t)P.W && hp_ >= 1 && hp_ <= (uint32_t)P.H && dp_ >= 1 && dp_ <= (uint32_t)P.D;
+    };
+    uint32_t p, wp, hp, dp, n_;
+    bool writes, interior;
+    locate(pair0, p, writes, interior, wp, hp, dp, n_);
+    // residual row of the thread's voxel, always fetched one tile ahead
+    uint4 sk[8];
+    bool use_skip = !LAST && P.skip != nullptr && interior;
+    if (use_skip) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)p * kC) + j);
+    }
     uint32_t acc_it = 0;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x, acc_it++) {
+    for (long long tp = pair0; tp < npairs; tp += pair_step, acc_it++) {
       const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-      const long long p = tile * kTile + r;
-      bool interior = false;
-      if (p < P.P) {
-        const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), dp = (int)((p / ((long long)Wp * Hp)) % Dp);
-        interior = wp >= 1 && wp <= P.W && hp >= 1 && hp <= P.H && dp >= 1 && dp <= P.D;
-      }
-      // residual row, fetched while the MMAs of this tile are still running
-      uint4 sk[8];
-      const bool use_skip = !LAST && P.skip != nullptr && interior;
-      if (use_skip) {
-#pragma unroll
-        for (int j = 0; j < 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + p * kC) + j);
-      }
+      uint32_t np, nwp, nhp, ndp, nn;
+      bool nwrites, ninterior;
+      locate(tp + pair_step, np, nwrites, ninterior, nwp, nhp, ndp, nn);
+      const bool nuse_skip = !LAST && P.skip != nullptr && ninterior;
+      cprof_add(P.prof, 10, &pt, pw);
       mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL);
+      cprof_add(P.prof, 8, &pt, pw);
       tc_fence_after();
-      if (LAST) {
-        uint32_t a[32];                                            // columns >= NOUT are not part of this layer
-        tmem_ld32(lane_addr + b * kC, a);
+      const uint32_t accb = lane_addr + b * kAccStride;
+#pragma unroll
+      for (int ck = 0; ck < NOUT / CH; ck++) {
+        uint32_t a0[CH], a1[CH], a2[CH];
+        tmem_ldn(accb + CH * ck, a0);
+        tmem_ldn(accb + NOUT + CH * ck, a1);
+        tmem_ldn(accb + 2 * NOUT + CH * ck, a2);
         tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(bar_acc_empty + 8 * b);
-        if (interior) {
-          const long long n_ = p / ((long long)Wp * Hp * Dp);
-          const int wp = (int)(p % Wp), hp = (int)((p / Wp) % Hp), dp = (int)((p / ((long long)Wp * Hp)) % Dp);
-          float* dst = P.y + ((((n_ * P.D + dp - 1) * P.H + hp - 1) * P.W) + wp - 1) * P.F;
-#pragma unroll
-          for (int f = 0; f < NOUT; f++)
-            if (f < P.F) { const float v = __uint_as_float(a[f]) + bias[f]; dst[f] = fmaxf(v, v * P.slope); }
+        if (ck == NOUT / CH - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
         }
-        continue;
-      }
-      uint32_t a0[32], a1[32];
-      tmem_ld32(lane_addr + b * kC, a0);
-      tmem_ld32(lane_addr + b * kC + 32, a1);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(bar_acc_empty + 8 * b);
-      if (p < P.P) {
-        uint4 o[8];
+        float v[CH];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          float v[8];
+        for (int i = 0; i < CH; i++) {
+          const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
+          const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
+          v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[CH * ck + i]);
+        }
+        if (LAST) {
+          if (interior) {
+            float* dst = P.y + ((((size_t)n_ * P.D + dp - 1) * P.H + hp - 1) * P.W + wp - 1) * P.F;
 #pragma unroll
-          for (int e = 0; e < 8; e++) {
-            const int c = 8 * j + e;
-            v[e] = __uint_as_float(c < 32 ? a0[c] : a1[c - 32]) + bias[c];
+            for (int f = 0; f < CH; f++)
+              if (CH * ck + f < P.F) dst[CH * ck + f] = fmaxf(v[f], v[f] * P.slope);
           }
+        } else {
           if (use_skip) {
-            const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[j]);
 #pragma unroll
-            for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[2 * e] += f.x; v[2 * e + 1] += f.y; }
-          }
-          uint32_t pk[4];
+            for (int h = 0; h < CH / 8; h++) {
+              const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[(CH / 8) * ck + h]);
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float x0 = interior ? fmaxf(v[2 * e], v[2 * e] * P.slope) : 0.f;
-            const float x1 = interior ? fmaxf(v[2 * e + 1], v[2 * e + 1] * P.slope) : 0.f;
-            pk[e] = pack_bf16(x0, x1);
+              for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[8 * h + 2 * e] += f.x; v[8 * h + 2 * e + 1] += f.y; }
+            }
           }
-          o[j] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          if (nuse_skip) {                                         // these registers are free again: next tile's residual row
+#pragma unroll
+            for (int h = 0; h < CH / 8; h++)
+              sk[(CH / 8) * ck + h] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)np * kC) + (CH / 8) * ck + h);
+          }
+          if (writes) {
+            uint4* dst = reinterpret_cast<uint4*>(P.out + (size_t)p * kC + CH * ck);
+#pragma unroll
+            for (int h = 0; h < CH / 8; h++) {
+              uint32_t pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                const float x0 = interior ? fmaxf(v[8 * h + 2 * e], v[8 * h + 2 * e] * P.slope) : 0.f;
+                const float x1 = interior ? fmaxf(v[8 * h + 2 * e + 1], v[8 * h + 2 * e + 1] * P.slope) : 0.f;
+                pk[e] = pack_bf16(x0, x1);
+              }
+              dst[h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          }
         }
-        uint4* dst = reinterpret_cast<uint4*>(P.out + p * kC);
-#pragma unroll
-        for (int j = 0; j < 8; j++) dst[j] = o[j];
       }
+      p = np; writes = nwrites; interior = ninterior; wp = nwp; hp = nhp; dp = ndp; n_ = nn; use_skip = nuse_skip;
     }
   }
   tc_fence_before();
@@ -245,9 +301,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
   if (*abort_flag && threadIdx.x == 0)
     for (int i = 0; i < 2000; i++) __nanosleep(1000);        // let copies in flight land before the CTA gives its memory back
   __syncthreads();
+  cluster_sync_all();                      // neither CTA leaves while its partner can still signal its barriers
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
   }
 }
 
@@ -373,7 +430,7 @@ ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
     if (!dw || !db) return fail("out of device memory for conv weights");
     m->w.push_back(dw); m->b.push_back(db);
     CUtensorMap map;
-    if (!make_map(&map, dw, 27 * rows, 3 * rows)) return fail("cuTensorMapEncodeTiled failed for conv weights");
+    if (!make_map(&map, dw, 27 * rows, 3 * rows / 2)) return fail("cuTensorMapEncodeTiled failed for conv weights");
     m->wmaps.push_back(map);
   }
   if (cudaMalloc(&m->status, sizeof(int)) != cudaSuccess) return fail("out of device memory");
@@ -395,7 +452,7 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     for (int b = 0; b < 4; b++) {
       if (cudaMalloc(&m->buf[b], (size_t)P * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
       cudaMemsetAsync(m->buf[b], 0, (size_t)P * kC * 2, s);        // the border must be zero before the first layer writes the interior
-      if (!make_map(&m->amaps[b], m->buf[b], P, kRowsA)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
+      if (!make_map(&m->amaps[b], m->buf[b], P, kTile / 4)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
     }
     m->P = P; m->shape[0] = N; m->shape[1] = D; m->shape[2] = H; m->shape[3] = W;
   }
@@ -406,8 +463,20 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     const long long blocks = (nvox + 255) / 256;
     conv_pack_input_kernel<<<(unsigned)(blocks < sms * 8 ? blocks : sms * 8), 256, 0, s>>>(x, m->buf[3], N, D, H, W, m->meta[0].cin);
   }
-  const long long ntiles = (P + kTile - 1) / kTile;
-  const int grid = (int)(ntiles < sms ? ntiles : sms);
+  const long long ntiles = (P + kTileOut - 1) / kTileOut, npairs = (ntiles + 1) / 2;
+  const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int grid = 2 * (int)(npairs < max_pairs ? npairs : max_pairs);          // clusters of two CTAs
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kConvThreads); cfg.dynamicSmemBytes = kConvSmem; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
+  static long long* dprof = nullptr;
+  if (want_prof && !dprof) cudaMalloc(&dprof, 16 * sizeof(long long));
+  if (want_prof) cudaMemsetAsync(dprof, 0, 16 * sizeof(long long), s);
   int cur = 3, skip = -1;
   for (int l = 0; l < nl; l++) {
     const LayerHost& L = m->meta[l];
@@ -419,12 +488,20 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l]; P_.bias = m->b[l];
     P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] : nullptr;
     P_.out = m->buf[dst]; P_.y = y; P_.F = L.cout;
-    P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status;
-    if (l == nl - 1) conv3d_tc_kernel<4, kEdgeC, true><<<grid, kConvThreads, kConvSmem, s>>>(P_);
-    else if (l == 0) conv3d_tc_kernel<1, kC, false><<<grid, kConvThreads, kConvSmem, s>>>(P_);
-    else conv3d_tc_kernel<4, kC, false><<<grid, kConvThreads, kConvSmem, s>>>(P_);
+    P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status; P_.prof = (want_prof && l == 2) ? dprof : nullptr;
+    const cudaError_t le = l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true>, P_)
+                           : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false>, P_)
+                                       : cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kC, false>, P_);
+    if (le != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(le); return false; }
     if (L.flags & LFLAG_SAVE_SKIP) skip = dst;
     cur = dst;
+  }
+  if (want_prof) {
+    long long h[16];
+    cudaStreamSynchronize(s);
+    cudaMemcpy(h, dprof, sizeof h, cudaMemcpyDeviceToHost);
+    std::fprintf(stderr, "conv prof, layer 2 (cycles, CTA 0): mma wait acc_empty %lld full %lld weights %lld issue %lld | tma wait empty %lld issue %lld | "
+                 "epilogue wait acc_full %lld boundary %lld rows %lld\n", h[0], h[1], h[3], h[2], h[6], h[7], h[8], h[9], h[10]);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(e); return false; }
