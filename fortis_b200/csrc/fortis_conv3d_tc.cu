@@ -8,24 +8,31 @@
 // reference chains behind it (runtime/fortis_rt.c:128-156, compiler/FortisFuse.cpp:626-655, 687-760).
 //
 // Layout: activations are bf16, channels-last, ZERO-PADDED in memory: [N][D+2][H+2][W+2][64], viewed as a matrix
-// [P rows][64 channels] (one 128-byte row per voxel).  With the border stored explicitly, the input rows a tap
-// (kd, kh, kw) needs for output rows p0..p0+127 are simply rows p0+shift..p0+shift+127 with
-// shift = (kd-1)(H+2)(W+2) + (kh-1)(W+2) + (kw-1): every tap is ONE plain 2-D TMA tile load, no im2col, no masks
-// (rows outside [0, P) are zero-filled by TMA).  Border rows of the output are computed and then written as zeros,
-// which keeps the padding intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work
-// at 33^3.
+// [P rows][64 channels] (one 128-byte row per voxel), with further zero rows in front of and behind the volume inside
+// its allocation.  With the border stored explicitly, the input rows the taps (kd, kh, *) need for output rows
+// p..p+31 are simply rows p+shift-1..p+shift+32 with shift = (kd-1)(H+2)(W+2) + (kh-1)(W+2): no im2col, no masks, and
+// no copy ever leaves the allocation.  Border rows of the output are computed and then written as zeros, which
+// keeps the padding intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work at 33^3.
 //
-// Per 128-row tile: D[128 x 64] = sum over 27 taps of A_tap[128 x 64] . W_tap[64 x 64]^T, 4 MMAs (K = 16) per tap.
-// The three kw taps of one (kd, kh) read the same activation rows shifted by one, so ONE 130-row tile is staged per
-// (kd, kh) and the three taps address it through descriptors whose start moves by 128 bytes (the kernel is bound
-// by the L2 -> shared-memory stream, and this cuts it from 648 KB to 366 KB per tile).  Ring of 5 stages of 41 KB
-// (activation tile + the three weight tiles, 128-byte swizzle); two accumulators so that the epilogue of a tile
-// overlaps the MMAs of the next.  Warp 0: TMA, warp 1: MMA, warps 2-5:
-// epilogue (thread = one voxel row, 64 channels).
+// The kernel runs as clusters of two CTAs (cta_group::2), one cluster per SM pair, each CTA owning a 128-row tile:
+//  * MMA: per (kd, kh) group ONE activation tile and KSTEPS MMAs of M = 256 (both CTAs' rows), N = 3 * 64, K = 16:
+//    the three kw taps are the three 64-column blocks of the accumulator, computed from the SAME (unshifted) rows,
+//    and the kw shift is applied once per tile in the epilogue: out[row] = acc_kw0[row-1] + acc_kw1[row] +
+//    acc_kw2[row+1].  (With one N = 64 MMA per tap both operands stream from shared memory at 128 B/clk and the MMA
+//    runs at 2/3 rate; N = 192 reads the activation slice once for three taps.)
+//  * weights: each CTA holds its half (96 of a group's 192 rows) of ALL 27 weight tiles in shared memory for the
+//    whole kernel (108 KB); cta_group::2 MMAs take half of B from each CTA.  Only activations stream: ring of 7
+//    stages of 16 KB, loaded by ONE 3-D TMA per stage: a tile is four 32-row boxes 30 rows apart (tensor map
+//    with an outer stride of 30 rows), one per TMEM lane quadrant, so that lanes 1..30 of every epilogue warp
+//    find both row neighbours in their own warp (shuffles; no shared-memory exchange).  No multicast loads anywhere:
+//    every copy goes to the issuing CTA's own shared memory, its completion counted on the leader's barrier.
+//  * two accumulators (2 x 192 TMEM columns) so that the epilogue of a tile overlaps the MMAs of the next.
+//  * warp 0: TMA (both CTAs), warp 1: MMA (leader only), warps 2-9: epilogue, two warps per lane quadrant (thread =
+//    one voxel row x 32 channels): bias + residual row (prefetched one tile ahead) + LeakyReLU -> bf16 -> row store.
 //
 // First layer: the fp32 NDHWC input is packed into its own padded bf16 volume with channels >= Cin zero, and the
-// weights are padded the same way, so the layer is the same shifted-tile GEMM with one k step per tap instead of
-// four.  Last layer: the weights are padded to 16 output channels; the epilogue adds the bias, applies the
+// weights are padded the same way, so the layer is the same GEMM with one k step per group instead of four.
+// Last layer: the weights are padded to 16 output channels (N = 48); the epilogue adds the bias, applies the
 // activation and writes the real channels of interior voxels as fp32.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -54,7 +61,7 @@ constexpr int kTileOut = 4 * kWarpOut;       // rows written per tile; a tile is
 constexpr int kStageA = kTile * kC * 2;      // 16 KB: one activation tile (a ring stage)
 constexpr int kResW = 9 * 96 * kC * 2;       // 108 KB: this CTA's half of all 27 weight tiles, resident for the whole kernel
 constexpr int kStagesC = 7;
-constexpr int kConvThreads = 192;
+constexpr int kConvThreads = 320;           // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int kConvSmem = kResW + kStagesC * kStageA + 256;
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators (each 3 * NOUT wide)
 template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT); };   // the pair's M = 256
@@ -62,7 +69,8 @@ constexpr int kEdgeC = 16;                   // first layer: input channels kept
 enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_WEIGHTS = 15, CST_ALIGN = 16 };
 
 struct ConvTcParams {
-  CUtensorMap amap;            // input activations [P][64] bf16, box 64 x 32
+  CUtensorMap amap;            // input activations as [4 (stride 30 rows)][rows][64] bf16 over the whole allocation, box 64 x 32 x 4
+  int front;                   // zero rows in front of row 0 of the volume inside the allocation
   CUtensorMap wmap;            // weights [27 * NOUT (tap, cout)][64 cin] bf16, box 64 x 3 NOUT
   const float* bias;           // [64] (zero beyond the layer's real outputs)
   const __nv_bfloat16* skip;   // [P][64] or null
@@ -112,7 +120,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStagesC; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 8); }   // 4 epilogue warps per CTA
+    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 16); }   // 8 epilogue warps per CTA
     mbar_init(bar_w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -150,9 +158,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
         cprof_add(P.prof, 6, &pt, pw);
         if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kStageA);
-#pragma unroll
-        for (int w = 0; w < 4; w++)                                // 32 rows per epilogue warp
-          tma_load_2d_pair(ring + s * kStageA + w * (kStageA / 4), &P.amap, 0, (int)(q0 + shift + kWarpOut * w), full0 + 8 * s);
+        // four 32-row boxes 30 rows apart (one per TMEM lane quadrant) in ONE copy: the tensor map's outer dimension
+        // has a stride of 30 rows.  The allocation carries zero rows on both sides, so every coordinate is in bounds.
+        tma_load_3d_pair(ring + s * kStageA, &P.amap, 0, (int)(q0 + shift) + P.front, 0, full0 + 8 * s);
         if (++s == kStagesC) { s = 0; ph ^= 1; }
       }
     }
@@ -193,13 +201,15 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     // ---- epilogue: thread = one computed row (voxel of the padded volume);
     //      out[row] = acc_kw0[row - 1] + acc_kw1[row] + acc_kw2[row + 1], the neighbours by warp shuffle: each warp's 32
     //      computed rows overlap the next warp's by two, so lanes 1..30 have both neighbours in their own warp
-    const int quad = warp & 3;
+    const int quad = warp & 3, half = (warp - 2) >> 2;            // TMEM lane quadrant; which half of the channels
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    constexpr int CH = NOUT >= 32 ? 32 : 16;                       // channels per pass
-    float bias[NOUT];
+    constexpr int CW = NOUT == kC ? kC / 2 : NOUT;                 // channels per warp: two warps share a row of 64
+    const bool active = NOUT == kC || half == 0;                   // a 16-channel layer needs one warp per quadrant
+    const int c0 = NOUT == kC ? CW * half : 0;
+    float bias[CW];
 #pragma unroll
-    for (int j = 0; j < NOUT / 4; j++) {
-      const float4 q = __ldg(reinterpret_cast<const float4*>(P.bias) + j);
+    for (int j = 0; j < CW / 4; j++) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(P.bias + c0) + j);
       bias[4 * j] = q.x; bias[4 * j + 1] = q.y; bias[4 * j + 2] = q.z; bias[4 * j + 3] = q.w;
     }
     const uint32_t arr_acc_empty = map_to_cta(bar_acc_empty, 0);   // the leader's barrier
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     // row of this thread in tile pair tp_ and whether it is written / an interior voxel (P < 2^31: 32-bit arithmetic)
     auto locate = [&](long long tp_, uint32_t& p_, bool& writes_, bool& interior_, uint32_t& wp_, uint32_t& hp_, uint32_t& dp_, uint32_t& n_) {
       const long long pl = (2 * tp_ + crank) * kTileOut + kWarpOut * quad + lane - 1;
-      writes_ = tp_ < npairs && lane >= 1 && lane <= kWarpOut && pl < P.P;
+      writes_ = active && tp_ < npairs && lane >= 1 && lane <= kWarpOut && pl < P.P;
       p_ = writes_ ? (uint32_t)pl : 0u;
       const uint32_t t1 = p_ / uW, t2 = t1 / uH;
       wp_ = p_ - t1 * uW; hp_ = t1 - t2 * uH; n_ = t2 / uD; dp_ = t2 - n_ * uD;
@@ -218,12 +228,12 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     uint32_t p, wp, hp, dp, n_;
     bool writes, interior;
     locate(pair0, p, writes, interior, wp, hp, dp, n_);
-    // residual row of the thread's voxel, always fetched one tile ahead
-    uint4 sk[8];
+    // this warp's half of the residual row of the thread's voxel, always fetched one tile ahead
+    uint4 sk[CW / 8];
     bool use_skip = !LAST && P.skip != nullptr && interior;
     if (use_skip) {
 #pragma unroll
-      for (int j = 0; j < 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)p * kC) + j);
+      for (int j = 0; j < CW / 8; j++) sk[j] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)p * kC + c0) + j);
     }
     uint32_t acc_it = 0;
     for (long long tp = pair0; tp < npairs; tp += pair_step, acc_it++) {
@@ -236,60 +246,57 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL);
       cprof_add(P.prof, 8, &pt, pw);
       tc_fence_after();
-      const uint32_t accb = lane_addr + b * kAccStride;
-#pragma unroll
-      for (int ck = 0; ck < NOUT / CH; ck++) {
-        uint32_t a0[CH], a1[CH], a2[CH];
-        tmem_ldn(accb + CH * ck, a0);
-        tmem_ldn(accb + NOUT + CH * ck, a1);
-        tmem_ldn(accb + 2 * NOUT + CH * ck, a2);
+      const uint32_t accb = lane_addr + b * kAccStride + c0;
+      uint32_t a0[CW], a1[CW], a2[CW];
+      if (active) {
+        tmem_ldn(accb, a0);
+        tmem_ldn(accb + NOUT, a1);
+        tmem_ldn(accb + 2 * NOUT, a2);
         tmem_ld_wait();
-        if (ck == NOUT / CH - 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
+      if (!active) continue;
+      float v[CW];
+#pragma unroll
+      for (int i = 0; i < CW; i++) {
+        const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
+        const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
+        v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[i]);
+      }
+      if (LAST) {
+        if (interior) {
+          float* dst = P.y + ((((size_t)n_ * P.D + dp - 1) * P.H + hp - 1) * P.W + wp - 1) * P.F;
+#pragma unroll
+          for (int f = 0; f < CW; f++)
+            if (f < P.F) dst[f] = fmaxf(v[f], v[f] * P.slope);
         }
-        float v[CH];
+      } else {
+        if (use_skip) {
 #pragma unroll
-        for (int i = 0; i < CH; i++) {
-          const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
-          const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
-          v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[CH * ck + i]);
+          for (int h = 0; h < CW / 8; h++) {
+            const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[h]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[8 * h + 2 * e] += f.x; v[8 * h + 2 * e + 1] += f.y; }
+          }
         }
-        if (LAST) {
-          if (interior) {
-            float* dst = P.y + ((((size_t)n_ * P.D + dp - 1) * P.H + hp - 1) * P.W + wp - 1) * P.F;
+        if (nuse_skip) {                                           // these registers are free again: next tile's residual row
 #pragma unroll
-            for (int f = 0; f < CH; f++)
-              if (CH * ck + f < P.F) dst[CH * ck + f] = fmaxf(v[f], v[f] * P.slope);
-          }
-        } else {
-          if (use_skip) {
+          for (int h = 0; h < CW / 8; h++) sk[h] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)np * kC + c0) + h);
+        }
+        if (writes) {
+          uint4* dst = reinterpret_cast<uint4*>(P.out + (size_t)p * kC + c0);
 #pragma unroll
-            for (int h = 0; h < CH / 8; h++) {
-              const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[(CH / 8) * ck + h]);
+          for (int h = 0; h < CW / 8; h++) {
+            uint32_t pk[4];
 #pragma unroll
-              for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[8 * h + 2 * e] += f.x; v[8 * h + 2 * e + 1] += f.y; }
+            for (int e = 0; e < 4; e++) {
+              const float x0 = interior ? fmaxf(v[8 * h + 2 * e], v[8 * h + 2 * e] * P.slope) : 0.f;
+              const float x1 = interior ? fmaxf(v[8 * h + 2 * e + 1], v[8 * h + 2 * e + 1] * P.slope) : 0.f;
+              pk[e] = pack_bf16(x0, x1);
             }
-          }
-          if (nuse_skip) {                                         // these registers are free again: next tile's residual row
-#pragma unroll
-            for (int h = 0; h < CH / 8; h++)
-              sk[(CH / 8) * ck + h] = __ldg(reinterpret_cast<const uint4*>(P.skip + (size_t)np * kC) + (CH / 8) * ck + h);
-          }
-          if (writes) {
-            uint4* dst = reinterpret_cast<uint4*>(P.out + (size_t)p * kC + CH * ck);
-#pragma unroll
-            for (int h = 0; h < CH / 8; h++) {
-              uint32_t pk[4];
-#pragma unroll
-              for (int e = 0; e < 4; e++) {
-                const float x0 = interior ? fmaxf(v[8 * h + 2 * e], v[8 * h + 2 * e] * P.slope) : 0.f;
-                const float x1 = interior ? fmaxf(v[8 * h + 2 * e + 1], v[8 * h + 2 * e + 1] * P.slope) : 0.f;
-                pk[e] = pack_bf16(x0, x1);
-              }
-              dst[h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
+            dst[h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           }
         }
       }
@@ -353,6 +360,18 @@ bool make_map(CUtensorMap* m, void* base, long long rows, int box_rows) {
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// the activation allocation (rows x 64 bf16) as [4][rows - 3 * 30][64] with the outer stride 30 rows: box {64, 32, 4}
+bool make_act_map(CUtensorMap* m, void* base, long long rows) {
+  EncodeTiledFn enc = conv_encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)kC, (cuuint64_t)(rows - 3 * kWarpOut), 4};
+  const cuuint64_t strides[2] = {(cuuint64_t)kC * 2, (cuuint64_t)kWarpOut * kC * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)kC, 32, 4};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 uint16_t to_bf16(float f) {
   uint32_t u;
   std::memcpy(&u, &f, 4);
@@ -369,7 +388,8 @@ struct ConvTcModel {
   std::vector<LayerHost> meta;
   std::vector<void*> w; std::vector<float*> b;             // per layer: bf16 [27 * rows][64] (rows = 64, last layer 16), fp32 bias [64]
   std::vector<CUtensorMap> wmaps;
-  __nv_bfloat16* buf[4] = {nullptr, nullptr, nullptr, nullptr};   // three rotating activation volumes + the packed input
+  __nv_bfloat16* buf[4] = {nullptr, nullptr, nullptr, nullptr};   // three rotating activation volumes + the packed input (allocations)
+  long long front = 0;                                            // zero rows in front of each volume inside its allocation
   CUtensorMap amaps[4];
   long long P = 0;
   int shape[4] = {0, 0, 0, 0};
@@ -450,9 +470,13 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   if (m->P != P || m->shape[0] != N || m->shape[1] != D || m->shape[2] != H || m->shape[3] != W) {
     for (auto& p : m->buf) { cudaFree(p); p = nullptr; }
     for (int b = 0; b < 4; b++) {
-      if (cudaMalloc(&m->buf[b], (size_t)P * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
-      cudaMemsetAsync(m->buf[b], 0, (size_t)P * kC * 2, s);        // the border must be zero before the first layer writes the interior
-      if (!make_map(&m->amaps[b], m->buf[b], P, kTile / 4)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
+      // zero rows on both sides of the volume cover every tap shift and the last (partial) pair of tiles, so the
+      // kernel's copies never leave the allocation
+      const long long front = (((long long)(H + 2) * (W + 2) + (W + 2) + 2 + 7) / 8) * 8, rows = front + P + front + 512;
+      m->front = front;
+      if (cudaMalloc(&m->buf[b], (size_t)rows * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
+      cudaMemsetAsync(m->buf[b], 0, (size_t)rows * kC * 2, s);     // padding and border must be zero before the first layer writes the interior
+      if (!make_act_map(&m->amaps[b], m->buf[b], rows)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
     }
     m->P = P; m->shape[0] = N; m->shape[1] = D; m->shape[2] = H; m->shape[3] = W;
   }
@@ -461,7 +485,7 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   {
     const long long blocks = (nvox + 255) / 256;
-    conv_pack_input_kernel<<<(unsigned)(blocks < sms * 8 ? blocks : sms * 8), 256, 0, s>>>(x, m->buf[3], N, D, H, W, m->meta[0].cin);
+    conv_pack_input_kernel<<<(unsigned)(blocks < sms * 8 ? blocks : sms * 8), 256, 0, s>>>(x, m->buf[3] + m->front * kC, N, D, H, W, m->meta[0].cin);
   }
   const long long ntiles = (P + kTileOut - 1) / kTileOut, npairs = (ntiles + 1) / 2;
   const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;
@@ -486,8 +510,8 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     ConvTcParams P_;
     std::memset(&P_, 0, sizeof P_);
     P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l]; P_.bias = m->b[l];
-    P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] : nullptr;
-    P_.out = m->buf[dst]; P_.y = y; P_.F = L.cout;
+    P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] + m->front * kC : nullptr;
+    P_.out = m->buf[dst] + m->front * kC; P_.y = y; P_.F = L.cout; P_.front = (int)m->front;
     P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status; P_.prof = (want_prof && l == 2) ? dprof : nullptr;
     const cudaError_t le = l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true>, P_)
                            : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false>, P_)

@@ -178,6 +178,12 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3}], [%4];\n\t}"
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t cluster_bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3, %4}], [%5];\n\t}"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(cluster_bar) : "memory");
+}
 // arrives on the barrier at the same shared-memory offset in BOTH CTAs once the pair's earlier MMAs are complete
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
   asm volatile(
