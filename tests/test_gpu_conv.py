@@ -68,6 +68,25 @@ def test_superres_net_bf16_tensor_cores(host, shape, blocks):
     assert host.L.fortis_device_status() == 0
 
 
+def test_conv_net_bf16_other_edge_widths(host):
+    """First / last layers with other channel counts (5 in, 7 out) and an extent whose row count is not a multiple of
+    the tile: the padded channels of the packed input and of the last layer's weights must stay out of the result."""
+    N, D, H, W = 1, 6, 9, 11
+    layers = fortis_b200.conv_layers(5, 64, 7, nblocks=1, seed=11)
+    for L in layers:
+        L["b"] = (np.random.default_rng(2).normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = np.random.default_rng(12).normal(size=(N, D, H, W, 5)).astype(np.float32)
+    model = fo.convnet_forward_lowp(layers, x)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", "bf16")
+    host.option("conv_shape", "%d,%d,%d,%d" % (N, D, H, W))
+    y = np.full((N, D, H, W, 7), np.nan, np.float32)
+    host.forward(x, y)
+    assert np.isfinite(y).all()
+    assert fo.rel_l2(y, model) < 2e-3
+    assert host.L.fortis_device_status() == 0
+
+
 def test_conv_probe_stamp_through_memref_entry(host, golden_dir):
     """The reference's conv probe (frontend/export_conv.py; README stamp 9617.28) through fortis_conv3d's memref ABI:
     NCDHW fp32, the bias and LeakyReLU(0.1) applied afterwards as the compiled program does in its epilogue kernel."""
