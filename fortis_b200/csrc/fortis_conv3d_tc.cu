@@ -10,25 +10,29 @@
 // Layout: activations are bf16, channels-last, ZERO-PADDED in memory: [N][D+2][H+2][W+2][64], viewed as a matrix
 // [P rows][64 channels] (one 128-byte row per voxel), with further zero rows in front of and behind the volume inside
 // its allocation.  With the border stored explicitly, the input rows the taps (kd, kh, *) need for output rows
-// p..p+31 are simply rows p+shift-1..p+shift+32 with shift = (kd-1)(H+2)(W+2) + (kh-1)(W+2): no im2col, no masks, and
-// no copy ever leaves the allocation.  Border rows of the output are computed and then written as zeros, which
-// keeps the padding intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work at 33^3.
+// p.. are simply rows p+shift.. with shift = (kd-1)(H+2)(W+2) + (kh-1)(W+2): no im2col, no masks, and no copy ever
+// leaves the allocation.  Border rows of the output are computed and then written as zeros, which keeps the padding
+// intact for the next layer; that costs ((D+2)(H+2)(W+2))/(DHW) = 1.19x the useful work at 33^3.
 //
 // The kernel runs as clusters of two CTAs (cta_group::2), one cluster per SM pair, each CTA owning a 128-row tile:
-//  * MMA: per (kd, kh) group ONE activation tile and KSTEPS MMAs of M = 256 (both CTAs' rows), N = 3 * 64, K = 16:
-//    the three kw taps are the three 64-column blocks of the accumulator, computed from the SAME (unshifted) rows,
-//    and the kw shift is applied once per tile in the epilogue: out[row] = acc_kw0[row-1] + acc_kw1[row] +
-//    acc_kw2[row+1].  (With one N = 64 MMA per tap both operands stream from shared memory at 128 B/clk and the MMA
-//    runs at 2/3 rate; N = 192 reads the activation slice once for three taps.)
+//  * MMA: per (kd, kh) KSTEPS MMAs of M = 256 (both CTAs' rows), N = 3 * 64, K = 16: the three kw taps are the three
+//    64-column blocks of the accumulator, computed from the SAME (unshifted) rows, and the kw shift is applied once
+//    per tile in the epilogue: out[row] = acc_kw0[row-1] + acc_kw1[row] + acc_kw2[row+1] (a tile writes 126 rows).
+//    (With one N = 64 MMA per tap both operands stream from shared memory at 128 B/clk and the MMA runs at 2/3
+//    rate; N = 192 reads the activation slice once for three taps.)
 //  * weights: each CTA holds its half (96 of a group's 192 rows) of ALL 27 weight tiles in shared memory for the
-//    whole kernel (108 KB); cta_group::2 MMAs take half of B from each CTA.  Only activations stream: ring of 7
-//    stages of 16 KB, loaded by ONE 3-D TMA per stage: a tile is four 32-row boxes 30 rows apart (tensor map
-//    with an outer stride of 30 rows), one per TMEM lane quadrant, so that lanes 1..30 of every epilogue warp
-//    find both row neighbours in their own warp (shuffles; no shared-memory exchange).  No multicast loads anywhere:
-//    every copy goes to the issuing CTA's own shared memory, its completion counted on the leader's barrier.
+//    whole kernel (108 KB); cta_group::2 MMAs take half of B from each CTA.  Only activations stream.
+//  * activations: ONE stage per kd holds rows q - (W+2) .. q + 127 + (W+2), which serve all three kh taps through
+//    descriptors whose start address moves by (W+2) rows (the 128-byte swizzle is a function of the shared-memory
+//    address, so shifted views match what TMA wrote).  Ring of kRingBytes / stage size stages (4 x 25 KB at W = 33).
+//    No multicast loads anywhere: every copy goes to the issuing CTA's own shared memory, its completion counted on
+//    the leader's barrier.
 //  * two accumulators (2 x 192 TMEM columns) so that the epilogue of a tile overlaps the MMAs of the next.
 //  * warp 0: TMA (both CTAs), warp 1: MMA (leader only), warps 2-9: epilogue, two warps per lane quadrant (thread =
-//    one voxel row x 32 channels): bias + residual row (prefetched one tile ahead) + LeakyReLU -> bf16 -> row store.
+//    one voxel row x 32 channels): row neighbours by warp shuffle, the rows on either side of a warp boundary through
+//    shared memory; bias + residual row (prefetched one tile ahead) + LeakyReLU -> bf16 -> row store.  The
+//    accumulator is handed back with a RELAXED cluster-scope arrive: a release would first drain the thread's
+//    outstanding global stores (measured ~1700 cycles per tile).
 //
 // First layer: the fp32 NDHWC input is packed into its own padded bf16 volume with channels >= Cin zero, and the
 // weights are padded the same way, so the layer is the same GEMM with one k step per group instead of four.
@@ -56,20 +60,22 @@ namespace {
 
 constexpr int kC = 64;                       // channels of the tensor-core layers
 constexpr int kTile = 128;                   // rows computed per tile (the MMA's M)
-constexpr int kWarpOut = 30;                 // rows written per epilogue warp: its first and last computed rows only feed their neighbours
-constexpr int kTileOut = 4 * kWarpOut;       // rows written per tile; a tile is four 32-row boxes whose rows overlap by two
-constexpr int kStageA = kTile * kC * 2;      // 16 KB: one activation tile (a ring stage)
+constexpr int kTileOut = kTile - 2;          // rows written per tile: the first and last computed rows only feed their neighbours
+constexpr int kRingBytes = 108 * 1024;       // activation ring: nstages stages of (128 + 2 (W+2)) rows each
+constexpr int kMaxStages = 7;
+constexpr int kXchBytes = 2 * 2 * 4 * kC * 4; // rows exchanged between epilogue warps: [tile parity][up | down][quadrant][channel] floats
 constexpr int kResW = 9 * 96 * kC * 2;       // 108 KB: this CTA's half of all 27 weight tiles, resident for the whole kernel
-constexpr int kStagesC = 7;
 constexpr int kConvThreads = 320;           // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
-constexpr int kConvSmem = kResW + kStagesC * kStageA + 256;
+constexpr int kConvSmem = kResW + kRingBytes + 256 + kXchBytes;
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators (each 3 * NOUT wide)
 template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT); };   // the pair's M = 256
 constexpr int kEdgeC = 16;                   // first layer: input channels kept; last layer: output channels computed
 enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_WEIGHTS = 15, CST_ALIGN = 16 };
 
 struct ConvTcParams {
-  CUtensorMap amap;            // input activations as [4 (stride 30 rows)][rows][64] bf16 over the whole allocation, box 64 x 32 x 4
+  CUtensorMap amap;            // the activation allocation [rows][64] bf16, box 64 x box_rows
+  int stage_bytes, nstages;    // activation ring geometry: one stage holds the 128 + 2 (W+2) rows one kd needs
+  int box_rows, nbox;          // a stage is loaded as nbox boxes of box_rows rows
   int front;                   // zero rows in front of row 0 of the volume inside the allocation
   CUtensorMap wmap;            // weights [27 * NOUT (tap, cout)][64 cin] bf16, box 64 x 3 NOUT
   const float* bias;           // [64] (zero beyond the layer's real outputs)
@@ -104,13 +110,14 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     return;
   }
   const uint32_t ring = base + kResW;
-  const uint32_t bars = ring + kStagesC * kStageA;
+  const uint32_t bars = ring + kRingBytes;
   // barrier block (256 B): full [0,56) empty [56,112) acc_full [112,128) acc_empty [128,144) weights [144,152)
   // tmem base 160, abort flag 164
   const uint32_t bar_full = bars, bar_empty = bars + 56, bar_acc_full = bars + 112, bar_acc_empty = bars + 128, bar_w = bars + 144;
-  uint8_t* barp = smem + kResW + kStagesC * kStageA;
+  uint8_t* barp = smem + kResW + kRingBytes;
   uint32_t* tmem_slot = (uint32_t*)(barp + 160);
   volatile int* abort_flag = (volatile int*)(barp + 164);
+  float* xch = (float*)(barp + 256);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = cluster_ctarank();
   const long long ntiles = (P.P + kTileOut - 1) / kTileOut;
@@ -119,7 +126,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
   const int Wp = P.W + 2, Hp = P.H + 2, Dp = P.D + 2;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStagesC; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int s = 0; s < kMaxStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 16); }   // 8 epilogue warps per CTA
     mbar_init(bar_w, 1);
     *abort_flag = 0;
@@ -150,18 +157,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     const bool pw = blockIdx.x == 0 && lane == 0;
     long long pt = clock64();
     for (long long tp = pair0; tp < npairs && !stop; tp += pair_step) {
-      const long long q0 = (2 * tp + crank) * kTileOut - 1;       // first computed row of this CTA's tile (warp w: q0 + 30 w ...)
-      for (int g = 0; g < 9; g++) {
-        const int kd = g / 3, kh = g % 3;
-        const long long shift = (long long)(kd - 1) * Hp * Wp + (long long)(kh - 1) * Wp;
+      const long long q0 = (2 * tp + crank) * kTileOut - 1;       // first computed row of this CTA's tile
+      for (int kd = 0; kd < 3; kd++) {
+        // rows q0 + (kd-1) Hp Wp - Wp ... + 127 + Wp serve the three kh taps of this kd.  The allocation carries zero
+        // rows on both sides, so every coordinate is in bounds.
+        const int y0 = (int)(q0 + (long long)(kd - 1) * Hp * Wp - Wp) + P.front;
         cprof_add(P.prof, 7, &pt, pw);
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
         cprof_add(P.prof, 6, &pt, pw);
-        if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kStageA);
-        // four 32-row boxes 30 rows apart (one per TMEM lane quadrant) in ONE copy: the tensor map's outer dimension
-        // has a stride of 30 rows.  The allocation carries zero rows on both sides, so every coordinate is in bounds.
-        tma_load_3d_pair(ring + s * kStageA, &P.amap, 0, (int)(q0 + shift) + P.front, 0, full0 + 8 * s);
-        if (++s == kStagesC) { s = 0; ph ^= 1; }
+        if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * P.nbox * P.box_rows * kC * 2);
+        for (int bx = 0; bx < P.nbox; bx++)
+          tma_load_2d_pair(ring + s * P.stage_bytes + bx * P.box_rows * kC * 2, &P.amap, 0, y0 + bx * P.box_rows, full0 + 8 * s);
+        if (++s == (uint32_t)P.nstages) { s = 0; ph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -181,18 +188,24 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
         cprof_add(P.prof, 0, &pt, pw);
         tc_fence_after();
         const uint32_t d_tmem = tmem + b * kAccStride;
-        for (int g = 0; g < 9; g++) {
+        for (int kd = 0; kd < 3; kd++) {
           cprof_add(P.prof, 2, &pt, pw);
           mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
           cprof_add(P.prof, 1, &pt, pw);
           tc_fence_after();
-          const uint64_t ad = desc_hi | (uint64_t)(((ring + s * kStageA) >> 4) & 0x3FFF);
-          const uint64_t bd = desc_hi | (uint64_t)(((base + g * kHalfBytes) >> 4) & 0x3FFF);
+          const uint32_t sa = ring + s * P.stage_bytes;
 #pragma unroll
-          for (int j = 0; j < KSTEPS; j++)
-            tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(g | j));
+          for (int kh = 0; kh < 3; kh++) {
+            // tap row kh reads the stage kh * Wp rows further down: the descriptor's start address moves; the 128-byte
+            // swizzle is a function of the shared-memory address, so the shifted view matches what TMA wrote
+            const uint64_t ad = desc_hi | (uint64_t)(((sa + kh * Wp * (kC * 2)) >> 4) & 0x3FFF);
+            const uint64_t bd = desc_hi | (uint64_t)(((base + (kd * 3 + kh) * kHalfBytes) >> 4) & 0x3FFF);
+#pragma unroll
+            for (int j = 0; j < KSTEPS; j++)
+              tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(kd | kh | j));
+          }
           tc_commit_pair(bar_empty + 8 * s);                      // frees this stage in both CTAs
-          if (++s == kStagesC) { s = 0; ph ^= 1; }
+          if (++s == (uint32_t)P.nstages) { s = 0; ph ^= 1; }
         }
         tc_commit_pair(bar_acc_full + 8 * b);                     // both CTAs' epilogues
       }
@@ -218,8 +231,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     const uint32_t uW = (uint32_t)Wp, uH = (uint32_t)Hp, uD = (uint32_t)Dp;
     // row of this thread in tile pair tp_ and whether it is written / an interior voxel (P < 2^31: 32-bit arithmetic)
     auto locate = [&](long long tp_, uint32_t& p_, bool& writes_, bool& interior_, uint32_t& wp_, uint32_t& hp_, uint32_t& dp_, uint32_t& n_) {
-      const long long pl = (2 * tp_ + crank) * kTileOut + kWarpOut * quad + lane - 1;
-      writes_ = active && tp_ < npairs && lane >= 1 && lane <= kWarpOut && pl < P.P;
+      const int r = quad * 32 + lane;                              // rows 0 and 127 of a tile are computed for their neighbours only
+      const long long pl = (2 * tp_ + crank) * kTileOut + r - 1;
+      writes_ = active && tp_ < npairs && r >= 1 && r <= kTileOut && pl < P.P;
       p_ = writes_ ? (uint32_t)pl : 0u;
       const uint32_t t1 = p_ / uW, t2 = t1 / uH;
       wp_ = p_ - t1 * uW; hp_ = t1 - t2 * uH; n_ = t2 / uD; dp_ = t2 - n_ * uD;
@@ -256,13 +270,28 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
+      if (lane == 0) mbar_arrive_cluster_relaxed(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
       if (!active) continue;
+      // rows on either side of a warp boundary go through shared memory (the buffer alternates per tile, so one
+      // barrier per tile among the four warps that hold the same channels is enough)
+      float* xu = xch + (acc_it & 1) * (2 * 4 * kC);               // kw = 0 partials of each quadrant's last row
+      float* xd = xu + 4 * kC;                                     // kw = 2 partials of each quadrant's first row
+      if (lane == 31) {
+#pragma unroll
+        for (int i = 0; i < CW; i++) xu[quad * kC + c0 + i] = __uint_as_float(a0[i]);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < CW; i++) xd[quad * kC + c0 + i] = __uint_as_float(a2[i]);
+      }
+      if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
       float v[CW];
 #pragma unroll
       for (int i = 0; i < CW; i++) {
-        const float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
-        const float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
+        float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
+        float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
+        if (lane == 0 && quad > 0) up = xu[(quad - 1) * kC + c0 + i];
+        if (lane == 31 && quad < 3) dn = xd[(quad + 1) * kC + c0 + i];
         v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[i]);
       }
       if (LAST) {
@@ -360,16 +389,17 @@ bool make_map(CUtensorMap* m, void* base, long long rows, int box_rows) {
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// the activation allocation (rows x 64 bf16) as [4][rows - 3 * 30][64] with the outer stride 30 rows: box {64, 32, 4}
-bool make_act_map(CUtensorMap* m, void* base, long long rows) {
-  EncodeTiledFn enc = conv_encode_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)kC, (cuuint64_t)(rows - 3 * kWarpOut), 4};
-  const cuuint64_t strides[2] = {(cuuint64_t)kC * 2, (cuuint64_t)kWarpOut * kC * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)kC, 32, 4};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+// geometry of the activation ring for a volume whose padded W extent is Wp: a stage holds 128 + 2 Wp rows, loaded as
+// nbox boxes of box_rows (<= 256, multiple of 8) rows
+struct RingGeom { int stage_bytes, nstages, box_rows, nbox; };
+bool ring_geometry(int Wp, RingGeom* g) {
+  const int R = kTile + 2 * Wp;
+  g->nbox = (R + 255) / 256;
+  g->box_rows = (((R + g->nbox - 1) / g->nbox) + 7) / 8 * 8;
+  g->stage_bytes = ((g->nbox * g->box_rows * kC * 2) + 1023) / 1024 * 1024;
+  g->nstages = kRingBytes / g->stage_bytes;
+  if (g->nstages > kMaxStages) g->nstages = kMaxStages;
+  return g->nstages >= 2;
 }
 
 uint16_t to_bf16(float f) {
@@ -476,10 +506,14 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
       m->front = front;
       if (cudaMalloc(&m->buf[b], (size_t)rows * kC * 2) != cudaSuccess) { if (err) *err = "out of device memory for conv activations"; return false; }
       cudaMemsetAsync(m->buf[b], 0, (size_t)rows * kC * 2, s);     // padding and border must be zero before the first layer writes the interior
-      if (!make_act_map(&m->amaps[b], m->buf[b], rows)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
+      RingGeom g;
+      if (!ring_geometry(W + 2, &g)) { if (err) *err = "conv3d bf16 path: W too large for the shared-memory activation ring (use precision=fp32)"; return false; }
+      if (!make_map(&m->amaps[b], m->buf[b], rows, g.box_rows)) { if (err) *err = "cuTensorMapEncodeTiled failed for conv activations"; return false; }
     }
     m->P = P; m->shape[0] = N; m->shape[1] = D; m->shape[2] = H; m->shape[3] = W;
   }
+  RingGeom geom;
+  ring_geometry(W + 2, &geom);
   const int nl = (int)m->meta.size();
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -512,6 +546,7 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     P_.amap = m->amaps[cur]; P_.wmap = m->wmaps[l]; P_.bias = m->b[l];
     P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] + m->front * kC : nullptr;
     P_.out = m->buf[dst] + m->front * kC; P_.y = y; P_.F = L.cout; P_.front = (int)m->front;
+    P_.stage_bytes = geom.stage_bytes; P_.nstages = geom.nstages; P_.box_rows = geom.box_rows; P_.nbox = geom.nbox;
     P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status; P_.prof = (want_prof && l == 2) ? dprof : nullptr;
     const cudaError_t le = l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true>, P_)
                            : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false>, P_)

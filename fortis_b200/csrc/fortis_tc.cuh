@@ -170,6 +170,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// the same without release semantics: for hand-offs that publish no generic-memory writes (an accumulator in tensor
+// memory has been read, tcgen05.wait::ld + tcgen05.fence::before_thread_sync done).  A cluster-scope release makes the
+// thread wait for its outstanding global stores first, measured at ~1700 cycles per tile in the conv epilogue.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // plain (no multicast) tile load into THIS CTA's shared memory whose completion is counted on `cluster_bar`, a barrier
 // given by its shared::cluster address
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
