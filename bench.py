@@ -1,26 +1,32 @@
 #!/usr/bin/env python3
 """Benchmark of the fused gather -> forward -> scatter step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--precision bf16|fp32|fp8w] [--workload column|stencil|...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--precision bf16|fp16|fp32|fp8w] [--workload column|stencil|conv|toy|column_c5]
     python bench.py --impl reference ...     # the CPU implementation of the same path on the host cores
+    python bench.py --impl incumbent ...     # the reference's own GPU runtime (cuBLAS SGEMM per layer), comparison only
 
-Workload (default "column", BASELINE config 2): 49,152 columns x 60 levels; 244 features gathered from four
-Fortran (ncol,60) fp32 fields + 4 per-column scalars; 244 -> 768 x4 -> 128 MLP with LeakyReLU(0.15); 128 outputs
-scattered into two (ncol,60) arrays and eight (ncol) vectors.  Synthetic seeded inputs with the configuration's
-shapes and distributions stand in for the climate data the reference measured on.
+Workload (default "column"): 49,152 columns x 60 levels; 244 features gathered from four Fortran (ncol,60) fp32
+fields + 4 per-column scalars; 244 -> 768 x4 -> 128 MLP with LeakyReLU(0.15); 128 outputs scattered into two
+(ncol,60) arrays and eight (ncol) vectors.  Synthetic seeded inputs with the configuration's shapes and distributions
+stand in for the climate data the reference measured on.
 
-One "step" = one call of the fused entry point over all columns of this rank.  `value` is measured with the
-Fortran arrays resident in HBM; `e2e` is the same call given HOST arrays (pinned), so the H2D of every input
-array and the D2H of every output array are inside the timed region.  Multi-GPU: one process per GPU, each rank
-owns its own contiguous column block (weak scaling, no data-path collective); the per-rank fp64 checksums are
-summed with one NCCL all-reduce after the timed loop.
+One "step" = one call of the fused entry point over all columns of this rank.  `value` is measured with the Fortran
+arrays resident in HBM; `e2e` is the same call given HOST arrays (pinned), so the H2D of every input array and the D2H
+of every output array are inside the timed region.  Timing: per step, CUDA events on the library's stream; the L2
+flush (a 256 MB fill) is enqueued on the same stream just before the first event, so the host has queued the step by
+the time the GPU reaches it and the event pair brackets device time only.
+
+Multi-GPU: one process per GPU, each rank owns its own contiguous column block (weak scaling, no data-path
+collective).  With more than one rank the line also carries a `sharded` block: the sharded configuration (2^20 columns
+per block, FP8-E4M3 weights) as ONE seeded global problem of 8 blocks, run weak (one block per rank) and strong (8
+blocks over the ranks), with the per-block checksums verified against a single-rank pass over the same blocks and
+summed with one NCCL all-reduce.
 """
 import argparse
 import json
 import os
 import subprocess
 import sys
-import threading
 import time
 
 import numpy as np
@@ -28,9 +34,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-FLOP_PER_COL = {"column": 2 * (244 * 768 + 3 * 768 * 768 + 768 * 128), "stencil": 2 * (27 * 20 + 20 * 20 + 20 * 3),
-                "toy": 2 * (64 * 256 + 256 * 256 + 256 * 64), "conv": 2 * 27 * (3 * 64 + 12 * 64 * 64 + 64 * 3)}
-BYTES_PER_COL = {"column": 4 * (244 + 128), "stencil": 24, "toy": 4 * 128}
+SHARD_BLOCKS = 8
+SHARD_COLS = 1 << 20
 
 
 def parse():
@@ -38,61 +43,21 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--impl", default="fortis_b200", choices=["fortis_b200", "reference"])
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32", "fp8w"])
+    ap.add_argument("--impl", default="fortis_b200", choices=["fortis_b200", "reference", "incumbent"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32", "fp8w"])
     ap.add_argument("--workload", default="column", choices=["column", "column_c5", "stencil", "toy", "conv"])
     ap.add_argument("--ncol", type=int, default=0, help="override the per-rank column count (column workloads)")
+    ap.add_argument("--sharded", action="store_true", help="run the sharded-configuration block also on one GPU")
+    ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true")
     return ap.parse_args()
 
 
-# -----------------------------------------------------------------------------------------------------------------
-# workloads
-# -----------------------------------------------------------------------------------------------------------------
-def make_workload(name, rank, ncol_override=0):
-    from oracle import fortis_oracle as fo     # descriptor builders only (plain dict construction)
-    import fortis_b200
-    if name in ("column", "column_c5"):
-        ncol = ncol_override or (49152 if name == "column" else 1 << 20)
-        nlev = 60
-        G, S, Lp, K = fo.column_descriptors(ncol, nlev)
-        rng = np.random.default_rng((2 if name == "column" else 7000) + rank)
-        f32 = np.float32
-        gin = [np.asfortranarray((250 + 20 * rng.standard_normal((ncol, nlev), dtype=f32))),
-               np.asfortranarray(np.exp(-6 + rng.standard_normal((ncol, nlev), dtype=f32))),
-               np.asfortranarray(10 * rng.standard_normal((ncol, nlev), dtype=f32)),
-               np.asfortranarray(10 * rng.standard_normal((ncol, nlev), dtype=f32))]
-        gin += [rng.standard_normal(ncol, dtype=f32) for _ in range(4)]
-        sout = [np.zeros((ncol, nlev), f32, order="F") for _ in range(2)] + [np.zeros(ncol, f32) for _ in range(8)]
-        layers = fortis_b200.mlp_layers([244, 768, 768, 768, 768, 128], seed=0)
-        return dict(G=G, S=S, Lp=Lp, K=K, gin=gin, sout=sout, layers=layers, units=ncol, kind="column",
-                    label="climate column MLP, %d columns x 60 levels, 244->768x4->128" % ncol)
-    if name == "stencil":
-        nx, ny, nz = 1440, 1080, 4
-        G, S, Lp, K = fo.stencil_descriptors(nx, ny, nz)
-        rng = np.random.default_rng(3 + rank)
-        gin = [np.asfortranarray(rng.standard_normal((nx + 2, ny + 2, nz), dtype=np.float32)) for _ in range(3)]
-        sout = [np.zeros((nx + 2, ny + 2, nz), np.float32, order="F") for _ in range(3)]
-        layers = fortis_b200.mlp_layers([27, 20, 20, 3], seed=4, init="uniform", act="relu", bias="uniform")
-        return dict(G=G, S=S, Lp=Lp, K=K, gin=gin, sout=sout, layers=layers, units=nx * ny * nz, kind="stencil",
-                    label="ocean stencil MLP, 1440x1080x4 points, 27->20->20->3")
-    if name == "conv":
-        shape = (8, 33, 33, 33)
-        rng = np.random.default_rng(5 + rank)
-        x = rng.standard_normal(shape + (3,), dtype=np.float32)
-        y = np.zeros(shape + (3,), np.float32)
-        layers = fortis_b200.conv_layers(3, 64, 3, nblocks=6, seed=6)
-        return dict(G=None, S=None, Lp=None, K=None, gin=[x], sout=[y], layers=layers, units=int(np.prod(shape)), kind="conv",
-                    shape=shape, label="conv3d super-resolution net, 8 x 33^3 x 3 NDHWC, 3->64, 6 residual blocks, 64->3")
-    ncol = 4096
-    G, S, Lp, K = fo.identity_descriptors(64, 64, ncol)
-    rng = np.random.default_rng(rank)
-    gin = [np.asfortranarray((2 * rng.random((64, ncol)) - 1).astype(np.float32))]
-    sout = [np.zeros((64, ncol), np.float32, order="F")]
-    layers = fortis_b200.mlp_layers([64, 256, 256, 64], seed=1, init="kaiming_uniform", act="relu")
-    return dict(G=G, S=S, Lp=Lp, K=K, gin=gin, sout=sout, layers=layers, units=ncol, kind="toy", label="toy MLP, 4096 columns")
+def make_workload(name, rank, ncol=0):
+    from fortis_b200 import workloads
+    return workloads.make(name, rank, ncol)
 
 
 # -----------------------------------------------------------------------------------------------------------------
@@ -133,16 +98,17 @@ class ClockSampler:
 
 
 # -----------------------------------------------------------------------------------------------------------------
-# CPU arm: the oracle's C port of the native forward, all host threads, bounded sample
+# CPU arm: the checker's C port of the reference's native forward, all host threads, bounded sample.
+# This is the only part of this file that touches oracle/ (the CPU baseline and the reference arm).
 # -----------------------------------------------------------------------------------------------------------------
 def cpu_step_fn(wl, sample_units):
     import ctypes
     from oracle import build as ob
     from oracle import cport
+    from oracle import fortis_oracle as fo
     lib = ctypes.CDLL(ob.build_port(verbose=False))
     # all host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which is not what a CPU baseline wants)
     threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    from oracle import fortis_oracle as fo
     G, S, Lp, K = wl["G"], wl["S"], wl["Lp"], wl["K"]
     P = fo.loop_params(Lp, K)
     Ag = fo.plan_arrays(G, [(s["array"], s["idx"]) for s in G["slots"]])
@@ -172,8 +138,6 @@ def cpu_step_fn(wl, sample_units):
     # a sample of `sample_units` columns of the first plane (columns are independent, cost is per column)
     count = min(sample_units, P["count"])
     cs = ctypes.c_double()
-
-    step_count = count
 
     def step():
         lib.oracle_step(ctypes.c_long(count), 1, P["ni"], len(G["slots"]), inp, ia, io, isi, isj, isk,
@@ -207,6 +171,9 @@ def run_reference(args):
     if rank != 0:
         return
     wl = make_workload(args.workload, 0, args.ncol)
+    if wl["kind"] == "conv":
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU port covers MLP hosts; the conv workload has no CPU arm"}))
+        return
     probe = 256 if wl["kind"] != "stencil" else 65536
     step, threads = cpu_step_fn(wl, probe)
     t0 = time.perf_counter(); n = step(); dt = time.perf_counter() - t0
@@ -233,187 +200,362 @@ def run_reference(args):
 
 
 # -----------------------------------------------------------------------------------------------------------------
-# GPU arm
+# Incumbent GPU path (comparison only, its own process): the reference's runtime compiled unchanged for sm_100a
+# (oracle/_ref/libfortis_ref_rt.so: runtime/fortis_rt.c + runtime/fortis_fft.cu) doing what its MLIR-generated
+# mlp_kernel does for a Linear stack: fortis_gemm (cuBLAS SGEMM on pre-transposed weights) per layer + a separate
+# bias / activation kernel, behind a gather that materialises X and in front of a scatter that reads Y
+# (compiler/FortisFuse.cpp:587-655).  Gather, epilogue and scatter are torch kernels here (the reference generates
+# them per host; its generator cannot express this configuration's constant level subscripts).
 # -----------------------------------------------------------------------------------------------------------------
-# the library path the reference's runtime takes on a GPU, for comparison (column workloads): materialise X with a
-# gather, one cuBLAS SGEMM per layer with a separate bias / activation pass, scatter Y (runtime/fortis_rt.c:87-100,
-# compiler/FortisFuse.cpp:587-655).  torch's fp32 matmul with TF32 off is that SGEMM.  Reported beside the result;
-# never part of `value`.
-# -----------------------------------------------------------------------------------------------------------------
-def time_incumbent(torch, wl, d_in, d_out, flush, steps=10):
-    torch.backends.cuda.matmul.allow_tf32 = False
+def run_incumbent(args):
+    import ctypes
+    import torch
+    so = os.path.join(ROOT, "oracle", "_ref", "libfortis_ref_rt.so")
+    if not os.path.exists(so):
+        print(json.dumps({"impl": "incumbent", "unavailable": "oracle/_ref/libfortis_ref_rt.so was not built (needs the reference checkout at build time)"}))
+        return
+    ref = ctypes.CDLL(so, mode=ctypes.RTLD_LOCAL | os.RTLD_DEEPBIND)
+    torch.cuda.set_device(0)
+    wl = make_workload(args.workload, 0, args.ncol)
+    if wl["kind"] not in ("column", "toy"):
+        print(json.dumps({"impl": "incumbent", "unavailable": "incumbent leg covers the column MLP workloads"}))
+        return
     ncol = wl["units"]
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    ref.fortis_gemm.argtypes = [vp, vp, cl, cl, cl, cl, cl] * 3 + [cl, cl, cl]
+    ref.fortis_gemm.restype = None
+    ref.mgpuStreamCreate.restype = vp
+    stream = torch.cuda.ExternalStream(ref.mgpuStreamCreate())
     W = [torch.from_numpy(L["W"]).cuda() for L in wl["layers"]]
     B = [torch.from_numpy(L["b"]).cuda() for L in wl["layers"]]
-    views_in = [a.view(-1, ncol).t() for a in d_in]                # Fortran (ncol, nlev) -> (ncol, nlev) strided views
-    outs = [a.view(-1, ncol).t() for a in d_out]
+    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
+    d_in = [to_dev(a) for a in wl["gin"]]
+    d_out = [to_dev(a) for a in wl["sout"]]
+    if wl["kind"] == "column":
+        views_in = [a.view(-1, ncol).t() for a in d_in]            # Fortran (ncol, nlev) -> (ncol, nlev) strided views
+        outs = [a.view(-1, ncol).t() for a in d_out]
+    else:
+        views_in = [d_in[0].view(ncol, -1)]
+        outs = [d_out[0].view(ncol, -1)]
+    acts = [torch.empty(ncol, L["W"].shape[0], device="cuda") for L in wl["layers"]]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def step():
         x = torch.cat(views_in, dim=1).contiguous()                # the gather kernel's X
         for l, L in enumerate(wl["layers"]):
-            x = torch.addmm(B[l], x, W[l].t())
+            n, k = L["W"].shape
+            y = acts[l]
+            ref.fortis_gemm(x.data_ptr(), x.data_ptr(), 0, ncol, k, k, 1, W[l].data_ptr(), W[l].data_ptr(), 0, n, k, k, 1,
+                            y.data_ptr(), y.data_ptr(), 0, ncol, n, n, 1, ncol, n, k)
+            y.add_(B[l])                                            # the epilogue kernel: bias, then the activation
             if L["act"] == "leaky":
-                x = torch.nn.functional.leaky_relu(x, L["slope"])
+                torch.nn.functional.leaky_relu(y, L["slope"], inplace=True)
             elif L["act"] == "relu":
-                x = torch.relu(x)
+                torch.relu_(y)
+            x = y
         o = 0
         for v in outs:                                             # the scatter kernel
             v.copy_(x[:, o:o + v.shape[1]])
             o += v.shape[1]
 
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    ms = []
-    for _ in range(steps):
-        flush.fill_(1)
+    steps = max(3, min(args.steps, 20))
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
         torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        step()
-        e.record()
-        torch.cuda.synchronize()
-        ms.append(s.elapsed_time(e))
+        ms = []
+        for _ in range(steps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            step()
+            e.record()
+            torch.cuda.synchronize()
+            ms.append(s.elapsed_time(e))
     med = float(np.median(ms))
-    return {"value": ncol / (med * 1e-3), "unit": "columns/s", "ms_per_step": med,
-            "what": "torch fp32: gather (cat) -> cuBLAS SGEMM + bias + activation per layer -> scatter (copy); library kernels, comparison only"}
+    cs = float(sum(t.double().sum().item() for t in d_out))
+    print(json.dumps({"impl": "incumbent", "value": ncol / (med * 1e-3), "unit": "columns/s", "ms_per_step": med, "steps": steps,
+                      "dtype": "f32", "checksum": cs, "config": {"workload": wl["label"]},
+                      "what": "reference runtime compiled unchanged (fortis_gemm = cuBLAS SGEMM on pre-transposed weights) per layer + "
+                              "separate bias/activation kernel; gather (cat) and scatter (copy) as torch kernels; comparison only"}))
 
 
 # -----------------------------------------------------------------------------------------------------------------
+# GPU arm
+# -----------------------------------------------------------------------------------------------------------------
+class Bench:
+    def __init__(self, args):
+        import torch
+        import fortis_b200
+        self.torch, self.fb, self.args = torch, fortis_b200, args
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        torch.cuda.set_device(self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+        self.h = fortis_b200.Host()
+        self.h.reset()
+        self.stream = torch.cuda.ExternalStream(self.h.stream())
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")     # > 126 MB L2
+
+    def to_dev(self, a):
+        return self.torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, steps, warmup, device_only=True):
+        """Per-step CUDA events on the library's stream.  Returns (max over ranks of the summed step times in ms,
+        this rank's per-step times)."""
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for s, e in ev:
+            with torch.cuda.stream(self.stream):
+                self.flush.fill_(1)              # L2 flush between timed iterations, outside the event pair
+            if not device_only:
+                torch.cuda.synchronize()         # end-to-end figures include the host's own path from an idle GPU
+            s.record(self.stream)
+            fn()
+            e.record(self.stream)
+        self.barrier()
+        ms = [s.elapsed_time(e) for s, e in ev]
+        total = float(sum(ms))
+        if self.dist is not None:
+            t = torch.tensor([total], dtype=torch.float64, device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            total = float(t.item())
+        return total, ms
+
+    def gather_floats(self, v):
+        """Every rank's value of `v` (list of floats) on every rank."""
+        if self.dist is None:
+            return [list(v)]
+        t = self.torch.tensor(list(v), dtype=self.torch.float64, device="cuda")
+        out = [self.torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [o.tolist() for o in out]
+
+    def configure(self, wl, prec, graph=True):
+        h = self.h
+        h.reset()
+        if wl["kind"] != "conv":
+            h.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"], kdist=wl["K"])
+        h.load_model(self.fb.write_blob(wl["layers"]))
+        h.option("precision", prec)
+        if wl["kind"] == "conv":
+            h.option("conv_shape", "%d,%d,%d,%d" % wl["shape"])
+        if graph:
+            h.option("graph", 1)                   # FORTIS_GRAPH: the launches of a step replay as one graph from call 2
+        h.option("checksum", 1)
+        h.option("async", 1)
+
+    # ---- the sharded configuration as one global problem --------------------------------------------------------
+    def sharded(self, steps):
+        """8 blocks of 2^20 columns (block b drawn with seed 7000 + b), FP8-E4M3 weights.  Weak: rank r runs block r.
+        Strong: the 8 blocks are split over the ranks in order.  Rank 0 then runs every block itself and the per-block
+        checksums must agree with what the owning ranks computed."""
+        from fortis_b200 import workloads
+        torch, h = self.torch, self.h
+        R, r = self.world, self.rank
+        owned = list(range(SHARD_BLOCKS * r // R, SHARD_BLOCKS * (r + 1) // R))
+        need = sorted(set(owned) | {r})
+        wl0 = None
+        dev = {}
+        for b in need:
+            wl = workloads.sharded_block(b, SHARD_COLS)
+            wl0 = wl0 or wl
+            dev[b] = ([self.to_dev(a) for a in wl["gin"]], [self.to_dev(a) for a in wl["sout"]])
+            del wl["gin"], wl["sout"]
+        self.configure(wl0, "fp8w", graph=False)
+        status = lambda: h.L.fortis_device_status()
+
+        def run_blocks(blocks):
+            for b in blocks:
+                h.step(dev[b][0], dev[b][1])
+
+        def checksums(blocks):
+            out = []
+            for b in blocks:
+                h.step_checksum()
+                h.step(dev[b][0], dev[b][1])
+                out.append(h.step_checksum())
+            return out
+        res = {}
+        for mode, blocks in (("weak", [r]), ("strong", owned)):
+            total, per = self.timed(lambda: run_blocks(blocks), steps, 3)
+            cs = checksums(blocks)
+            allcs = self.gather_floats(cs)
+            spread = self.gather_floats([min(per), float(np.median(per)), max(per)])
+            cols = SHARD_COLS * (R if mode == "weak" else SHARD_BLOCKS)
+            flop = cols * wl0["flop_per_unit"]
+            res[mode] = {"columns": cols, "columns_per_rank": SHARD_COLS * len(blocks), "value": cols * steps / (total * 1e-3),
+                         "unit": "columns/s", "ms_per_step": total / steps, "tflops": flop * steps / (total * 1e-3) / 1e12,
+                         "per_rank_step_ms_min_med_max": spread, "block_checksums": [c for rk in allcs for c in rk]}
+        if status() != 0:
+            raise SystemExit("device status %d in the sharded run" % status())
+        # the one collective: sum of the per-rank checksums of the strong run
+        local_sum = float(sum(res["strong"]["block_checksums"][SHARD_BLOCKS * r // R: SHARD_BLOCKS * (r + 1) // R]))
+        glob = local_sum
+        if self.dist is not None:
+            t = torch.tensor([local_sum], dtype=torch.float64, device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+            glob = float(t.item())
+        verified = None
+        if r == 0:
+            # single-rank pass over all 8 blocks, one at a time, reusing one set of device buffers
+            mine = []
+            for b in range(SHARD_BLOCKS):
+                if b not in dev:
+                    wl = workloads.sharded_block(b, SHARD_COLS)
+                    for d, a in zip(dev[0][0], wl["gin"]):
+                        d.copy_(torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))))
+                    src = dev[0]
+                else:
+                    src = dev[b]
+                h.step_checksum()
+                h.step(src[0], src[1])
+                mine.append(h.step_checksum())
+            want = float(sum(mine))
+            worst = max(abs(a - b) / max(1.0, abs(b)) for a, b in zip(res["strong"]["block_checksums"], mine))
+            worst_w = max(abs(a - b) / max(1.0, abs(b)) for a, b in zip(res["weak"]["block_checksums"], mine[:R]))
+            verified = {"single_rank_block_checksums": mine, "single_rank_sum": want, "allreduced_sum": glob,
+                        "rel_diff_sum": abs(glob - want) / max(1.0, abs(want)), "worst_block_rel_diff_strong": worst,
+                        "worst_block_rel_diff_weak": worst_w, "ok": bool(abs(glob - want) <= 1e-9 * max(1.0, abs(want)) and worst <= 1e-12 and worst_w <= 1e-12)}
+            if not verified["ok"]:
+                raise SystemExit("sharded run: checksums of the ranks disagree with the single-rank pass: %r" % verified)
+        res["verified"] = verified
+        res["config"] = "8 blocks x 2^20 columns, block b seeded 7000+b, 244->768x4->128, FP8-E4M3 weights (per-channel scales), bf16 activations"
+        return res
+
+    # ---- main ---------------------------------------------------------------------------------------------------
+    def run(self):
+        args, torch, h = self.args, self.torch, self.h
+        rank, world = self.rank, self.world
+        wl = make_workload(args.workload, rank, args.ncol)
+        prec = args.precision
+        is_conv = wl["kind"] == "conv"
+        self.configure(wl, prec)
+        d_in = [self.to_dev(a) for a in wl["gin"]]
+        d_out = [self.to_dev(a) for a in wl["sout"]]
+        sampler = ClockSampler(self.local) if rank == 0 else None
+        if sampler:
+            sampler.start()
+        if is_conv:
+            h.L.mlp_upload(wl["gin"][0].ctypes.data)           # input resident in HBM; every step runs the whole network
+            step_fn = lambda: h.L.mlp_forward_dev()
+        else:
+            step_fn = lambda: h.step(d_in, d_out)
+        warm = max(3, args.warmup)
+        total_ms, per = self.timed(step_fn, args.steps, warm)
+        clocks = sampler.stop() if sampler else None
+        status = h.L.fortis_device_status()
+        if status != 0:
+            raise SystemExit("device status %d: a bounded wait in the tensor-core kernel gave up" % status)
+        # checksum of ONE step (the accumulator also holds the warm-up and timed steps: drain it, run one more)
+        cs_local = 0.0
+        if not is_conv:
+            h.step_checksum()
+            step_fn()
+            cs_local = h.step_checksum()
+            want = float(sum(t.double().sum().item() for t in d_out))
+            scale = float(sum(t.double().abs().sum().item() for t in d_out))
+            if abs(cs_local - want) > 1e-9 * max(1.0, scale):
+                raise SystemExit("step checksum %r differs from the sum of the scattered arrays %r" % (cs_local, want))
+        else:
+            h.L.mlp_download(wl["sout"][0].ctypes.data)
+            cs_local = float(wl["sout"][0].astype(np.float64).sum())
+        units = wl["units"] * world
+        value = units * args.steps / (total_ms * 1e-3)
+        kernel_ms = float(np.median(per))
+        spread = self.gather_floats([min(per), kernel_ms, max(per)])
+
+        e2e = None
+        if not args.no_e2e:
+            # host arrays: the library pins them once, then every step copies all inputs H2D and all outputs D2H
+            h.option("async", 0)
+            e_steps = max(3, min(args.steps, 20))
+            e_fn = (lambda: h.forward(wl["gin"][0], wl["sout"][0])) if is_conv else (lambda: h.step(wl["gin"], wl["sout"]))
+            e_total, _ = self.timed(e_fn, e_steps, 3, device_only=False)
+            e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
+                   "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
+        cs_global = cs_local
+        if self.dist is not None:
+            t = torch.tensor([cs_local], dtype=torch.float64, device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)               # the one collective: per-rank checksums
+            cs_global = float(t.item())
+        sharded = None
+        if (world > 1 or args.sharded) and not args.no_sharded and wl["kind"] == "column":
+            del d_in, d_out
+            sharded = self.sharded(max(3, min(args.steps, 10)))
+
+        if rank == 0:
+            peaks = {}
+            try:
+                peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            except Exception:
+                pass
+            kind = wl["kind"]
+            if kind == "stencil":
+                peak, src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
+                ach = wl["units"] * wl["bytes_per_unit"] / (kernel_ms * 1e-3) / 1e9
+                roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": src}
+            else:
+                peak, src = (peaks.get("bf16_tflops"), "measured burst") if peaks.get("bf16_tflops") else (1590.0, "fallback")
+                ach = wl["units"] * wl["flop_per_unit"] / (kernel_ms * 1e-3) / 1e12
+                roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": src}
+            traffic = None
+            try:
+                traffic = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get("%s_%s" % (args.workload, prec))
+            except Exception:
+                pass
+            roof["traffic"] = traffic
+            roof["kernel_ms"] = kernel_ms
+            cpu = None if (args.no_cpu or is_conv or world > 1) else time_cpu(wl)      # the CPU baseline is an N = 1 figure
+            incumbent = None
+            if kind == "column" and world == 1 and not args.no_incumbent and wl["units"] <= 1 << 18:
+                try:
+                    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "incumbent", "--workload", args.workload,
+                                          "--steps", "10"] + (["--ncol", str(args.ncol)] if args.ncol else []),
+                                         capture_output=True, text=True, timeout=600).stdout.strip().splitlines()
+                    incumbent = json.loads(out[-1]) if out else None
+                except Exception as ex:
+                    incumbent = {"unavailable": repr(ex)}
+            tc = prec != "fp32"
+            launches_per_step = (len(wl["layers"]) + (1 if tc else 0)) if is_conv else 2 if (tc or kind == "stencil") else (3 + len(wl["layers"]))
+            line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
+                    "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                    "vs_baseline": None,
+                    "dtype": {"bf16": "bf16", "fp16": "f16", "fp32": "f32", "fp8w": "bf16 (fp8-e4m3 weights)"}[prec],
+                    "data": "synthetic",
+                    "config": {"workload": wl["label"], "columns_per_gpu": wl["units"], "precision": prec,
+                               "l2": "flushed between timed steps (256 MB write on the same stream)",
+                               "parallelism": "contiguous column block per rank, no data-path collective",
+                               "replay": "CUDA graph from the second call (FORTIS_GRAPH)"},
+                    "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "roofline": roof, "cpu_baseline": cpu,
+                    "incumbent_gpu_library_path": incumbent, "clocks": clocks, "checksum": cs_global,
+                    "per_rank_step_ms_min_med_max": spread, "sharded": sharded}
+            print(json.dumps(line))
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
-        return
-    import torch
-    import fortis_b200
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    wl = make_workload(args.workload, rank, args.ncol)
-    prec = args.precision
-    h = fortis_b200.Host()
-    h.reset()
-    is_conv = wl["kind"] == "conv"
-    if not is_conv:
-        h.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"], kdist=wl["K"])
-    h.load_model(fortis_b200.write_blob(wl["layers"]))
-    h.option("precision", prec)
-    if is_conv:
-        h.option("conv_shape", "%d,%d,%d,%d" % wl["shape"])
-        h.option("graph", 1)                               # FORTIS_GRAPH: the 14 launches of a step replay as one graph
-    h.option("checksum", 1)
-    h.option("async", 1)
-    stream = torch.cuda.ExternalStream(h.stream())
-    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
-    d_in = [to_dev(a) for a in wl["gin"]]
-    d_out = [to_dev(a) for a in wl["sout"]]
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")     # > 126 MB L2
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-        for s, e in ev:
-            flush.fill_(1)                       # L2 flush between timed iterations (outside the event pair)
-            torch.cuda.synchronize()
-            s.record(stream)
-            fn()
-            e.record(stream)
-        barrier()
-        ms = [s.elapsed_time(e) for s, e in ev]
-        total = float(sum(ms))
-        if dist is not None:
-            t = torch.tensor([total], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            total = float(t.item())
-        return total, ms
-
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    if is_conv:
-        h.L.mlp_upload(wl["gin"][0].ctypes.data)           # input resident in HBM; every step runs the whole network
-        step_fn = lambda: h.L.mlp_forward_dev()
+    elif args.impl == "incumbent":
+        run_incumbent(args)
     else:
-        step_fn = lambda: h.step(d_in, d_out)
-    total_ms, per = timed(step_fn, args.steps, max(3, args.warmup))
-    clocks = sampler.stop() if sampler else None
-    status = h.L.fortis_device_status()
-    if status != 0:
-        raise SystemExit("device status %d: a bounded wait in the tensor-core kernel gave up" % status)
-    cs_local = h.step_checksum() if not is_conv else 0.0
-    if is_conv:
-        h.L.mlp_download(wl["sout"][0].ctypes.data)
-        cs_local = float(wl["sout"][0].astype(np.float64).sum())
-    units = wl["units"] * world
-    value = units * args.steps / (total_ms * 1e-3)
-    kernel_ms = float(np.median(per))
-
-    e2e = None
-    if not args.no_e2e:
-        # host arrays: the library pins them once, then every step copies all inputs H2D and all outputs D2H
-        h.option("async", 0)
-        e_steps = max(3, min(args.steps, 20))
-        e_fn = (lambda: h.forward(wl["gin"][0], wl["sout"][0])) if is_conv else (lambda: h.step(wl["gin"], wl["sout"]))
-        e_total, _ = timed(e_fn, e_steps, 3)
-        e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
-               "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
-    incumbent = None
-    if wl["kind"] == "column" and world == 1 and not args.no_incumbent and wl["units"] <= 1 << 18:
-        incumbent = time_incumbent(torch, wl, d_in, d_out, flush)
-    cs_global = cs_local
-    if dist is not None:
-        t = torch.tensor([cs_local], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)               # the one collective: per-rank checksums
-        cs_global = float(t.item())
-
-    if rank == 0:
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except Exception:
-            pass
-        kind = wl["kind"]
-        if kind == "stencil":
-            peak, src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
-            ach = wl["units"] * BYTES_PER_COL[kind] / (kernel_ms * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": src}
-        else:
-            peak, src = (peaks.get("bf16_tflops"), "measured burst") if peaks.get("bf16_tflops") else (1590.0, "fallback")
-            ach = wl["units"] * FLOP_PER_COL[kind] / (kernel_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "peak_source": src}
-        traffic = None
-        try:
-            traffic = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get("%s_%s" % (args.workload, prec))
-        except Exception:
-            pass
-        roof["traffic"] = traffic
-        roof["kernel_ms"] = kernel_ms
-        cpu = None if (args.no_cpu or is_conv or world > 1) else time_cpu(wl)      # the CPU baseline is an N = 1 figure
-        launches_per_step = (len(wl["layers"]) + (1 if prec != "fp32" else 0)) if is_conv else 2 if (prec != "fp32" or kind == "stencil") else (2 + len(wl["layers"]))
-        line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
-                "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": {"bf16": "bf16", "fp32": "f32", "fp8w": "bf16 (fp8-e4m3 weights)"}[prec],
-                "data": "synthetic",
-                "config": {"workload": wl["label"], "columns_per_gpu": wl["units"], "precision": prec, "l2": "flushed between timed steps (256 MB write)",
-                           "parallelism": "contiguous column block per rank, no data-path collective"},
-                "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "roofline": roof, "cpu_baseline": cpu,
-                "incumbent_gpu_library_path": incumbent, "clocks": clocks, "checksum": cs_global}
-        print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+        Bench(args).run()
 
 
 if __name__ == "__main__":

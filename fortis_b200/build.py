@@ -16,7 +16,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 
 def _deps():
-    return [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "fortis_b200.h")]
+    inc = os.path.join(HERE, "..", "include")
+    return [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(inc, f) for f in os.listdir(inc)]
 
 
 def build(force=False, verbose=False):
@@ -32,7 +33,7 @@ def build(force=False, verbose=False):
         hdr_newest = max(os.path.getmtime(p) for p in _deps() if p.endswith((".h", ".cuh")))
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(srcp), hdr_newest):
             return obj
-        extra = os.environ.get("FORTIS_NVCC_FLAGS", "").split()       # e.g. -DFORTIS_TC_PROFILE for the cycle counters
+        extra = os.environ.get("FORTIS_NVCC_FLAGS", "").split()       # extra nvcc flags, e.g. -DFORTIS_TC_PROF (cycle counters)
         cmd = ["nvcc"] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", srcp, "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode:

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "../../include/fortis_b200.h"
+#include "../../include/fortis_b200_test.h"
 #include "fortis_device.cuh"
 #include "fortis_kernels.h"
 #include "fortis_model.h"
@@ -55,6 +56,8 @@ cudaStream_t stream() {
   return g_stream;
 }
 
+// The policy restates runtime/fortis_rt.c:14-40 (it IS the contract of fortis_alloc / fortis_free): 256 slots, best
+// fit among released buffers, cudaMalloc on a miss, release every unused buffer and retry once, 0 + message on failure.
 constexpr int kPool = 256;
 struct PoolSlot { long n; void* p; int used; } g_pool[kPool];
 
@@ -320,7 +323,7 @@ void ensure_model() {
     if (s.precision != PREC_F32) {
       std::string err;
       s.tc = tc_model_create(s.model, s.precision, st, &err);
-      if (!s.tc) throw std::runtime_error("precision " + std::string(s.precision == PREC_BF16 ? "bf16" : "fp8w") +
+      if (!s.tc) throw std::runtime_error("precision " + std::string(s.precision == PREC_BF16 ? "bf16" : s.precision == PREC_FP16 ? "fp16" : "fp8w") +
                                           " needs the tensor-core kernel, which cannot take this model: " + err);
     }
   } else if (s.model.is_conv()) {
@@ -517,6 +520,7 @@ void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
 struct StepArgs {
   bool use_gather = false;      // model input comes from the gather plan (else din)
   bool fuse_scatter = false;    // outputs go straight to the host arrays (all planes)
+  bool unfused = false;         // run gather, forward and scatter as separate kernels (gather and scatter share memory)
   ArrayTable TG{}, TS{};
   long long rows = 0;
 };
@@ -565,6 +569,17 @@ bool small_fast_operands(const StepArgs& A, const RowGeom& g, SmallFast* F) {
   return true;
 }
 
+// the standalone scatter of a step; with option "checksum" its stores are summed like those of the fused kernels
+void scatter_with_checksum(const StepArgs& A, const RowGeom& g) {
+  Session& s = S();
+  cudaStream_t st = stream();
+  double* partials = nullptr;
+  const int grid = scatter_grid(g.count * g.nk);
+  if (s.want_checksum) { ensure_aux(grid); partials = s.d_partials; }
+  launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, A.TS, g, s.dout, st, partials);
+  if (partials) launch_fold(s.d_partials, grid, s.d_sum, 1, st);
+}
+
 void run_step_kernels(const StepArgs& A) {
   Session& s = S();
   cudaStream_t st = stream();
@@ -577,14 +592,15 @@ void run_step_kernels(const StepArgs& A) {
       throw std::runtime_error(err);
     return;
   }
-  const bool fused_gather = A.use_gather && s.fuse;
+  const bool fuse = s.fuse && !A.unfused;
+  const bool fused_gather = A.use_gather && fuse;
   if (s.precision != PREC_F32) {
     // The tensor-core kernel fuses the gather / scatter when the descriptor is in its table-driven class (fp32
     // arrays, no lifted expressions or scalars, at most two stride classes, <= 256 inputs / <= 128 outputs);
     // other descriptors run the bit-exact standalone gather / scatter kernels around it.
     TcLaunch L{};
-    const bool fuse_in = A.use_gather && s.fuse && s.G.fast && s.model.n_in() <= 256;
-    const bool fuse_out = A.fuse_scatter && s.fuse && s.S.fast && s.model.n_out() <= 128;
+    const bool fuse_in = A.use_gather && fuse && s.G.fast && s.model.n_in() <= 256;
+    const bool fuse_out = A.fuse_scatter && fuse && s.S.fast && s.model.n_out() <= 128;
     if (fuse_in) { L.GP = s.G.hdr; L.slots = (const Access*)s.G.items; L.TG = A.TG; L.fast_in = 1; std::memcpy(L.cin, s.G.cls, sizeof L.cin); }
     else {
       if (A.use_gather) launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, A.TG, g, s.din, st);
@@ -600,7 +616,7 @@ void run_step_kernels(const StepArgs& A) {
     std::string err;
     if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
     if (L.partials) launch_fold(s.d_partials, tc_grid(rows), s.d_sum, 1, st);
-    if (A.fuse_scatter && !fuse_out) launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, A.TS, g, s.dout, st);
+    if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);
     return;
   }
   if (fused_gather && s.small_ok) {
@@ -629,12 +645,13 @@ void run_step_kernels(const StepArgs& A) {
                       l == nl - 1 ? s.d_out_mul : nullptr, l == nl - 1 ? s.d_relu_mask : nullptr, st);
     src = dst;
   }
-  if (A.fuse_scatter) launch_scatter(s.S.hdr, (const StoreTarget*)s.S.items, s.S.h.n, A.TS, g, s.dout, st);
+  if (A.fuse_scatter) scatter_with_checksum(A, g);
 }
 
 std::string step_key(const StepArgs& A) {
   std::string k((const char*)&A.use_gather, sizeof(bool));
   k.append((const char*)&A.fuse_scatter, sizeof(bool));
+  k.append((const char*)&A.unfused, sizeof(bool));
   k.append((const char*)&A.rows, sizeof A.rows);
   if (A.use_gather) k.append((const char*)&A.TG, sizeof A.TG);
   if (A.fuse_scatter) k.append((const char*)&A.TS, sizeof A.TS);
@@ -672,6 +689,16 @@ void run_step(const StepArgs& A) {
 void prepare(long long* rows_out) {
   ensure_plans();
   ensure_model();
+  Session& s0 = S();
+  if (s0.model.is_mlp()) {
+    // descriptors and model arrive independently: a pair that does not fit would index past the model's buffers
+    if (s0.G.h.ok && s0.G.h.n != s0.model.n_in())
+      throw std::runtime_error("the gather descriptor produces " + std::to_string(s0.G.h.n) + " inputs per row, the model takes " +
+                               std::to_string(s0.model.n_in()));
+    if (s0.S.h.ok && s0.S.h.n != s0.model.n_out())
+      throw std::runtime_error("the scatter descriptor consumes " + std::to_string(s0.S.h.n) + " outputs per row, the model produces " +
+                               std::to_string(s0.model.n_out()));
+  }
   const long long rows = model_rows();
   ensure_buffers(rows);
   *rows_out = rows;
@@ -786,7 +813,16 @@ void do_scatter(const int* iargs, int nint, void* const* ptrs, int narr) {
   if (!s.async) cudaStreamSynchronize(st);
 }
 
-void do_step(void* const* gptrs, int ng, void* const* sptrs, int ns) {
+// byte ranges [lo, hi) of two arrays of a call overlap
+bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb) {
+  const char *a0 = (const char*)a, *b0 = (const char*)b;
+  return a0 < b0 + nb && b0 < a0 + na;
+}
+
+// The fused step: gather -> forward -> scatter of every plane in one launch.  `iargs` are the enclosing-loop
+// indices (1-based) that select the plane of arrays with "v" subscripts when the loop is NOT k-distributed; a
+// k-distributed loop takes none (all planes klo .. klo+nk-1 are processed).
+void do_step(const int* iargs, int nint, void* const* gptrs, int ng, void* const* sptrs, int ns) {
   Session& s = S();
   long long rows;
   prepare(&rows);
@@ -797,14 +833,41 @@ void do_step(void* const* gptrs, int ng, void* const* sptrs, int ns) {
       if (s.S.h.arrays[t.a.array].vdims.empty())
         throw std::runtime_error("fortis_step: stored array " + s.S.h.arrays[t.a.array].name +
                                  " has no plane dimension; the host consumes it between planes, use fortis_scatter per plane");
+  const bool multi = s.loop.kdist;
+  if (!multi) {
+    // planes are chosen by the integer arguments, as in fortis_gather / fortis_scatter: every argument a used
+    // array's "v" subscript names must be there, else the plane would be a guess
+    int need = 0;
+    for (PlanDev* P : {&s.G, &s.S})
+      for (auto& a : P->h.arrays)
+        if (a.used) for (auto& t : a.vterms) need = t.first + 1 > need ? t.first + 1 : need;
+    if (nint < need)
+      throw std::runtime_error("fortis_step: the descriptors select a plane by " + std::to_string(need) +
+                               " enclosing-loop index argument(s) and the loop is not k-distributed; pass them first");
+  }
   cudaStream_t st = stream();
-  int args[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  int args[8];
+  for (int i = 0; i < 8; i++) args[i] = i < nint ? iargs[i] : 1;
   StepArgs A;
   A.rows = rows; A.use_gather = true; A.fuse_scatter = true;
-  bind_arrays(s.G, gptrs, args, 0, true, true, &A.TG);
-  bind_arrays(s.S, sptrs, args, 0, true, true, &A.TS);
+  bind_arrays(s.G, gptrs, args, nint, multi, true, &A.TG);
+  bind_arrays(s.S, sptrs, args, nint, multi, true, &A.TS);
+  // A fused kernel reads its inputs and writes its outputs in the same launch.  When a device-resident gather array
+  // shares memory with a device-resident stored array, a stencil would read neighbours another thread is
+  // overwriting; the reference is well-defined there because gather and scatter work on separate staging copies.
+  // Such a call runs as separate gather, forward and scatter kernels (host-resident arrays are staged separately
+  // anyway).
+  for (size_t gi = 0; gi < s.G.h.arrays.size() && !A.unfused; gi++) {
+    if (!s.G.on_dev[gi] || !s.G.h.arrays[gi].used) continue;
+    const ArrayInfo& ga = s.G.h.arrays[gi];
+    for (size_t si = 0; si < s.S.h.arrays.size(); si++) {
+      if (!s.S.on_dev[si] || !s.S.h.written[si]) continue;
+      const ArrayInfo& sa = s.S.h.arrays[si];
+      if (ranges_overlap(gptrs[gi], (size_t)ga.total * elt_size(ga.elt), sptrs[si], (size_t)sa.total * elt_size(sa.elt))) { A.unfused = true; break; }
+    }
+  }
   run_step(A);
-  download_stores(s.S, args, 0, true);
+  download_stores(s.S, args, nint, multi);
   if (!s.async) cudaStreamSynchronize(st);
 }
 
@@ -894,7 +957,8 @@ int fortis_set_option(const char* key, const char* value) {
     if (v == "fp32" || v == "f32") p = PREC_F32;
     else if (v == "bf16") p = PREC_BF16;
     else if (v == "fp8w") p = PREC_FP8W;
-    else throw std::runtime_error("precision must be fp32, bf16 or fp8w");
+    else if (v == "fp16" || v == "f16") p = PREC_FP16;
+    else throw std::runtime_error("precision must be fp32, bf16, fp16 or fp8w");
     if (p != s.precision) { s.precision = p; free_model_dev(); }
   } else if (k == "fuse") { s.fuse = v != "0"; drop_graph(); }
   else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
@@ -970,7 +1034,13 @@ void fortis_scatterv(const int* iargs, int nint, void* const* arrays, int narray
 
 void fortis_stepv(const void* const* ga, int ng, void* const* sa, int ns) {
   FORTIS_TRY
-  do_step((void* const*)ga, ng, sa, ns);
+  do_step(nullptr, 0, (void* const*)ga, ng, sa, ns);
+  FORTIS_CATCH(return)
+}
+
+void fortis_stepvi(const int* iargs, int nint, const void* const* ga, int ng, void* const* sa, int ns) {
+  FORTIS_TRY
+  do_step(iargs, nint, (void* const*)ga, ng, sa, ns);
   FORTIS_CATCH(return)
 }
 
@@ -1000,17 +1070,18 @@ void fortis_scatter(long a0, ...) {
   FORTIS_CATCH(return)
 }
 
-void fortis_step(const void* first, ...) {
+void fortis_step(long a0, ...) {
   FORTIS_TRY
   ensure_plans();
   Session& s = S();
   if (!s.G.h.ok || !s.S.h.ok) throw std::runtime_error("fortis_step: needs both a gather and a scatter descriptor");
-  std::vector<void*> g, sc;
-  va_list ap; va_start(ap, first);
-  for (size_t i = 0; i < s.G.h.arrays.size(); i++) g.push_back(i == 0 ? (void*)first : va_arg(ap, void*));
+  // [the gather entry's integer arguments unless the loop is k-distributed], gather arrays, scatter arrays
+  std::vector<int> ints; std::vector<void*> g, sc;
+  va_list ap; va_start(ap, a0);
+  collect_args(s.G, s.loop.kdist, a0, ap, true, &ints, &g);
   for (size_t i = 0; i < s.S.h.arrays.size(); i++) sc.push_back(va_arg(ap, void*));
   va_end(ap);
-  do_step(g.data(), (int)g.size(), sc.data(), (int)sc.size());
+  do_step(ints.data(), (int)ints.size(), g.data(), (int)g.size(), sc.data(), (int)sc.size());
   FORTIS_CATCH(return)
 }
 
@@ -1058,7 +1129,7 @@ void mlp_forward(void* in, void* out) {
     // (driver/fortis_shim.py:123-133); transpose + cast + lifted expressions run fused around the model
     void* gp[1] = {in};
     void* sp[1] = {out};
-    do_step(gp, 1, sp, 1);
+    do_step(nullptr, 0, gp, 1, sp, 1);
     cudaStreamSynchronize(stream());
     return;
   }
@@ -1134,14 +1205,32 @@ void fortis_unpack(void* o, int col) {
 void fortis_gemm(float* Aa, float* A, long Ao, long As0, long As1, long At0, long At1,
                  float* Wa, float* W, long Wo, long Ws0, long Ws1, long Wt0, long Wt1,
                  float* Ca, float* C, long Co, long Cs0, long Cs1, long Ct0, long Ct1, long B, long N, long K) {
-  (void)Aa; (void)As0; (void)As1; (void)At0; (void)At1; (void)Wa; (void)Ws0; (void)Ws1; (void)Wt0; (void)Wt1;
-  (void)Ca; (void)Cs0; (void)Cs1; (void)Ct0; (void)Ct1;
+  (void)Aa; (void)As0; (void)As1; (void)Wa; (void)Ws0; (void)Ws1; (void)Ca; (void)Cs0; (void)Cs1;
+  // The kernels (like the reference's cuBLAS call) address dense row-major operands; a strided memref would be
+  // computed wrong without a word, so it is refused instead and C is left untouched.
+  auto dense = [](long t0, long t1, long rows, long cols) { return (cols <= 1 || t1 == 1) && (rows <= 1 || t0 == cols); };
+  if (!dense(At0, At1, B, K) || !dense(Wt0, Wt1, N, K) || !dense(Ct0, Ct1, B, N)) {
+    std::fprintf(stderr, "fortis_gemm: operands must be dense row-major (A %ldx%ld strides %ld,%ld; W %ldx%ld strides %ld,%ld; C %ldx%ld strides %ld,%ld)\n",
+                 B, K, At0, At1, N, K, Wt0, Wt1, B, N, Ct0, Ct1);
+    return;
+  }
   launch_linear_f32(A + Ao, W + Wo, nullptr, C + Co, B, (int)N, (int)K, ACT_NONE, 0.f, nullptr, nullptr, nullptr, stream());
+}
+
+// dense NCDHW-style strides of a rank-5 memref (dimensions of extent 1 may carry any stride)
+static bool dense5(const long* t, long n0, long n1, long n2, long n3, long n4) {
+  const long want[5] = {n1 * n2 * n3 * n4, n2 * n3 * n4, n3 * n4, n4, 1}, ext[5] = {n0, n1, n2, n3, n4};
+  for (int d = 0; d < 5; d++) if (ext[d] > 1 && t[d] != want[d]) return false;
+  return true;
 }
 
 static void conv3d_entry(const char* who, float* x, long xo, float* w, long wo, float* y, long yo, long N, long C, long Din, long Hin,
                          long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout, long sd, long sh, long sw,
-                         long pd, long ph, long pw) {
+                         long pd, long ph, long pw, const long* xt, const long* wt, const long* yt) {
+  if (!dense5(xt, N, C, Din, Hin, Win) || !dense5(wt, F, C, KD, KH, KW) || !dense5(yt, N, F, Dout, Hout, Wout)) {
+    std::fprintf(stderr, "%s: operands must be dense NCDHW / FCKKK memrefs\n", who);
+    return;
+  }
   if (sd != 1 || sh != 1 || sw != 1 || KD != KH || KD != KW || pd != ph || pd != pw || Dout != Din + 2 * pd - KD + 1 ||
       Hout != Hin + 2 * ph - KH + 1 || Wout != Win + 2 * pw - KW + 1) {
     std::fprintf(stderr, "%s: unsupported shape\n", who);
@@ -1157,10 +1246,10 @@ void fortis_conv3d(float* xa, float* x, long xo, long x0, long x1, long x2, long
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
                    long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
                    long sd, long sh, long sw, long pd, long ph, long pw) {
-  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)xt0; (void)xt1; (void)xt2; (void)xt3; (void)xt4;
-  (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; (void)wt0; (void)wt1; (void)wt2; (void)wt3; (void)wt4;
-  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; (void)yt0; (void)yt1; (void)yt2; (void)yt3; (void)yt4;
-  conv3d_entry("fortis_conv3d", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw);
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4;
+  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4;
+  const long xt[5] = {xt0, xt1, xt2, xt3, xt4}, wt[5] = {wt0, wt1, wt2, wt3, wt4}, yt[5] = {yt0, yt1, yt2, yt3, yt4};
+  conv3d_entry("fortis_conv3d", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt, yt);
 }
 
 void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
@@ -1168,10 +1257,10 @@ void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
                    long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
                    long sd, long sh, long sw, long pd, long ph, long pw) {
-  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)xt0; (void)xt1; (void)xt2; (void)xt3; (void)xt4;
-  (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; (void)wt0; (void)wt1; (void)wt2; (void)wt3; (void)wt4;
-  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; (void)yt0; (void)yt1; (void)yt2; (void)yt3; (void)yt4;
-  conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw);
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4;
+  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4;
+  const long xt[5] = {xt0, xt1, xt2, xt3, xt4}, wt[5] = {wt0, wt1, wt2, wt3, wt4}, yt[5] = {yt0, yt1, yt2, yt3, yt4};
+  conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt, yt);
 }
 
 int fortis_copy_to_host(void* dst, const void* dev, long nbytes) {

@@ -122,6 +122,17 @@ void launch_conv(const float* x, const float* wt, const float* bias, const float
   conv3d_f32_kernel<<<grid, 256, 0, s>>>(x, wt, bias, residual, y, g, act, slope);
 }
 
+// the same repack on the device, for weights that only exist there (the memref entry)
+__global__ void repack_weights_kernel(const float* __restrict__ w, float* __restrict__ out, int F, int C, int taps) {
+  const size_t n = (size_t)F * C * taps;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;     // index into out: [tap][C][F]
+  if (i >= n) return;
+  const int f = (int)(i % F);
+  const int c = (int)((i / F) % C);
+  const int t = (int)(i / ((size_t)F * C));
+  out[i] = w[((size_t)f * C + c) * taps + t];
+}
+
 // torch layout (F, C, K, K, K) -> [tap][C][F]
 std::vector<float> repack_weights(const float* w, int F, int C, int K) {
   const int taps = K * K * K;
@@ -155,12 +166,12 @@ int conv_model_status(ConvModel* m) { return m && m->tcm ? conv_tc_status(m->tcm
 
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
   (void)s;
-  if (precision == PREC_FP8W) { if (err) *err = "conv3d networks run in fp32 or bf16"; return nullptr; }
+  if (precision == PREC_FP8W) { if (err) *err = "conv3d networks run in fp32, bf16 or fp16"; return nullptr; }
   ConvModel* m = new ConvModel();
-  if (precision == PREC_BF16) {
+  if (precision == PREC_BF16 || precision == PREC_FP16) {
     std::string why;
-    m->tcm = conv_tc_create(M, &why);
-    if (!m->tcm) { if (err) *err = "precision bf16 needs the tensor-core conv kernel, which cannot take this model: " + why; delete m; return nullptr; }
+    m->tcm = conv_tc_create(M, precision == PREC_FP16, &why);
+    if (!m->tcm) { if (err) *err = "precision bf16 / fp16 needs the tensor-core conv kernel, which cannot take this model: " + why; delete m; return nullptr; }
     return m;
   }
   for (auto& L : M.layers) {
@@ -230,19 +241,31 @@ bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D,
                   cudaStream_t s, std::string* err) {
   // weights are constants of the caller: repack each distinct (pointer, shape) once, as the reference caches its
   // transposed GEMM weights (runtime/fortis_rt.c:55-66)
-  struct Cached { const float* w; int F, C, K; float* wt; };
+  // The repack runs as a kernel on the caller's stream (no synchronisation, no host round trip).  The cache holds 64
+  // entries; when it is full the oldest entry is replaced and its buffer reused or freed.  A weight seen for the
+  // first time needs a buffer: that cannot happen while the stream is being captured into a graph, so such a call
+  // is refused (the reference captures on the second call for the same reason: the first call allocates).
+  struct Cached { const float* w; int F, C, K; float* wt; size_t cap; };
   static std::vector<Cached> cache;
+  static size_t victim = 0;
   float* wt = nullptr;
   for (auto& c : cache) if (c.w == w && c.F == F && c.C == C && c.K == K) wt = c.wt;
   if (!wt) {
     const size_t n = (size_t)F * C * K * K * K;
-    std::vector<float> hw(n);
-    cudaStreamSynchronize(s);
-    if (cudaMemcpy(hw.data(), w, n * 4, cudaMemcpyDeviceToHost) != cudaSuccess) { if (err) *err = "cannot read the conv weights"; return false; }
-    std::vector<float> r = repack_weights(hw.data(), F, C, K);
-    if (cudaMalloc(&wt, n * 4) != cudaSuccess) { if (err) *err = "out of device memory for conv weights"; return false; }
-    cudaMemcpy(wt, r.data(), n * 4, cudaMemcpyHostToDevice);
-    if (cache.size() < 64) cache.push_back({w, F, C, K, wt});
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(s, &cs);
+    if (cs != cudaStreamCaptureStatusNone) { if (err) *err = "conv weights seen for the first time during graph capture; run one eager call first"; return false; }
+    Cached* slot = nullptr;
+    if (cache.size() < 64) { cache.push_back({nullptr, 0, 0, 0, nullptr, 0}); slot = &cache.back(); }
+    else { slot = &cache[victim]; victim = (victim + 1) % cache.size(); }
+    if (slot->cap < n) {
+      if (slot->wt) { cudaStreamSynchronize(s); cudaFree(slot->wt); slot->wt = nullptr; slot->cap = 0; }
+      if (cudaMalloc(&slot->wt, n * 4) != cudaSuccess) { slot->w = nullptr; if (err) *err = "out of device memory for conv weights"; return false; }
+      slot->cap = n;
+    }
+    slot->w = w; slot->F = F; slot->C = C; slot->K = K;
+    wt = slot->wt;
+    repack_weights_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(w, wt, F, C, K * K * K);
   }
   ConvGeom g;
   g.N = N; g.D = D; g.H = H; g.W = W; g.C = C; g.F = F; g.K = K; g.pad = pad;

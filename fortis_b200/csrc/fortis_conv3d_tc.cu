@@ -40,6 +40,7 @@
 // activation and writes the real channels of interior voxels as fp32.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -68,7 +69,20 @@ constexpr int kResW = 9 * 96 * kC * 2;       // 108 KB: this CTA's half of all 2
 constexpr int kConvThreads = 320;           // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int kConvSmem = kResW + kRingBytes + 256 + kXchBytes;
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators (each 3 * NOUT wide)
-template <int NOUT> struct ConvIdesc { static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT); };   // the pair's M = 256
+// the pair's M = 256; operand format code 1 = bf16, 0 = IEEE half (bits 7-9 for A, 10-12 for B)
+template <int NOUT, bool F16> struct ConvIdesc {
+  static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT) & ~(F16 ? ((1u << 7) | (1u << 10)) : 0u);
+};
+// the 16-bit storage format of activations and weights: bf16 (range of fp32, 8 significant bits) or IEEE half (11
+// significant bits, values beyond 65504 overflow)
+template <bool F16> __device__ __forceinline__ uint32_t cpack16(float lo, float hi) {
+  if constexpr (F16) { const __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t*>(&v); }
+  else return pack_bf16(lo, hi);
+}
+template <bool F16> __device__ __forceinline__ float2 cunpack16(uint32_t u) {
+  if constexpr (F16) return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  else return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
 constexpr int kEdgeC = 16;                   // first layer: input channels kept; last layer: output channels computed
 enum { CST_FULL = 11, CST_EMPTY = 12, CST_ACC_FULL = 13, CST_ACC_EMPTY = 14, CST_WEIGHTS = 15, CST_ALIGN = 16 };
 
@@ -98,9 +112,9 @@ __device__ __forceinline__ void cprof_add(long long* prof, int slot, long long* 
 // KSTEPS: 16-wide k steps issued per (kd, kh) group (4 = all 64 input channels, 1 = only the first 16);  NOUT: output
 // channels (weight rows per tap);  LAST: write fp32 NDHWC instead of the padded bf16 volume.
 // Launched as clusters of two CTAs (cta_group::2): the leader's MMA warp issues for both.
-template <int KSTEPS, int NOUT, bool LAST>
+template <int KSTEPS, int NOUT, bool LAST, bool F16>
 __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid_constant__ ConvTcParams P) {
-  constexpr uint32_t kIdescN = ConvIdesc<NOUT>::value;            // M = 256 (128 rows per CTA), N = 3 * NOUT
+  constexpr uint32_t kIdescN = ConvIdesc<NOUT, F16>::value;            // M = 256 (128 rows per CTA), N = 3 * NOUT
   constexpr int kHalfRows = 3 * NOUT / 2;                         // weight rows of one (kd, kh) group held by each CTA
   constexpr int kHalfBytes = kHalfRows * kC * 2;                  // 12 KB (3 KB for the last layer)
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -305,9 +319,9 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
         if (use_skip) {
 #pragma unroll
           for (int h = 0; h < CW / 8; h++) {
-            const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sk[h]);
+            const uint32_t* s2 = reinterpret_cast<const uint32_t*>(&sk[h]);
 #pragma unroll
-            for (int e = 0; e < 4; e++) { const float2 f = __bfloat1622float2(s2[e]); v[8 * h + 2 * e] += f.x; v[8 * h + 2 * e + 1] += f.y; }
+            for (int e = 0; e < 4; e++) { const float2 f = cunpack16<F16>(s2[e]); v[8 * h + 2 * e] += f.x; v[8 * h + 2 * e + 1] += f.y; }
           }
         }
         if (nuse_skip) {                                           // these registers are free again: next tile's residual row
@@ -323,7 +337,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
             for (int e = 0; e < 4; e++) {
               const float x0 = interior ? fmaxf(v[8 * h + 2 * e], v[8 * h + 2 * e] * P.slope) : 0.f;
               const float x1 = interior ? fmaxf(v[8 * h + 2 * e + 1], v[8 * h + 2 * e + 1] * P.slope) : 0.f;
-              pk[e] = pack_bf16(x0, x1);
+              pk[e] = cpack16<F16>(x0, x1);
             }
             dst[h] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           }
@@ -347,6 +361,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
 // ---- network input: fp32 NDHWC with C <= 16 channels -> the first 16 channels (32 bytes) of the padded bf16 rows; the
 // border rows and the channels beyond 16 of this buffer are never written (zero from allocation; the first layer's
 // MMAs read only the first 16 channels)
+template <bool F16>
 __global__ void __launch_bounds__(256) conv_pack_input_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                                               int N, int D, int H, int W, int C) {
   const long long nvox = (long long)N * D * H * W;
@@ -358,7 +373,7 @@ __global__ void __launch_bounds__(256) conv_pack_input_kernel(const float* __res
     for (int c = 0; c < 16; c++) f[c] = c < C ? __ldg(x + v * C + c) : 0.f;
     uint32_t pk[8];
 #pragma unroll
-    for (int e = 0; e < 8; e++) pk[e] = pack_bf16(f[2 * e], f[2 * e + 1]);
+    for (int e = 0; e < 8; e++) pk[e] = cpack16<F16>(f[2 * e], f[2 * e + 1]);
     uint4* dst = reinterpret_cast<uint4*>(out + p * kC);
     dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
@@ -410,6 +425,13 @@ uint16_t to_bf16(float f) {
   return (uint16_t)(u >> 16);
 }
 
+uint16_t to_f16(float f) {
+  const __half h = __float2half_rn(f);
+  uint16_t u;
+  std::memcpy(&u, &h, 2);
+  return u;
+}
+
 float slope_of(const LayerHost& L) { return L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope; }
 
 }  // namespace
@@ -424,6 +446,7 @@ struct ConvTcModel {
   long long P = 0;
   int shape[4] = {0, 0, 0, 0};
   int* status = nullptr;
+  bool f16 = false;                                               // operands and stored activations are IEEE half instead of bf16
 };
 
 bool conv_tc_supported(const ModelHost& M, std::string* why) {
@@ -451,10 +474,11 @@ void conv_tc_destroy(ConvTcModel* m) {
   delete m;
 }
 
-ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
+ConvTcModel* conv_tc_create(const ModelHost& M, bool f16, std::string* err) {
   std::string why;
   if (!conv_tc_supported(M, &why)) { if (err) *err = why; return nullptr; }
   ConvTcModel* m = new ConvTcModel();
+  m->f16 = f16;
   auto fail = [&](const std::string& w) { if (err) *err = w; conv_tc_destroy(m); return (ConvTcModel*)nullptr; };
   const int nl = (int)M.layers.size();
   auto upload = [&](const void* h, size_t bytes) -> void* {
@@ -472,7 +496,7 @@ ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
     std::vector<uint16_t> wb((size_t)27 * rows * kC, 0);
     for (int f = 0; f < L.cout; f++)
       for (int c = 0; c < L.cin; c++)
-        for (int t = 0; t < 27; t++) wb[((size_t)t * rows + f) * kC + c] = to_bf16(L.W[((size_t)f * L.cin + c) * 27 + t]);
+        for (int t = 0; t < 27; t++) wb[((size_t)t * rows + f) * kC + c] = f16 ? to_f16(L.W[((size_t)f * L.cin + c) * 27 + t]) : to_bf16(L.W[((size_t)f * L.cin + c) * 27 + t]);
     std::vector<float> bias(kC, 0.f);
     for (int f = 0; f < L.cout; f++) bias[f] = L.b[f];
     void* dw = upload(wb.data(), wb.size() * 2);
@@ -485,9 +509,13 @@ ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err) {
   }
   if (cudaMalloc(&m->status, sizeof(int)) != cudaSuccess) return fail("out of device memory");
   cudaMemset(m->status, 0, sizeof(int));
-  if (cudaFuncSetAttribute(conv3d_tc_kernel<4, kC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess ||
-      cudaFuncSetAttribute(conv3d_tc_kernel<1, kC, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess ||
-      cudaFuncSetAttribute(conv3d_tc_kernel<4, kEdgeC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kConvSmem) != cudaSuccess)
+  const cudaFuncAttribute att = cudaFuncAttributeMaxDynamicSharedMemorySize;
+  if (cudaFuncSetAttribute(conv3d_tc_kernel<4, kC, false, false>, att, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<1, kC, false, false>, att, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<4, kEdgeC, true, false>, att, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<4, kC, false, true>, att, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<1, kC, false, true>, att, kConvSmem) != cudaSuccess ||
+      cudaFuncSetAttribute(conv3d_tc_kernel<4, kEdgeC, true, true>, att, kConvSmem) != cudaSuccess)
     return fail("cannot reserve shared memory for the tensor-core conv kernel");
   return m;
 }
@@ -519,13 +547,14 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   {
     const long long blocks = (nvox + 255) / 256;
-    conv_pack_input_kernel<<<(unsigned)(blocks < sms * 8 ? blocks : sms * 8), 256, 0, s>>>(x, m->buf[3] + m->front * kC, N, D, H, W, m->meta[0].cin);
+    const unsigned pg = (unsigned)(blocks < sms * 8 ? blocks : sms * 8);
+    if (m->f16) conv_pack_input_kernel<true><<<pg, 256, 0, s>>>(x, m->buf[3] + m->front * kC, N, D, H, W, m->meta[0].cin);
+    else conv_pack_input_kernel<false><<<pg, 256, 0, s>>>(x, m->buf[3] + m->front * kC, N, D, H, W, m->meta[0].cin);
   }
   const long long ntiles = (P + kTileOut - 1) / kTileOut, npairs = (ntiles + 1) / 2;
   const int max_pairs = sms / 2 > 0 ? sms / 2 : 1;
   const int grid = 2 * (int)(npairs < max_pairs ? npairs : max_pairs);          // clusters of two CTAs
-  cudaLaunchConfig_t cfg;
-  std::memset(&cfg, 0, sizeof cfg);
+  cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kConvThreads); cfg.dynamicSmemBytes = kConvSmem; cfg.stream = s;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeClusterDimension;
@@ -548,9 +577,12 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     P_.out = m->buf[dst] + m->front * kC; P_.y = y; P_.F = L.cout; P_.front = (int)m->front;
     P_.stage_bytes = geom.stage_bytes; P_.nstages = geom.nstages; P_.box_rows = geom.box_rows; P_.nbox = geom.nbox;
     P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status; P_.prof = (want_prof && l == 2) ? dprof : nullptr;
-    const cudaError_t le = l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true>, P_)
-                           : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false>, P_)
-                                       : cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kC, false>, P_);
+    const cudaError_t le = m->f16 ? (l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true, true>, P_)
+                                     : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false, true>, P_)
+                                                 : cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kC, false, true>, P_))
+                                  : (l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true, false>, P_)
+                                     : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false, false>, P_)
+                                                 : cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kC, false, false>, P_));
     if (le != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(le); return false; }
     if (L.flags & LFLAG_SAVE_SKIP) skip = dst;
     cur = dst;

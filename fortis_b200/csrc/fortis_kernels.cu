@@ -47,11 +47,13 @@ __global__ void __launch_bounds__(256) gather_kernel(const IoPlanDev* __restrict
 // lanes along columns so that each store instruction writes 32 neighbouring host-array elements.
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) scatter_kernel(const IoPlanDev* __restrict__ P, const StoreTarget* __restrict__ stores,
-                                                      ArrayTable T, RowGeom g, const float* __restrict__ Y) {
+                                                      ArrayTable T, RowGeom g, const float* __restrict__ Y,
+                                                      double* __restrict__ partials) {
   extern __shared__ float tile[];                 // [32][nout + 1]
   const int n = P->n, ld = n + 1;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long nrows = g.count * g.nk;
+  double csum = 0.0;
   for (long long r0 = (long long)blockIdx.x * 32; r0 < nrows; r0 += (long long)gridDim.x * 32) {
     const long long rows_here = min((long long)32, nrows - r0);
     const long long total = rows_here * n;
@@ -68,9 +70,23 @@ __global__ void __launch_bounds__(256) scatter_kernel(const IoPlanDev* __restric
         const StoreTarget st = stores[s];
         const double v = scatter_value(*P, T, st.slot, tile[lane * ld + st.slot], sc);
         store_elem(T, st.a, access_offset(st.a, ci, cj, kk), v);
+        csum += st.a.elt == 0 ? (double)(float)v : v;
       }
     }
     __syncthreads();
+  }
+  if (partials) {
+    // deterministic per-block partial: shuffle tree per warp, then the warp results in index order
+    __shared__ double wsum[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) csum += __shfl_down_sync(0xffffffffu, csum, o);
+    if (lane == 0) wsum[warp] = csum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double t = 0.0;
+      for (int w = 0; w < 8; w++) t += wsum[w];
+      partials[blockIdx.x] = t;
+    }
   }
 }
 
@@ -89,8 +105,13 @@ void launch_gather(const IoPlanDev* P, const Access* slots, int n, const ArrayTa
   gather_kernel<<<grid, 256, smem, s>>>(P, slots, T, g, X);
 }
 
+int scatter_grid(long long nrows) {
+  const long long tiles = (nrows + 31) / 32;
+  return (int)(tiles < 148 * 8 ? (tiles > 0 ? tiles : 1) : 148 * 8);
+}
+
 void launch_scatter(const IoPlanDev* P, const StoreTarget* stores, int nout, const ArrayTable& T, const RowGeom& g,
-                    const float* Y, cudaStream_t s) {
+                    const float* Y, cudaStream_t s, double* partials) {
   const long long nrows = g.count * g.nk;
   if (nrows <= 0) return;
   const size_t smem = (size_t)32 * (nout + 1) * sizeof(float);
@@ -99,9 +120,7 @@ void launch_scatter(const IoPlanDev* P, const StoreTarget* stores, int nout, con
     cudaFuncSetAttribute(scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     scatter_smem_set = smem;
   }
-  const long long tiles = (nrows + 31) / 32;
-  const int grid = (int)(tiles < 148 * 8 ? tiles : 148 * 8);
-  scatter_kernel<<<grid, 256, smem, s>>>(P, stores, T, g, Y);
+  scatter_kernel<<<scatter_grid(nrows), 256, smem, s>>>(P, stores, T, g, Y, partials);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

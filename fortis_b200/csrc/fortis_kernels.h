@@ -16,8 +16,10 @@ constexpr int kSmallConstFloats = 8192;     // constant-bank budget of the fused
 constexpr int kChecksumBlocks = 592;        // 4 x 148 SMs
 
 void launch_gather(const IoPlanDev* P, const Access* slots, int n, const ArrayTable& T, const RowGeom& g, float* X, cudaStream_t s);
+// `partials` (optional, scatter_grid(rows) doubles): per-block fp64 sums of the stored values in a fixed order
 void launch_scatter(const IoPlanDev* P, const StoreTarget* stores, int nout, const ArrayTable& T, const RowGeom& g,
-                    const float* Y, cudaStream_t s);
+                    const float* Y, cudaStream_t s, double* partials = nullptr);
+int scatter_grid(long long nrows);
 void launch_linear_f32(const float* A, const float* W, const float* bias, float* C, long long M, int N, int K, int act,
                        float slope, const float* in_div, const float* out_mul, const float* relu_mask, cudaStream_t s);
 
@@ -54,7 +56,7 @@ void launch_small_mlp(int nlayers, const int* dims, const SmallMlpLaunch& L, cud
 // ---- tensor-core fused MLP (fortis_mlp_tc.cu) ----------------------------------------------------------------
 struct ModelHost;
 struct TcModel;                                        // packed bf16 weights, TMA tensor maps, biases, scales
-enum { PREC_F32 = 0, PREC_BF16 = 1, PREC_FP8W = 2 };
+enum { PREC_F32 = 0, PREC_BF16 = 1, PREC_FP8W = 2, PREC_FP16 = 3 };
 bool tc_model_supported(const ModelHost& M, std::string* why);
 TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
 void tc_model_destroy(TcModel* m);
@@ -90,7 +92,7 @@ bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D,
 // tensor-core conv network (fortis_conv3d_tc.cu): bf16 activations in a zero-padded channels-last volume
 struct ConvTcModel;
 bool conv_tc_supported(const ModelHost& M, std::string* why);
-ConvTcModel* conv_tc_create(const ModelHost& M, std::string* err);
+ConvTcModel* conv_tc_create(const ModelHost& M, bool f16, std::string* err);
 void conv_tc_destroy(ConvTcModel* m);
 bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 int conv_tc_status(ConvTcModel* m);

@@ -27,6 +27,7 @@
 // abort flag that turns all later waits into no-ops, and the CTA still frees its tensor memory and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cmath>
@@ -121,8 +122,16 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t saddr) {
   return d;
 }
 
-// instruction descriptor: D = f32, A = B = bf16, both K-major, N = 64, M = 128
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kChunkN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+// instruction descriptor: D = f32, A and B both bf16 (format code 1) or both IEEE half (code 0), both K-major,
+// N = 64, M = 128
+template <bool F16> struct MlpIdesc {
+  static constexpr uint32_t value = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(kChunkN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+};
+// two consecutive k values as one 32-bit tensor-memory column, in the kernel's 16-bit operand format
+template <bool F16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (F16) { const __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<const uint32_t*>(&v); }
+  else return pack_bf16(lo, hi);
+}
 
 __device__ __forceinline__ float act_f(float v, float slope) { return fmaxf(v, v * slope); }
 
@@ -136,8 +145,9 @@ __device__ __forceinline__ void prof_add(long long* prof, int slot, long long* t
 // ---------------------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------------------
-template <bool HAS_SCALE>
+template <bool HAS_SCALE, bool F16>
 __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
+  constexpr uint32_t kIdesc = MlpIdesc<F16>::value;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);                         // parked chunks: 8 x 16 KB at offset 0
   if (base & 1023u) {                                           // the swizzled weight stages need 1024-byte alignment
@@ -305,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             }
             uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j++) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+            for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
             tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
           }
         } else {
@@ -321,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             }
             uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j++) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+            for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
             tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
           }
         }
@@ -370,8 +380,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
               const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
               const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
-              pk[2 * j] = pack_bf16(v0, v1);
-              pk[2 * j + 1] = pack_bf16(v2, v3);
+              pk[2 * j] = pack16<F16>(v0, v1);
+              pk[2 * j + 1] = pack16<F16>(v2, v3);
             }
           };
           // chunks parked in shared memory: a rolled loop (the address depends on c only arithmetically)
@@ -540,6 +550,13 @@ uint16_t f32_to_bf16(float f) {
   return (uint16_t)(u >> 16);
 }
 
+uint16_t f32_to_f16(float f) {
+  const __half h = __float2half_rn(f);
+  uint16_t u;
+  std::memcpy(&u, &h, 2);
+  return u;
+}
+
 // nearest (ties-to-even) E4M3 value, saturating at +-448: 4 exponent bits (bias 7), 3 mantissa bits, subnormal
 // step 2^-9
 float e4m3_round(float v) {
@@ -563,7 +580,7 @@ struct TcModel {
   float *in_div = nullptr, *out_mul = nullptr, *relu_mask = nullptr;
   TcLayer layer[kMaxLayers];
   CUtensorMap maps[kMaxLayers];
-  bool has_scale = false;
+  bool has_scale = false, f16 = false;
 };
 
 bool tc_model_supported(const ModelHost& M, std::string* why) {
@@ -624,7 +641,7 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
       for (int k = 0; k < L.cin; k++) {
         float w = L.W[(size_t)n * L.cin + k];
         if (precision == PREC_FP8W) w = e4m3_round(w / sc);       // E4M3 codes are exact in bf16
-        wb[(size_t)n * K + k] = f32_to_bf16(w);
+        wb[(size_t)n * K + k] = precision == PREC_FP16 ? f32_to_f16(w) : f32_to_bf16(w);
       }
     }
     void* dw = nullptr; float *db = nullptr, *ds = nullptr;
@@ -646,7 +663,7 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
     const cuuint32_t box[3] = {64, (cuuint32_t)kChunkN, (cuuint32_t)(kStageK / 64)};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(&m->maps[l], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = enc(&m->maps[l], precision == PREC_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
   }
@@ -658,10 +675,12 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     return d;
   };
   m->in_div = up(M.in_div); m->out_mul = up(M.out_mul); m->relu_mask = up(M.relu_mask);
-  if (cudaFuncSetAttribute(mlp_tc_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(mlp_tc_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+  if (cudaFuncSetAttribute(mlp_tc_fused_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
     return fail("cannot reserve " + std::to_string(kSmemBytes) + " bytes of shared memory for the tensor-core kernel");
   m->has_scale = precision == PREC_FP8W;
+  m->f16 = precision == PREC_FP16;
   return m;
 }
 
@@ -693,8 +712,9 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
     cudaMemsetAsync(dprof, 0, 32 * sizeof(long long), s);
     P.prof = dprof;
   }
-  if (m->has_scale) mlp_tc_fused_kernel<true><<<grid, kThreads, kSmemBytes, s>>>(P);
-  else mlp_tc_fused_kernel<false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  if (m->has_scale) mlp_tc_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  else if (m->f16) mlp_tc_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, s>>>(P);
+  else mlp_tc_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, s>>>(P);
   if (want_prof) {
     long long h[32];
     cudaStreamSynchronize(s);

@@ -88,7 +88,7 @@ struct ArrayInfo {
 
 struct LoopInfo {
   long long batch = 0, count = 0;
-  int ilo = 1, ni = 1, jlo = 0, nj = 1, nk = 1, klo = 0;
+  int ilo = 1, ni = 1, jlo = 0, nj = 1, nk = 1, klo = 1;
   bool kdist = false, has_outer = false;
 };
 

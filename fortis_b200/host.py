@@ -81,8 +81,12 @@ class Host:
         self.L.fortis_scatterv(self._ip(list(args)), len(args), self._vp(arrays), len(arrays))
         self.check()
 
-    def step(self, gather_arrays, scatter_arrays):
-        self.L.fortis_stepv(self._vp(gather_arrays), len(gather_arrays), self._vp(scatter_arrays), len(scatter_arrays))
+    def step(self, gather_arrays, scatter_arrays, args=()):
+        if args:
+            self.L.fortis_stepvi(self._ip(list(args)), len(args), self._vp(gather_arrays), len(gather_arrays),
+                                 self._vp(scatter_arrays), len(scatter_arrays))
+        else:
+            self.L.fortis_stepv(self._vp(gather_arrays), len(gather_arrays), self._vp(scatter_arrays), len(scatter_arrays))
         self.check()
 
     def forward(self, x, y):

@@ -35,6 +35,7 @@ def load():
         "fortis_gatherv": (None, [c.POINTER(ci), ci, c.POINTER(vp), ci]),
         "fortis_scatterv": (None, [c.POINTER(ci), ci, c.POINTER(vp), ci]),
         "fortis_stepv": (None, [c.POINTER(vp), ci, c.POINTER(vp), ci]),
+        "fortis_stepvi": (None, [c.POINTER(ci), ci, c.POINTER(vp), ci, c.POINTER(vp), ci]),
         "mlp_forward_batched": (None, [vp, vp]), "mlp_forward": (None, [vp, vp]), "mlp_upload": (None, [vp]),
         "mlp_forward_dev": (None, []), "mlp_download": (None, [vp]), "fortis_pack": (None, [vp, ci]),
         "fortis_unpack": (None, [vp, ci]), "fortis_model_input": (vp, []), "fortis_model_output": (vp, []),

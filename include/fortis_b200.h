@@ -119,18 +119,23 @@ void fortis_sync(void);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * 3. Fused and array-argument forms (no counterpart in the reference's generated code; they are what a maintainer
- *    would have the host rewriter emit: see INTEGRATION.md)
+ *    would have the host rewriter, driver/fortis_fission_hlfir.py:76-109, emit instead of the three calls)
  * ------------------------------------------------------------------------------------------------------------- */
 
-/* One launch for the whole step: gather -> forward -> scatter of every plane.  Arguments: the gather entry's
- * arrays, then the scatter entry's arrays (no integer arguments: all planes of a k-distributed loop are done).
- * Refused (message, nothing run) when a stored array has no plane dimension while nk > 1, because the host
- * consumes such an array between the per-plane scatters. */
-void fortis_step(const void* first, ...);
+/* One launch for the whole step: gather -> forward -> scatter.  Arguments: [the gather entry's integer arguments,
+ * by value, unless the enclosing loop is k-distributed], the gather entry's arrays, then the scatter entry's arrays.
+ * A k-distributed loop processes all its planes; otherwise the integers select the plane as they do for
+ * fortis_gather / fortis_scatter.  Refused (message, nothing run) when a stored array has no plane dimension while
+ * nk > 1, because the host consumes such an array between the per-plane scatters, and when a plane-selecting
+ * integer is missing.  When a device-resident gather array shares memory with a device-resident stored array the
+ * step runs as separate gather, forward and scatter kernels, so that no input is read after it was overwritten. */
+void fortis_step(long a0, ...);
 /* the same three entries with arguments in arrays, for bindings that cannot call C variadics */
 void fortis_gatherv(const int* iargs, int nint, const void* const* arrays, int narrays);
 void fortis_scatterv(const int* iargs, int nint, void* const* arrays, int narrays);
 void fortis_stepv(const void* const* gather_arrays, int ngather, void* const* scatter_arrays, int nscatter);
+void fortis_stepvi(const int* iargs, int nint, const void* const* gather_arrays, int ngather, void* const* scatter_arrays,
+                   int nscatter);
 
 /* synchronous copies between host memory and buffers of this library (fortis_alloc, fortis_model_input/output);
  * the first waits for the persistent stream */
@@ -146,22 +151,15 @@ int fortis_checksum(const void* data, long n, int elt, double* out);
  * order and nothing is synchronised.  The block partials live in a 32 KB array inside the library image, so n is
  * limited to 2^28 elements (return -2 and a message beyond that) and the call performs no cudaMalloc / cudaFree and
  * uses no pool.  The first call on each device resolves the array's device address (a set-up step: make that call
- * before any stream capture).  All calls share the array: calls that can overlap on the GPU race on it.
- * Returns 0, or a negative code with a message on stderr. */
+ * before any stream capture).  The address is remembered per device ordinal for the life of the process: a host that
+ * destroys the device's primary context (cudaDeviceReset) must not call this entry afterwards.  All calls share the
+ * array: calls that can overlap on the GPU race on it.  Returns 0, or a negative code with a message on stderr. */
 int fortis_checksum_noalloc(const void* dev_data, long n, int elt, double* dev_out, void* stream);
 
 /* fp64 sum of everything the fused steps scattered since the last call (needs option "checksum" = "1") */
 int fortis_step_checksum(double* out);
 /* device status word of the tensor-core kernel: 0, or the code of a bounded wait that gave up */
 int fortis_device_status(void);
-
-/* Host-only introspection of the expression compiler and the descriptor planner (no CUDA call is made):
- * evaluate the expression list `exprs_json` (a JSON array of strings) on one value; list the element offsets one
- * row touches.  Used by the CPU test-suite; no counterpart in the reference. */
-int fortis_debug_eval_expr(const char* exprs_json, int tv_double, double tv, const double* scalars, const int* scalar_elt,
-                           int nscalars, double* out);
-int fortis_debug_plan(const char* desc_json, const char* loop_json, const char* kdist_json, int is_scatter, long row,
-                      const int* args, int nargs, long long* offsets, int* arrays, int* slots, int cap, long long* geom);
 
 #ifdef __cplusplus
 }

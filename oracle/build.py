@@ -2,7 +2,8 @@
 """Build recipe for the checker code under oracle/.  TEST INFRASTRUCTURE ONLY.
 
   python oracle/build.py            # oracle/libfortis_oracle.so   (C port of the native forward, OpenMP)
-                                    # oracle/_ref/libfortis_ref_zb.so when the reference checkout is present
+                                    # oracle/_ref/libfortis_ref_zb.so and libfortis_ref_rt.so when the reference
+                                    # checkout is present
 
 oracle/_ref/ holds the REFERENCE's own generated gather/scatter kernels for the MOM6-ZB host
 (mom6_zb/gather.cu, compiled where it lies, never copied) linked against oracle/ref_stubs.cu, which supplies the
@@ -15,7 +16,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("FORTIS_REFERENCE", "/root/reference")
+# the reference checkout: FORTIS_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("FORTIS_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -52,6 +54,28 @@ def build_ref(verbose=True):
     return out
 
 
+def build_ref_rt(verbose=True):
+    """The reference's runtime compiled unchanged where it lies: runtime/fortis_rt.c (stream, pool, fortis_gemm ->
+    cuBLAS SGEMM, fortis_conv3d -> cuDNN) + runtime/fortis_fft.cu (direct and FFT conv).  Used on the GPU box as the
+    incumbent GPU path the benchmark is compared with, and as a second checker of fortis_gemm / fortis_conv3d.
+    Returns the library path, or None when the reference checkout is absent."""
+    rt = os.path.join(REF, "runtime", "fortis_rt.c")
+    fft = os.path.join(REF, "runtime", "fortis_fft.cu")
+    out_dir = os.path.join(HERE, "_ref")
+    out = os.path.join(out_dir, "libfortis_ref_rt.so")
+    if not (os.path.exists(rt) and os.path.exists(fft)):
+        return out if os.path.exists(out) else None
+    os.makedirs(out_dir, exist_ok=True)
+    if _stale(out, [rt, fft]):
+        cmd = ["nvcc", "-O2", "-lineinfo"] + ARCH + ["-shared", "-Xcompiler", "-fPIC", "-x", "cu", rt, fft, "-o", out,
+               "-lcublas", "-lcudnn", "-lcufft", "-lcudart"]
+        if verbose:
+            print(" ".join(cmd))
+        subprocess.run(cmd, check=True)
+    return out
+
+
 if __name__ == "__main__":
     print(build_port())
     print(build_ref())
+    print(build_ref_rt())

@@ -439,6 +439,13 @@ def round_bf16(x: np.ndarray) -> np.ndarray:
     return np.where(np.isnan(x), x, out).astype(np.float32)
 
 
+def round_fp16(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even float32 -> IEEE half -> float32 (overflow goes to infinity, as the conversion
+    instruction does)."""
+    with np.errstate(over="ignore"):
+        return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+
 def quant_e4m3(W: np.ndarray):
     """Per-output-channel FP8-E4M3 weights: scale[n] = max_k |W[n,k]| / 448; Wq = e4m3(W / scale)
     (round-to-nearest-even, saturating).  Returns (dequantised-code values as float32, scale)."""
@@ -463,18 +470,19 @@ def e4m3_round(v: np.ndarray) -> np.ndarray:
 
 
 def mlp_forward_lowp(layers, X, mode: str) -> np.ndarray:
-    """Model of the tensor-core path: activations rounded to bf16 at every layer input, weights bf16 (mode
-    'bf16') or E4M3 codes with a per-channel fp32 scale applied after accumulation (mode 'fp8w'), products
-    accumulated in high precision, bias + activation in fp32."""
+    """Model of the tensor-core path: activations rounded to bf16 (mode 'fp16': to IEEE half) at every layer input,
+    weights bf16 (mode 'bf16'), half (mode 'fp16') or E4M3 codes with a per-channel fp32 scale applied after
+    accumulation (mode 'fp8w'), products accumulated in high precision, bias + activation in fp32."""
     h = np.asarray(X, dtype=np.float32)
+    rnd = round_fp16 if mode == "fp16" else round_bf16
     for L in layers:
-        a = round_bf16(h).astype(np.float64)
+        a = rnd(h).astype(np.float64)
         W = np.asarray(L["W"], dtype=np.float32)
         if mode == "fp8w":
             Wq, sc = quant_e4m3(W)
             y = (a @ Wq.astype(np.float64).T) * sc.astype(np.float64)[None, :]
         else:
-            y = a @ round_bf16(W).astype(np.float64).T
+            y = a @ rnd(W).astype(np.float64).T
         y = y.astype(np.float32) + np.asarray(L["b"], dtype=np.float32)
         h = act_apply(y, L.get("act", "none"), L.get("slope", 0.0)).astype(np.float32)
     return h
@@ -516,11 +524,13 @@ def convnet_forward(layers: Sequence[Dict], x: np.ndarray, dtype=np.float32) -> 
     return h
 
 
-def convnet_forward_lowp(layers: Sequence[Dict], x: np.ndarray) -> np.ndarray:
-    """Model of the bf16 tensor-core conv network: the input and every layer's weights are rounded to bf16, products
-    are accumulated wide, bias / skip / activation are applied in fp32, and every intermediate activation (including
-    the remembered skip) is stored as bf16; the last layer's output stays fp32."""
+def convnet_forward_lowp(layers: Sequence[Dict], x: np.ndarray, mode: str = "bf16") -> np.ndarray:
+    """Model of the 16-bit tensor-core conv network: the input and every layer's weights are rounded to bf16 (mode
+    'fp16': IEEE half), products are accumulated wide, bias / skip / activation are applied in fp32, and every
+    intermediate activation (including the remembered skip) is stored in the 16-bit format; the last layer's output
+    stays fp32."""
     n = len(layers)
+    round_bf16 = globals()["round_fp16"] if mode == "fp16" else globals()["round_bf16"]      # noqa: F841 (shadows on purpose)
     h = round_bf16(np.asarray(x, dtype=np.float32))
     skip = None
     for l, L in enumerate(layers):

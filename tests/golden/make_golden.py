@@ -37,7 +37,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import fortis_oracle as fo  # noqa: E402
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("FORTIS_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference"))
 
 SHIM = r"""
 #include <math.h>

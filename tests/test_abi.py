@@ -1,4 +1,4 @@
-"""The C-ABI library loads and exports every symbol include/fortis_b200.h declares (no compute call is made)."""
+"""The C-ABI library loads and exports every symbol the headers under include/ declare (no compute call is made)."""
 import ctypes
 import os
 import re
@@ -18,7 +18,8 @@ def lib():
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "fortis_b200.h")).read()
+    inc = os.path.join(ROOT, "include")
+    text = "\n".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = re.findall(r"^\s*(?:const\s+)?(?:void|int|double|char|long)\s*\*?\s*(\w+)\s*\(", text, flags=re.M)
     names += re.findall(r"^extern\s+int\s+(\w+)\s*;", text, flags=re.M)

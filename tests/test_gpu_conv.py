@@ -59,12 +59,17 @@ def test_superres_net_bf16_tensor_cores(host, shape, blocks):
     y2 = np.zeros_like(y)
     host.forward(x, y2)                                      # second call reuses the padded buffers
     assert y2.tobytes() == y.tobytes()
-    e_model, e_exact = fo.rel_l2(y, model), fo.rel_l2(y, exact)
-    bar = max(5e-3, 1.1 * fo.rel_l2(model, exact))
-    # A deep residual stack amplifies rounding decorrelation: merely accumulating the MODEL in fp32 instead of fp64
-    # moves its 6-block output by 5e-3 (4e-4 at 2 blocks, 3e-5 at 1), so the tight model check is for shallow stacks.
-    model_bar = 2e-3 if blocks <= 2 else bar
-    assert e_model < model_bar and e_exact < bar, "vs bf16 model %.3e, vs fp32 %.3e (bar %.3e)" % (e_model, e_exact, bar)
+    e_model, e_exact, m_exact = fo.rel_l2(y, model), fo.rel_l2(y, exact), fo.rel_l2(model, exact)
+    print("conv bf16 %s, %d blocks: vs bf16 model %.3e, vs fp32 %.3e (the model itself: %.3e)" % (shape, blocks, e_model, e_exact, m_exact))
+    if blocks <= 2:
+        # shallow stacks: the north-star bf16 bar itself, and a tight check against the model of the arithmetic
+        assert e_model < 2e-3 and e_exact < 5e-3
+    else:
+        # A deep residual stack amplifies rounding decorrelation (merely accumulating the MODEL in fp32 instead of
+        # fp64 moves its 6-block output by 5e-3), so the kernel is held to bf16 arithmetic's own distance from fp32:
+        # it may add nothing on top.  The 5e-3 bar itself is asserted (and expected to fail in bf16) at full size in
+        # test_gpu_fullsize.py; the layer-by-layer and boundary-row checks below are the tight ones.
+        assert e_exact < 1.15 * m_exact
     assert host.L.fortis_device_status() == 0
 
 
@@ -118,3 +123,52 @@ def test_conv_probe_stamp_through_memref_entry(host, golden_dir):
                            1, 3, 16, 16, 16, 8, 3, 3, 3, 16, 16, 16, 2, 2, 2, 1, 1, 1)
     host.sync()
     assert float(y.min()) == -7.0 and float(y.max()) == -7.0
+
+
+@pytest.mark.parametrize("W", [6, 7, 8, 9, 10, 11, 12, 13])
+def test_conv_bf16_every_row_pitch_residue(host, W):
+    """The three kh taps of a kd read ONE staged activation tile through shared-memory descriptors whose start moves
+    by (W+2) rows of 128 bytes, i.e. to every residue of the 8-row (1024-byte) swizzle period as W varies.  One
+    64 -> 64 layer stack per residue, checked against the oracle's bf16 model per layer (no amplification)."""
+    N, D, H = 1, 4, 5
+    layers = fortis_b200.conv_layers(3, 64, 3, nblocks=1, seed=20 + W)
+    for L in layers:
+        L["b"] = (np.random.default_rng(3).normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = np.random.default_rng(W).normal(size=(N, D, H, W, 3)).astype(np.float32)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", "bf16")
+    host.option("conv_shape", "%d,%d,%d,%d" % (N, D, H, W))
+    y = np.zeros((N, D, H, W, 3), np.float32)
+    host.forward(x, y)
+    assert fo.rel_l2(y, fo.convnet_forward_lowp(layers, x)) < 2e-3, "W + 2 = %d (residue %d)" % (W + 2, (W + 2) % 8)
+    assert host.L.fortis_device_status() == 0
+
+
+def test_conv_bf16_layer_by_layer_at_tile_and_quadrant_boundaries(host):
+    """Per-layer check without amplification: each tensor-core layer is fed the oracle's own bf16 activations (a
+    one-layer-deep network per layer type) and compared at 1e-3, with the rows at tile and lane-quadrant boundaries
+    (padded rows 1, 31/32, 63/64, 95/96, 126/127 of every tile of 126 written rows) compared explicitly."""
+    N, D, H, W = 1, 10, 9, 12
+    rng = np.random.default_rng(41)
+    full = fortis_b200.conv_layers(3, 64, 3, nblocks=1, seed=9)
+    for L in full:
+        L["b"] = (rng.normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = rng.normal(size=(N, D, H, W, 3)).astype(np.float32)
+    host.load_model(fortis_b200.write_blob(full))
+    host.option("precision", "bf16")
+    host.option("conv_shape", "%d,%d,%d,%d" % (N, D, H, W))
+    y = np.zeros((N, D, H, W, 3), np.float32)
+    host.forward(x, y)
+    want = fo.convnet_forward_lowp(full, x)
+    assert fo.rel_l2(y, want) < 1e-3
+    # rows of the padded volume -> interior voxels; tile t writes padded rows 126 t .. 126 t + 125
+    Dp, Hp, Wp = D + 2, H + 2, W + 2
+    p = np.arange(N * Dp * Hp * Wp)
+    wp, hp, dp = p % Wp, (p // Wp) % Hp, (p // (Wp * Hp)) % Dp
+    interior = (wp >= 1) & (wp <= W) & (hp >= 1) & (hp <= H) & (dp >= 1) & (dp <= D)
+    r = p % 126
+    edge = interior & np.isin(r, [0, 1, 30, 31, 32, 62, 63, 64, 94, 95, 96, 124, 125])
+    assert edge.sum() > 50
+    ye = y[0, dp[edge] - 1, hp[edge] - 1, wp[edge] - 1]
+    we = want[0, dp[edge] - 1, hp[edge] - 1, wp[edge] - 1]
+    assert fo.rel_l2(ye, we) < 1e-3

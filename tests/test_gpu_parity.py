@@ -368,3 +368,108 @@ def test_errors_are_messages_not_crashes(host):
     host.option("precision", "bf16")
     with pytest.raises(fortis_b200.FortisError):    # no silent fallback when the tensor-core kernel cannot take it
         host.step([A], [np.zeros((2, 8), np.float32, order="F")])
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the fused step outside its simplest form
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("resident", [False, True])
+def test_fused_step_with_plane_chosen_by_argument(host, golden_dir, resident):
+    """Descriptors whose arrays carry a "v" subscript while the loop is NOT k-distributed: the fused step takes the
+    enclosing-loop index like fortis_gather / fortis_scatter do, and touches that plane only."""
+    g = json.load(open(os.path.join(golden_dir, "gather_scatter_golden.json")))["arg_plane"]
+    G, S, Lp, K, a0s = g["gather"], g["scatter"], g["loop"], g["kdist"], g["a0s"]
+    rng = np.random.default_rng(21)
+    layers = [dict(W=rng.normal(size=(S["n"], G["n"])).astype(np.float32), b=rng.normal(size=S["n"]).astype(np.float32), act="none")]
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(layers))
+    gin, sin = case_inputs(G, 11), case_inputs(S, 12)
+    for k in (1, a0s[0], 4):
+        ref = [a.copy(order="F") for a in sin]
+        X = fo.gather(G, Lp, K, gin, args=(k,))
+        fo.scatter(S, Lp, K, fo.mlp_forward(layers, X), ref, args=(k,))
+        work = [a.copy(order="F") for a in sin]
+        g_arr = [dev(a) for a in gin] if resident else gin
+        s_arr = [dev(a) for a in work] if resident else work
+        host.step(g_arr, s_arr, args=(k,))
+        host.sync()
+        got = [back(t, a) for t, a in zip(s_arr, work)] if resident else work
+        for a, b, orig in zip(got, ref, sin):
+            assert fo.rel_l2(a, b) < FP32_TOL
+            assert np.array_equal(a != orig, b != orig)        # exactly the cells of plane k's rectangle changed
+    # without the index the call is refused and nothing is written
+    work = [a.copy(order="F") for a in sin]
+    with pytest.raises(fortis_b200.FortisError, match="plane"):
+        host.step(gin, work)
+    assert all(a.tobytes(order="F") == b.tobytes(order="F") for a, b in zip(work, sin))
+
+
+def test_descriptor_and_model_that_do_not_fit_are_refused(host):
+    G, S, Lp, K = fo.identity_descriptors(6, 3, 16)
+    host.configure(gather=G, scatter=S, loop=Lp)
+    A, B = np.zeros((6, 16), np.float32, order="F"), np.zeros((3, 16), np.float32, order="F")
+    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([5, 8, 3], seed=0)))      # 5 inputs, the gather makes 6
+    with pytest.raises(fortis_b200.FortisError, match="inputs per row"):
+        host.step([A], [B])
+    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([6, 8, 4], seed=0)))      # 4 outputs, the scatter takes 3
+    with pytest.raises(fortis_b200.FortisError, match="outputs per row"):
+        host.step([A], [B])
+    # a 27-20-3 shaped model with a descriptor of another width must not reach the stencil kernel either
+    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([27, 20, 3], seed=0)))
+    with pytest.raises(fortis_b200.FortisError):
+        host.step([A], [B])
+
+
+def test_in_place_stencil_on_one_device_array_matches_the_staged_semantics(host):
+    """The host passes the SAME device array as gather input and as scatter target (an in-place update with a halo
+    stencil).  The reference is well-defined here (gather and scatter work on separate staging copies: every input is
+    read before any output is written); the fused kernels would read neighbours that other threads are overwriting,
+    so such a call has to run unfused."""
+    nx, ny, nz = 70, 33, 2
+    G, S, Lp, K = fo.stencil_descriptors(nx, ny, nz, nfields=3, nout=3)
+    rng = np.random.default_rng(31)
+    fields = [np.asfortranarray(rng.normal(size=(nx + 2, ny + 2, nz)).astype(np.float32)) for _ in range(3)]
+    layers = fortis_b200.mlp_layers([27, 20, 20, 3], seed=4, init="uniform", act="relu", bias="uniform")
+    ref = [a.copy(order="F") for a in fields]
+    fo.full_step(G, S, Lp, K, layers, fields, ref)            # gathers from `fields`, scatters into copies
+    host.configure(gather=G, scatter=S, loop=Lp, kdist=K)
+    host.load_model(fortis_b200.write_blob(layers))
+    d = [dev(a) for a in fields]
+    host.step(d, d)
+    host.sync()
+    for t, a, b in zip(d, fields, ref):
+        assert fo.rel_l2(back(t, a), b) < FP32_TOL
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_step_checksum_on_the_unfused_paths(host, precision):
+    """Option checksum = 1 must give the sum of what was scattered whichever kernels ran the step."""
+    ncol = 333
+    G, S, Lp, K = fo.column_descriptors(ncol, 7, nfields=2, nscal=2, nout_fields=1, nout_scal=3)
+    rng = np.random.default_rng(5)
+    gin = [np.asfortranarray(rng.normal(size=(ncol, 7)).astype(np.float32)) for _ in range(2)] + [rng.normal(size=ncol).astype(np.float32) for _ in range(2)]
+    sout = [np.zeros((ncol, 7), np.float32, order="F")] + [np.zeros(ncol, np.float32) for _ in range(3)]
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([16, 64, 10], seed=2)))
+    host.option("precision", precision)
+    host.option("checksum", 1)
+    host.option("fuse", 0)
+    d_in, d_out = [dev(a) for a in gin], [dev(a) for a in sout]
+    host.step(d_in, d_out)
+    host.sync()
+    total = float(sum(t.double().sum().item() for t in d_out))
+    assert abs(host.step_checksum() - total) <= 1e-9 * max(1.0, float(sum(t.double().abs().sum().item() for t in d_out)))
+
+
+def test_gemm_entry_refuses_strided_operands(host):
+    Bn, N, K = 16, 8, 12
+    A = torch.randn(Bn, 2 * K, device="cuda")[:, :K]            # row stride 2K: not dense
+    W = torch.randn(N, K, device="cuda")
+    C = torch.full((Bn, N), -3.0, device="cuda")
+    L = host.L
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    L.fortis_gemm.argtypes = [vp, vp, cl, cl, cl, cl, cl] * 3 + [cl, cl, cl]
+    L.fortis_gemm(A.data_ptr(), A.data_ptr(), 0, Bn, K, 2 * K, 1, W.data_ptr(), W.data_ptr(), 0, N, K, K, 1,
+                  C.data_ptr(), C.data_ptr(), 0, Bn, N, N, 1, Bn, N, K)
+    host.sync()
+    assert float(C.min()) == -3.0 and float(C.max()) == -3.0

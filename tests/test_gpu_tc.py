@@ -14,10 +14,12 @@ import fortis_b200
 from oracle import fortis_oracle as fo
 
 BF16_TOL, FP8W_TOL, MODEL_TOL = 5e-3, 2e-2, 2e-3
-# What rounding alone costs: the oracle's reduced-precision MODEL (exact arithmetic on bf16 / E4M3 operands) already
-# differs from fp32 by 2.3e-3 (bf16) / 2.6e-2 (E4M3) per 244->768 layer and 5.6e-3 / 6.3e-2 over the 5-layer net on
-# N(0,1) inputs, so a kernel can only be asked to add nothing on top: error vs fp32 <= SLACK x (model vs fp32).
-# On BASELINE config 2's own inputs and weights the bf16 path meets the 5e-3 bar outright (test_column_config).
+# These tests run the kernel on N(0,1) inputs and arbitrary layer shapes, where exact arithmetic on bf16 / E4M3
+# operands (the oracle's reduced-precision MODEL) is itself 2.3e-3 (bf16) / 2.6e-2 (E4M3) from fp32 per 244->768 layer
+# and 5.6e-3 / 6.3e-2 over a 5-layer net.  They therefore hold the kernel to the model (MODEL_TOL, tight) and to
+# "adds nothing on top": error vs fp32 <= SLACK x (model vs fp32).  The north-star bars themselves (5e-3 / 2e-2
+# against fp32) are asserted without any slack on the benchmark configurations in test_gpu_fullsize.py and in
+# test_column_config_fused_step below.
 SLACK = 1.1
 
 
@@ -49,7 +51,7 @@ def test_bf16_array_form(host, dims, rows):
     model = fo.mlp_forward_lowp(layers, X, "bf16")
     exact = fo.mlp_forward(layers, X)
     e_model, e_exact = fo.rel_l2(Y, model), fo.rel_l2(Y, exact)
-    bar = max(BF16_TOL, SLACK * fo.rel_l2(model, exact))
+    bar = SLACK * fo.rel_l2(model, exact) + 1e-4
     assert e_model < MODEL_TOL and e_exact < bar, "dims %s rows %d: vs bf16 model %.3e, vs fp32 %.3e; Y[0,:4]=%s want %s" % (
         dims, rows, e_model, e_exact, Y[0, :4], model[0, :4])
 
@@ -61,7 +63,7 @@ def test_fp8_weights_array_form(host):
     Y = run_array_form(host, layers, X, "fp8w")
     model, exact = fo.mlp_forward_lowp(layers, X, "fp8w"), fo.mlp_forward(layers, X)
     e_model, e_exact = fo.rel_l2(Y, model), fo.rel_l2(Y, exact)
-    bar = max(FP8W_TOL, SLACK * fo.rel_l2(model, exact))
+    bar = SLACK * fo.rel_l2(model, exact) + 1e-4
     assert e_model < MODEL_TOL and e_exact < bar, "vs fp8w model %.3e, vs fp32 %.3e (bar %.3e)" % (e_model, e_exact, bar)
 
 
@@ -78,7 +80,7 @@ def column_case(ncol, seed=2):
     return G, S, Lp, K, gin, sout, layers
 
 
-@pytest.mark.parametrize("precision,tol", [("bf16", BF16_TOL), ("fp8w", FP8W_TOL)])
+@pytest.mark.parametrize("precision,tol", [("bf16", BF16_TOL), ("fp16", BF16_TOL), ("fp8w", FP8W_TOL)])
 @pytest.mark.parametrize("resident", [True, False])
 def test_column_config_fused_step(host, precision, tol, resident):
     """BASELINE config 2's layout (ragged column count): gather fused into layer 0, scatter into the last epilogue."""
@@ -102,7 +104,9 @@ def test_column_config_fused_step(host, precision, tol, resident):
         got = sout
     cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
     e_model, e_exact = fo.rel_l2(cat(got), cat(model)), fo.rel_l2(cat(got), cat(ref))
-    bar = tol if precision == "bf16" else max(tol, SLACK * fo.rel_l2(cat(model), cat(ref)))
+    # bf16 / fp16: the north-star bar itself.  fp8w: E4M3's own distance from fp32 (the 2e-2 bar is an expected
+    # failure of its own in test_gpu_fullsize.py)
+    bar = tol if precision != "fp8w" else SLACK * fo.rel_l2(cat(model), cat(ref)) + 1e-4
     assert e_model < MODEL_TOL and e_exact < bar, "vs %s model %.3e, vs fp32 %.3e (bar %.3e)" % (precision, e_model, e_exact, bar)
     cs = host.step_checksum()
     want = float(cat(got).astype(np.float64).sum())
