@@ -72,6 +72,7 @@ int main(int argc, char** argv) {
   const char* dir = argv[1];
   const int k = argc > 2 ? atoi(argv[2]) : 1;
   const long xbytes = argc > 3 ? atol(argv[3]) : 0;
+  (void)k; (void)xbytes;
   float* g[NG]; long gn[NG];
   float* s[NS]; long sn[NS];
   char name[64];
