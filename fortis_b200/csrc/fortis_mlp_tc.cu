@@ -21,7 +21,7 @@
 //     slot is a coalesced load); the last layer's epilogue stores straight into the host arrays and accumulates
 //     the fp64 checksum.  This fusion is table-driven and covers fp32 arrays without lifted expressions; any other
 //     descriptor is served by the standalone gather / scatter kernels writing X / reading Y around this kernel.
-// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 3 x 32 KB weight ring.
+// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 96 KB parked chunks + 4 x 32 KB weight ring.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word, raises a CTA-wide
 // abort flag that turns all later waits into no-ops, and the CTA still frees its tensor memory and returns.
@@ -31,6 +31,7 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <type_traits>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -51,13 +52,30 @@ constexpr int kChunkN = 64;                 // output features per accumulator
 constexpr int kStageK = 256;                // k extent of one weight stage: four 64-wide swizzled sub-tiles, ONE TMA
 constexpr int kStageBytes = kChunkN * kStageK * 2;   // 32 KB
 constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 KB
-constexpr int kStages = 3;
-constexpr int kSmemChunks = 8;              // parked chunks held in shared memory; the rest in registers
+// Two builds of the same kernel.  Shallow ring (default): 3 weight stages, 8 output chunks parked in shared memory and
+// up to 4 in registers, 320 threads, 168 registers.  Deep ring (-DFORTIS_TC_DEEP_RING=1): 4 stages, 6 + 6 parked
+// chunks, which needs the row warps' register budget raised (setmaxnreg; 384 threads so that the producer warps form a
+// warpgroup of their own) and, because a function call stops the compiler from allocating per budget, the barrier waits
+// inlined.  Measured: the inlined waits cost 10 % by themselves (whatever the polling loop looks like), more than
+// the fourth stage returns, so the deep ring is not the default.
+#ifndef FORTIS_TC_DEEP_RING
+#define FORTIS_TC_DEEP_RING 0
+#endif
+constexpr bool kRegRealloc = FORTIS_TC_DEEP_RING != 0;
+#ifdef FORTIS_TC_INLINE_WAIT
+constexpr bool kInlineWait = true;
+#else
+constexpr bool kInlineWait = false;
+#endif
+constexpr int kStages = kRegRealloc ? 4 : 3;
+constexpr int kSmemChunks = kRegRealloc ? 6 : 8;   // parked chunks held in shared memory; the rest in registers
+constexpr int kRegsProducer = 40, kRegsRow = 232;  // 168 at launch; 2 x 128 x 232 + 128 x 40 = 64 K registers
+constexpr int kMaxKBlocks = 3;                     // 768 / 256: K-blocks of a layer's A, each with its own hand-off barriers
 constexpr int kMaxChunks = 12;              // 768 / 64
 constexpr int kMaxK = 768;
 constexpr int kMaxLayers = 8;
 constexpr int kEpiThreads = 256;
-constexpr int kThreads = kEpiThreads + 64;  // + TMA warp + MMA warp
+constexpr int kThreads = kEpiThreads + (kRegRealloc ? 128 : 64);   // + TMA warp + MMA warp (+ two idle warps: register re-allocation works per warpgroup)
 constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
 constexpr int kBarBytes = 256;
@@ -68,7 +86,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol0 = 384;
 
 // status codes (which wait gave up)
-enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6 };
+enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6, ST_A_DEAD = 7 };
 
 struct TcLayer {
   int K, N;                // padded: K multiple of 256, N multiple of 64 (hidden: multiple of 256)
@@ -135,11 +153,28 @@ template <bool F16> __device__ __forceinline__ uint32_t pack16(float lo, float h
 
 __device__ __forceinline__ float act_f(float v, float slope) { return fmaxf(v, v * slope); }
 
-// cycle accounting for diagnostics: adds the time since *t to prof[slot] (CTA 0, one lane) and restarts the clock
-__device__ __forceinline__ void prof_add(long long* prof, int slot, long long* t, bool who) {
-  // always compiled (one well-predicted branch per call when prof is null): compiling it out makes the optimiser
-  // restructure the role loops and nvcc's front end then runs for tens of minutes on this kernel
-  if (prof && who) { const long long n = clock64(); atomicAdd((unsigned long long*)&prof[slot], (unsigned long long)(n - *t)); *t = n; }
+// A 16-byte read-only load that stays where it is written: the compiler hoists plain loads to the top of the epilogue,
+// where they would be live next to the parked chunks
+__device__ __forceinline__ float4 ldg4_here(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+// Cycle accounting of the three roles (CTA 0, one lane each), compiled in with -DFORTIS_TC_PROF only: PROF_ADD(slot) adds
+// the time since the previous call to prof[slot].
+#ifdef FORTIS_TC_PROF
+#define PROF_DECL(who) const bool prof_who = P.prof && (who); long long prof_t = clock64()
+#define PROF_ADD(slot) do { if (prof_who) { const long long n_ = clock64(); atomicAdd((unsigned long long*)&P.prof[slot], (unsigned long long)(n_ - prof_t)); prof_t = n_; } } while (0)
+#else
+#define PROF_DECL(who) do { } while (0)
+#define PROF_ADD(slot) do { } while (0)
+#endif
+
+// the kernel's bounded barrier wait: inlined where warpgroups get different register budgets (a call would stop that)
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if constexpr (kRegRealloc || kInlineWait) return mbar_wait_inline(bar, parity, abort_flag, status, code);
+  else return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -149,18 +184,18 @@ template <bool HAS_SCALE, bool F16>
 __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
   constexpr uint32_t kIdesc = MlpIdesc<F16>::value;
   extern __shared__ __align__(1024) uint8_t smem[];
-  const uint32_t base = smem_u32(smem);                         // parked chunks: 8 x 16 KB at offset 0
+  const uint32_t base = smem_u32(smem);                         // parked chunks: kSmemChunks x 16 KB at offset 0
   if (base & 1023u) {                                           // the swizzled weight stages need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(P.status, 0, ST_SMEM_ALIGN);
     return;
   }
-  const uint32_t ring = base + kParkBytes;                      // kStages x 16 KB
+  const uint32_t ring = base + kParkBytes;                      // kStages x 32 KB
   const uint32_t bars = ring + kRingBytes;
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;            // [kStages] each
-  const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;   // [2] each
-  const uint32_t bar_a_ready = bar_acc_empty + 16;
-  // barrier block (256 B): full [0,48) empty [48,96) acc_full [96,112) acc_empty [112,128) a_ready [128,136)
-  // tmem base 144, abort flag 148, checksum scratch [160,224)
+  // barrier block (256 B): full [kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2]
+  // (at most 136 bytes); tmem base 144, abort flag 148, checksum scratch [160,224)
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
+  const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;
+  const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
   uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 144);
   volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 148);
   uint32_t* s_off = (uint32_t*)(smem + kParkBytes + kRingBytes + kBarBytes);          // [kFastIn] input slot offsets
@@ -178,7 +213,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kEpiThreads); }
-    mbar_init(bar_a_ready, kEpiThreads);
+    for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kEpiThreads);
+    for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -217,280 +253,375 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer (whole warp, one lane issues)
-    uint32_t s = 0, ph = 0;
-    const bool pw = blockIdx.x == 0 && lane == 0;
-    long long pt = clock64();
-    bool stop = false;
-    for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
-      for (int l = 0; l < P.nlayers && !stop; l++) {
-        const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
-        const CUtensorMap* map = &P.maps[l];
-        for (int c = 0; c < nchunks && !stop; c++)
-          for (int kb = 0; kb < nkb; kb++) {
-            prof_add(P.prof, 17, &pt, pw);
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
-            prof_add(P.prof, 16, &pt, pw);
-            mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-            const uint32_t dst = ring + s * kStageBytes;
-            tma_load_3d(dst, map, 0, c * kChunkN, kb * (kStageK / 64), bar_full + 8 * s);
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-      }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer (whole warp, one lane issues)
-    uint32_t s = 0, ph = 0, acc_it = 0, a_it = 0;
-    const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
-    const bool pw = blockIdx.x == 0 && lane == 0;
-    long long pt = clock64();
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
-      for (int l = 0; l < P.nlayers; l++, a_it++) {
-        const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
-        prof_add(P.prof, 0, &pt, pw);
-        mbar_wait(bar_a_ready, a_it & 1, abort_flag, P.status, ST_A_READY);      // A of this layer is in TMEM
-        prof_add(P.prof, 1, &pt, pw);
-        tc_fence_after();
-        for (int c = 0; c < nchunks; c++, acc_it++) {
-          const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-          prof_add(P.prof, 0, &pt, pw);
-          mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
-          prof_add(P.prof, 2, &pt, pw);
-          tc_fence_after();
-          const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
-          for (int kb = 0; kb < nkb; kb++) {
-            prof_add(P.prof, 0, &pt, pw);
-            mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
-            prof_add(P.prof, 3, &pt, pw);
-            tc_fence_after();
-            // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
-            // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
-            const uint32_t sb = ring + s * kStageBytes;
-            const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
-            const uint32_t a0 = tmem + kb * (kStageK / 2);
-            tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)kb);
-#pragma unroll
-            for (int j = 1; j < kStageK / 16; j++)
-              tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
-            tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
-            if (++s == kStages) { s = 0; ph ^= 1; }
-          }
-          tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
+  if (warp >= 8) {
+    // Register re-allocation between warpgroups (deep-ring build): the producer warpgroup (TMA warp, MMA warp, two idle
+    // warps) keeps kRegsProducer registers per thread and hands the rest to the two row warpgroups, whose threads park
+    // six output chunks (96 registers) next to the epilogue's working set.
+    if constexpr (kRegRealloc) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer (whole warp, one lane issues)
+      uint32_t s = 0, ph = 0;
+      PROF_DECL(blockIdx.x == 0 && lane == 0);
+      bool stop = false;
+      for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
+        for (int l = 0; l < P.nlayers && !stop; l++) {
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          const CUtensorMap* map = &P.maps[l];
+          for (int c = 0; c < nchunks && !stop; c++)
+            for (int kb = 0; kb < nkb; kb++) {
+              PROF_ADD(17);
+              if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
+              PROF_ADD(16);
+              mbar_expect_tx(bar_full + 8 * s, kStageBytes);
+              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, kb * (kStageK / 64), bar_full + 8 * s);
+              if (++s == kStages) { s = 0; ph ^= 1; }
+            }
         }
-      }
+    } else if (warp == 9) {
+      // ---------------------------------------------------------------- MMA issuer (whole warp, one lane issues)
+      uint32_t s = 0, ph = 0, acc_it = 0, lay_it = 0;
+      const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
+      PROF_DECL(blockIdx.x == 0 && lane == 0);
+      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+        for (int l = 0; l < P.nlayers; l++, lay_it++) {
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          const uint32_t lph = lay_it & 1;
+          for (int c = 0; c < nchunks; c++, acc_it++) {
+            const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
+            const bool lastc = c == nchunks - 1;
+            PROF_ADD(0);
+            wait_bar(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
+            PROF_ADD(2);
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
+            for (int kb = 0; kb < nkb; kb++) {
+              if (c == 0) {                                   // K-block kb of this layer's A is in tensor memory
+                PROF_ADD(0);
+                wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
+                PROF_ADD(1);
+              }
+              PROF_ADD(0);
+              wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+              PROF_ADD(3);
+              tc_fence_after();
+              // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
+              // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
+              const uint32_t sb = ring + s * kStageBytes;
+              const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
+              const uint32_t a0 = tmem + kb * (kStageK / 2);
+              tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)kb);
+#pragma unroll
+              for (int j = 1; j < kStageK / 16; j++)
+                tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
+              tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
+              if (lastc) {
+                // the layer's last MMAs on K-block kb: once they retire, those columns of A may be overwritten with
+                // the next layer's input.  Blocks this layer does not have are signalled with the last one, which
+                // keeps every barrier at one phase per layer.
+                if (kb < kMaxKBlocks - 1) tc_commit(bar_a_dead + 8 * kb);
+                if (kb == nkb - 1)
+                  for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) tc_commit(bar_a_dead + 8 * k2);
+              }
+              if (++s == kStages) { s = 0; ph ^= 1; }
+            }
+            tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
+          }
+        }
+    }
   } else {
+    if constexpr (kRegRealloc) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsRow));
     // ------------------------------------------------------------------ row warps: gather, epilogues, scatter
     const int quad = warp & 3, half = warp >> 2;              // TMEM lane quadrant, which 32 of a chunk's 64 features
     const int r = quad * 32 + lane;                           // row of the tile = TMEM lane
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
-    uint32_t acc_it = 0;
+    uint32_t acc_it = 0, lay_it = 0;
     double csum = 0.0;
-    const bool pw = blockIdx.x == 0 && threadIdx.x == 0;
-    long long pt = clock64();
-    uint32_t kept[(kMaxChunks - kSmemChunks) * 16];           // parked chunks 8..11 of this thread (bf16 pairs)
+    PROF_DECL(blockIdx.x == 0 && threadIdx.x == 0);
+    const int per0 = P.layer[0].K / 2;                        // model inputs per half row (padded)
+    const bool can_prefetch = P.layer[0].K == kStageK;        // one K-block of inputs: 64 packed registers per thread
+
+    // position of row `row_` in the host arrays, once per stride class of the gather
+    auto locate_in = [&](long long row_, bool& live_, long long& p0, long long& p1) {
+      live_ = row_ < P.nrows;
+      long long ci = 0, cj = 0, kk = 0;
+      if (live_) row_to_pos(P.g, row_, &ci, &cj, &kk);
+      p0 = ci * P.cin[0].si + cj * P.cin[0].sj + kk * P.cin[0].sk;
+      p1 = ci * P.cin[1].si + cj * P.cin[1].sj + kk * P.cin[1].sk;
+    };
+    // model inputs q0 .. q0 + 31 of one row as 16 packed 16-bit pairs: 32 independent loads, each coalesced across the
+    // warp (thread = row).  Either straight from the host arrays through the per-CTA slot table, or from a
+    // materialised X (array-form calls, and descriptors the table cannot express: lifted expressions, f64 arrays,
+    // scalars, for which the standalone gather kernel ran first).
+    auto gather_group = [&](long long row_, bool live_, long long p0, long long p1, int q0, uint32_t (&pk)[16]) {
+      float v[32];
+      if (P.fast_in) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const uint32_t code = s_code[q0 + j];
+          v[j] = 0.f;
+          if (live_ && code != 0xFF)
+            v[j] = __ldg(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? p1 : p0)));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] = (live_ && q0 + j < P.n_in) ? __ldg(P.X + row_ * P.n_in + q0 + j) : 0.f;
+      }
+      if (P.in_div) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
+    };
+    // layer 0's A is complete: release all K-block barriers (blocks the layer does not have stay in step)
+    auto release_layer0 = [&]() {
+      tmem_st_wait();
+      tc_fence_before();
+#pragma unroll
+      for (int k = 0; k < kMaxKBlocks; k++) mbar_arrive(bar_a_ready + 8 * k);
+    };
+
+    bool prefetched = false;
     for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const long long row = tile * kTileM + r;
       const bool live = row < P.nrows;
-      long long ci = 0, cj = 0, kk = 0;
-      if (live) row_to_pos(P.g, row, &ci, &cj, &kk);
-      // ---- layer 0 input: this thread's half of the row, 32 features (16 packed columns) at a time
-      {
-        const int K0 = P.layer[0].K, per = K0 / 2;            // features per half
-        if (P.fast_in) {
-          // one position per stride class, then 32 independent loads per step: base[array] + offset + position
-          const long long pos0 = ci * P.cin[0].si + cj * P.cin[0].sj + kk * P.cin[0].sk;
-          const long long pos1 = ci * P.cin[1].si + cj * P.cin[1].sj + kk * P.cin[1].sk;
-          for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-              const uint32_t code = s_code[q0 + j];
-              v[j] = 0.f;
-              if (live && code != 0xFF)
-                v[j] = __ldg(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? pos1 : pos0)));
-            }
-            if (P.in_div) {
-#pragma unroll
-              for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
-            }
-            uint32_t pk[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
-            tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
-          }
-        } else {
-          // input already materialised as X (rows, n_in): array-form calls, and descriptors the fast tables cannot
-          // express (lifted expressions, f64 arrays, scalars), for which the standalone gather kernel ran first
-          for (int q0 = half * per; q0 < (half + 1) * per; q0 += 32) {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) v[j] = (live && q0 + j < P.n_in) ? __ldg(P.X + row * P.n_in + q0 + j) : 0.f;
-            if (P.in_div) {
-#pragma unroll
-              for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
-            }
-            uint32_t pk[16];
-#pragma unroll
-            for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
-            tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
-          }
+      if (!prefetched) {
+        // ---- layer 0 input straight into A: the CTA's first tile, or inputs wider than one K-block.  The previous
+        //      tile's MMAs have all retired (its last accumulator was read), so A may be overwritten.
+        bool lv; long long p0, p1;
+        locate_in(row, lv, p0, p1);
+        for (int q0 = half * per0; q0 < (half + 1) * per0; q0 += 32) {
+          uint32_t pk[16];
+          gather_group(row, lv, p0, p1, q0, pk);
+          tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
         }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(bar_a_ready);
-        prof_add(P.prof, 9, &pt, pw);
+        release_layer0();
+        PROF_ADD(9);
       }
-      for (int l = 0; l < P.nlayers; l++) {
+      prefetched = false;
+      for (int l = 0; l < P.nlayers; l++, lay_it++) {
         const TcLayer& L = P.layer[l];
-        const int nchunks = L.N / kChunkN;
+        const int nchunks = L.N / kChunkN, nkb = L.K / kStageK;
         const bool last = l == P.nlayers - 1;
         const float slope = L.slope;
+        const uint32_t lph = lay_it & 1;
         if (!last) {
-          // epilogue of one chunk: accumulator -> (x scale) + bias -> activation -> 16 packed bf16 pairs
+          uint32_t kept[(kMaxChunks - kSmemChunks) * 16];     // this thread's parked chunks beyond those in shared memory (16-bit pairs)
+          // epilogue of one chunk: accumulator -> (x scale) + bias -> activation -> 16 packed 16-bit pairs
           auto chunk_epilogue = [&](int c, uint32_t (&pk)[16]) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
             const int n0 = c * kChunkN + half * 32;
-            // the 32 biases of this thread's features: warp-uniform 16-byte loads issued before the wait
-            float4 bq[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
-            prof_add(P.prof, 11, &pt, pw);
-            mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
-            prof_add(P.prof, 10, &pt, pw);
+            PROF_ADD(11);
+            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            PROF_ADD(10);
             tc_fence_after();
-            uint32_t a[32];
-            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * b);             // the MMA warp may refill this accumulator
-            if (HAS_SCALE) {
+            // the 32 features in two passes of 16 with their biases (and scales) loaded in place: a working set of 48
+            // registers beside the parked chunks
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
-                a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
-                a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
-                a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
-                a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
+            for (int h = 0; h < 2; h++) {
+              uint32_t a[16];
+              tmem_ld16(lane_addr + kAccCol0 + b * kChunkN + half * 32 + 16 * h, a);
+              tmem_ld_wait();
+              if (h == 1) {
+                tc_fence_before();
+                mbar_arrive(bar_acc_empty + 8 * b);           // the MMA warp may refill this accumulator
+              }
+              float4 bq[4], sq[4];
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                bq[j] = ldg4_here(L.bias + n0 + 16 * h + 4 * j);
+                if (HAS_SCALE) sq[j] = ldg4_here(L.scale + n0 + 16 * h + 4 * j);
+                else sq[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+              }
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                const int i = 4 * j;
+                float x0 = __uint_as_float(a[i]), x1 = __uint_as_float(a[i + 1]), x2 = __uint_as_float(a[i + 2]), x3 = __uint_as_float(a[i + 3]);
+                if (HAS_SCALE) { x0 *= sq[j].x; x1 *= sq[j].y; x2 *= sq[j].z; x3 *= sq[j].w; }
+                pk[8 * h + 2 * j] = pack16<F16>(act_f(x0 + bq[j].x, slope), act_f(x1 + bq[j].y, slope));
+                pk[8 * h + 2 * j + 1] = pack16<F16>(act_f(x2 + bq[j].z, slope), act_f(x3 + bq[j].w, slope));
               }
             }
-#pragma unroll
-            for (int j = 0; j < 8; j++) {
-              const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
-              const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
-              const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
-              const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
-              pk[2 * j] = pack16<F16>(v0, v1);
-              pk[2 * j + 1] = pack16<F16>(v2, v3);
-            }
           };
-          // chunks parked in shared memory: a rolled loop (the address depends on c only arithmetically)
-          const int nsm = nchunks < kSmemChunks ? nchunks : kSmemChunks;
-#pragma unroll 1
-          for (int c = 0; c < nsm; c++) {
-            uint32_t pk[16];
-            chunk_epilogue(c, pk);
-            // [chunk][half][16-byte piece][row]: lanes are rows, so every store is conflict-free
+          // shared-memory park: [chunk][half][16-byte piece][row]: lanes are rows, so every access is conflict-free
+          auto park_smem = [&](int c, const uint32_t (&pk)[16]) {
             uint8_t* dst = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
             for (int p = 0; p < 4; p++)
               *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
+          };
+          const int lastc = nchunks - 1;
+          // all chunks but the last: those parked in shared memory in a rolled loop (the address depends on c only
+          // arithmetically), those parked in registers unrolled so that `kept` is indexed statically
+          const int nsm = lastc < kSmemChunks ? lastc : kSmemChunks;
+#pragma unroll 1
+          for (int c = 0; c < nsm; c++) {
+            uint32_t pk[16];
+            chunk_epilogue(c, pk);
+            park_smem(c, pk);
           }
-          // chunks parked in registers: unrolled so that `kept` is indexed statically
 #pragma unroll
           for (int c = kSmemChunks; c < kMaxChunks; c++) {
-            if (c < nchunks) {
+            if (c < lastc) {
               uint32_t pk[16];
               chunk_epilogue(c, pk);
 #pragma unroll
               for (int j = 0; j < 16; j++) kept[(c - kSmemChunks) * 16 + j] = pk[j];
             }
           }
-          // every MMA of this layer has retired (its last accumulator was complete), so A may be overwritten:
-          // move the parked chunks into the A columns and release the next layer
-          prof_add(P.prof, 11, &pt, pw);
-#pragma unroll 1
-          for (int c = 0; c < nsm; c++) {
-            uint32_t pk[16];
-            const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+          // The next layer's A, K-block by K-block (four output chunks each).  A block of A may be overwritten once
+          // this layer's last MMAs on it have retired: the MMA warp signals that per block while the last chunk is
+          // still being computed, so blocks 0 and 1 are moved during the last chunk's MMAs and the next layer's first
+          // MMAs run while the last chunk's epilogue and block are finished.
+          const int nkb2 = L.N / kStageK;
+          // blocks before `wall` only need this layer's MMAs on the same block retired; from `wall` on a block holds
+          // the last chunk or columns the layer reads to its end, so everything has to have retired
+          const int wall = (nkb2 < nkb ? nkb2 : nkb) - 1;
+          // move output chunks 4 kb2 .. 4 kb2 + 3 into the A columns of K-block kb2 and release the block
+          auto move_block = [&](auto KB2) {
+            constexpr int kb2 = decltype(KB2)::value;
 #pragma unroll
-            for (int p = 0; p < 4; p++) {
-              const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
-              pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
-            }
-            tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
-          }
-#pragma unroll
-          for (int c = kSmemChunks; c < kMaxChunks; c++) {
-            if (c < nchunks) {
+            for (int c4 = 0; c4 < 4; c4++) {
+              const int c = 4 * kb2 + c4;                     // compile-time after unrolling
               uint32_t pk[16];
+              if (c < kSmemChunks) {
+                const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
-              for (int j = 0; j < 16; j++) pk[j] = kept[(c - kSmemChunks) * 16 + j];
+                for (int p = 0; p < 4; p++) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
+                  pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) pk[j] = kept[(c - kSmemChunks) * 16 + j];
+              }
               tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
             }
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar_a_ready + 8 * kb2);
+          };
+          PROF_ADD(11);
+          if (0 < wall) { wait_bar(bar_a_dead + 0, lph, abort_flag, P.status, ST_A_DEAD); tc_fence_after(); move_block(std::integral_constant<int, 0>{}); }
+          if (1 < wall) { wait_bar(bar_a_dead + 8, lph, abort_flag, P.status, ST_A_DEAD); tc_fence_after(); move_block(std::integral_constant<int, 1>{}); }
+          {
+            uint32_t pk[16];
+            chunk_epilogue(lastc, pk);                        // waits for the layer's last accumulator: every MMA has retired
+            if (lastc < kSmemChunks) park_smem(lastc, pk);
+            else {
+#pragma unroll
+              for (int cc = kSmemChunks; cc < kMaxChunks; cc++)
+                if (lastc == cc) {
+#pragma unroll
+                  for (int j = 0; j < 16; j++) kept[(cc - kSmemChunks) * 16 + j] = pk[j];
+                }
+            }
           }
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(bar_a_ready);
-          prof_add(P.prof, 12, &pt, pw);
+          if (wall <= 0 && 0 < nkb2) move_block(std::integral_constant<int, 0>{}); else if (nkb2 <= 0) mbar_arrive(bar_a_ready + 0);
+          if (wall <= 1 && 1 < nkb2) move_block(std::integral_constant<int, 1>{}); else if (nkb2 <= 1) mbar_arrive(bar_a_ready + 8);
+          if (2 < nkb2) move_block(std::integral_constant<int, 2>{}); else mbar_arrive(bar_a_ready + 16);   // blocks the next layer does not have stay in step
+          PROF_ADD(12);
         } else {
-          // ---- last layer: bias, output scaling / masks, then straight into the host arrays
+          // ---- last layer: bias, output scaling / masks, then straight into the host arrays.  While its MMAs run, the
+          //      next tile's inputs are fetched into registers; they go into A as soon as the layer's last MMAs on
+          //      K-block 0 have retired, so that the next tile's first layer runs under this tile's scatter.
+          long long ci = 0, cj = 0, kk = 0;
+          if (live) row_to_pos(P.g, row, &ci, &cj, &kk);
           const long long opos0 = ci * P.cout[0].si + cj * P.cout[0].sj + kk * P.cout[0].sk;
           const long long opos1 = ci * P.cout[1].si + cj * P.cout[1].sj + kk * P.cout[1].sk;
+          const bool do_pre = can_prefetch && tile + gridDim.x < ntiles;
+          // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
+          // has been moved), in the park's thread-private layout, so no other thread ever touches them.
+          static_assert(kStageK / 2 / 32 == 4 && kSmemChunks >= 4, "the prefetch uses four park slots of 32 inputs per half row");
+          if (do_pre) {
+            const long long nrow = (tile + gridDim.x) * kTileM + r;
+            bool lv; long long p0, p1;
+            locate_in(nrow, lv, p0, p1);
+#pragma unroll 1
+            for (int g = 0; g < 4; g++) {
+              uint32_t pk[16];
+              gather_group(nrow, lv, p0, p1, half * per0 + 32 * g, pk);
+              uint8_t* dst = smem + g * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+#pragma unroll
+              for (int p = 0; p < 4; p++)
+                *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
+            }
+          }
           for (int c = 0; c < nchunks; c++) {
+            if (c == nchunks - 1 && do_pre) {
+              wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD);
+              tc_fence_after();
+#pragma unroll 1
+              for (int g = 0; g < 4; g++) {
+                uint32_t pk[16];
+                const uint8_t* src = smem + g * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                  const uint4 q = *reinterpret_cast<const uint4*>(src + p * (kTileM * 16));
+                  pk[4 * p] = q.x; pk[4 * p + 1] = q.y; pk[4 * p + 2] = q.z; pk[4 * p + 3] = q.w;
+                }
+                tmem_st16(lane_addr + (uint32_t)((half * per0 + 32 * g) >> 1), pk);
+              }
+              release_layer0();
+              prefetched = true;
+            }
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
-            const int n0 = c * kChunkN + half * 32;
-            float4 bq[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
-            prof_add(P.prof, 13, &pt, pw);
-            mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
-            prof_add(P.prof, 14, &pt, pw);
+            PROF_ADD(13);
+            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            PROF_ADD(14);
             tc_fence_after();
-            uint32_t a[32];
-            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * b);
-            float v[32];
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-              float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
-              if (HAS_SCALE) sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
-              v[4 * j] = act_f(__uint_as_float(a[4 * j]) * sq.x + bq[j].x, slope);
-              v[4 * j + 1] = act_f(__uint_as_float(a[4 * j + 1]) * sq.y + bq[j].y, slope);
-              v[4 * j + 2] = act_f(__uint_as_float(a[4 * j + 2]) * sq.z + bq[j].z, slope);
-              v[4 * j + 3] = act_f(__uint_as_float(a[4 * j + 3]) * sq.w + bq[j].w, slope);
-            }
-            if (P.out_mul || P.relu_mask) {
+            for (int h = 0; h < 2; h++) {
+              const int n0 = c * kChunkN + half * 32 + 16 * h;       // this pass: outputs n0 .. n0 + 15 of the thread's row
+              uint32_t a[16];
+              tmem_ld16(lane_addr + kAccCol0 + b * kChunkN + half * 32 + 16 * h, a);
+              tmem_ld_wait();
+              if (h == 1) {
+                tc_fence_before();
+                mbar_arrive(bar_acc_empty + 8 * b);
+              }
+              float v[16];
 #pragma unroll
-              for (int j = 0; j < 32; j++) {
-                const int n = n0 + j;
-                if (n < P.n_out) {
-                  if (P.out_mul) v[j] *= __ldg(P.out_mul + n);
-                  if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v[j] = fmaxf(v[j], 0.f);
+              for (int j = 0; j < 4; j++) {
+                const float4 bq = ldg4_here(L.bias + n0 + 4 * j);
+                float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (HAS_SCALE) sq = ldg4_here(L.scale + n0 + 4 * j);
+                v[4 * j] = act_f(__uint_as_float(a[4 * j]) * sq.x + bq.x, slope);
+                v[4 * j + 1] = act_f(__uint_as_float(a[4 * j + 1]) * sq.y + bq.y, slope);
+                v[4 * j + 2] = act_f(__uint_as_float(a[4 * j + 2]) * sq.z + bq.z, slope);
+                v[4 * j + 3] = act_f(__uint_as_float(a[4 * j + 3]) * sq.w + bq.w, slope);
+              }
+              if (P.out_mul || P.relu_mask) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                  const int n = n0 + j;
+                  if (n < P.n_out) {
+                    if (P.out_mul) v[j] *= __ldg(P.out_mul + n);
+                    if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v[j] = fmaxf(v[j], 0.f);
+                  }
                 }
               }
-            }
-            if (live) {
-              if (P.Y) {
+              if (live) {
+                if (P.Y) {
 #pragma unroll
-                for (int j = 0; j < 32; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
-              }
-              if (P.fast_out) {
+                  for (int j = 0; j < 16; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
+                }
+                if (P.fast_out) {
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                  const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
-                  if (code != 0xFF) {
-                    s_base_out[code & 0x7F][(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
-                    csum += (double)v[j];
+                  for (int j = 0; j < 16; j++) {
+                    const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
+                    if (code != 0xFF) {
+                      s_base_out[code & 0x7F][(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
+                      csum += (double)v[j];
+                    }
                   }
                 }
               }
             }
           }
-          prof_add(P.prof, 13, &pt, pw);
+          PROF_ADD(13);
         }
       }
     }
@@ -705,7 +836,11 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(nrows);
+#ifdef FORTIS_TC_PROF
   static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
+#else
+  static const bool want_prof = false;
+#endif
   static long long* dprof = nullptr;
   if (want_prof) {
     if (!dprof) cudaMalloc(&dprof, 32 * sizeof(long long));

@@ -51,6 +51,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 
+// The same wait without a function call, for kernels whose warpgroups run with different register budgets (setmaxnreg):
+// a call there stops the compiler from allocating per budget.  The polling loop is one PTX block, so the surrounding
+// code stays as compact as with the call.  The abort flag is read once, after the first failed poll; a thread that is
+// already polling when another one gives up runs to its own limit.
+__device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .u32 i;\n\tmov.u32 i, 0;\n"
+      "WAIT_LOOP_%=:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra WAIT_DONE_%=;\n\t"
+      "add.u32 i, i, 1;\n\t"
+      "setp.lt.u32 q, i, %3;\n\t"
+      "@q bra WAIT_LOOP_%=;\n"
+      "WAIT_DONE_%=:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "n"(kWaitLimit) : "memory");
+  if (ok) return true;
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
@@ -117,6 +142,13 @@ __device__ __forceinline__ void tmem_ldn(uint32_t taddr, uint32_t (&r)[16]) { tm
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_st16p(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
