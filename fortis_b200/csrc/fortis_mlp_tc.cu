@@ -412,36 +412,37 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
             const int n0 = c * kChunkN + half * 32;
+            // the 32 biases of this thread's features: warp-uniform 16-byte loads issued before the wait
+            float4 bq[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
             PROF_ADD(11);
             wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
             PROF_ADD(10);
             tc_fence_after();
-            // the 32 features in two passes of 16 with their biases (and scales) loaded in place: a working set of 48
-            // registers beside the parked chunks
+            uint32_t a[32];
+            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty + 8 * b);               // the MMA warp may refill this accumulator
+            if (HAS_SCALE) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-              uint32_t a[16];
-              tmem_ld16(lane_addr + kAccCol0 + b * kChunkN + half * 32 + 16 * h, a);
-              tmem_ld_wait();
-              if (h == 1) {
-                tc_fence_before();
-                mbar_arrive(bar_acc_empty + 8 * b);           // the MMA warp may refill this accumulator
+              for (int j = 0; j < 8; j++) {
+                const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+                a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
+                a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
+                a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
+                a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
               }
-              float4 bq[4], sq[4];
+            }
 #pragma unroll
-              for (int j = 0; j < 4; j++) {
-                bq[j] = ldg4_here(L.bias + n0 + 16 * h + 4 * j);
-                if (HAS_SCALE) sq[j] = ldg4_here(L.scale + n0 + 16 * h + 4 * j);
-                else sq[j] = make_float4(1.f, 1.f, 1.f, 1.f);
-              }
-#pragma unroll
-              for (int j = 0; j < 4; j++) {
-                const int i = 4 * j;
-                float x0 = __uint_as_float(a[i]), x1 = __uint_as_float(a[i + 1]), x2 = __uint_as_float(a[i + 2]), x3 = __uint_as_float(a[i + 3]);
-                if (HAS_SCALE) { x0 *= sq[j].x; x1 *= sq[j].y; x2 *= sq[j].z; x3 *= sq[j].w; }
-                pk[8 * h + 2 * j] = pack16<F16>(act_f(x0 + bq[j].x, slope), act_f(x1 + bq[j].y, slope));
-                pk[8 * h + 2 * j + 1] = pack16<F16>(act_f(x2 + bq[j].z, slope), act_f(x3 + bq[j].w, slope));
-              }
+            for (int j = 0; j < 8; j++) {
+              const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
+              const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
+              const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
+              const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
+              pk[2 * j] = pack16<F16>(v0, v1);
+              pk[2 * j + 1] = pack16<F16>(v2, v3);
             }
           };
           // shared-memory park: [chunk][half][16-byte piece][row]: lanes are rows, so every access is conflict-free
@@ -568,54 +569,51 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             }
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
+            const int n0 = c * kChunkN + half * 32;
+            float4 bq[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
             PROF_ADD(13);
             wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
             PROF_ADD(14);
             tc_fence_after();
+            uint32_t a[32];
+            tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty + 8 * b);
+            float v[32];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-              const int n0 = c * kChunkN + half * 32 + 16 * h;       // this pass: outputs n0 .. n0 + 15 of the thread's row
-              uint32_t a[16];
-              tmem_ld16(lane_addr + kAccCol0 + b * kChunkN + half * 32 + 16 * h, a);
-              tmem_ld_wait();
-              if (h == 1) {
-                tc_fence_before();
-                mbar_arrive(bar_acc_empty + 8 * b);
-              }
-              float v[16];
+            for (int j = 0; j < 8; j++) {
+              float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
+              if (HAS_SCALE) sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+              v[4 * j] = act_f(__uint_as_float(a[4 * j]) * sq.x + bq[j].x, slope);
+              v[4 * j + 1] = act_f(__uint_as_float(a[4 * j + 1]) * sq.y + bq[j].y, slope);
+              v[4 * j + 2] = act_f(__uint_as_float(a[4 * j + 2]) * sq.z + bq[j].z, slope);
+              v[4 * j + 3] = act_f(__uint_as_float(a[4 * j + 3]) * sq.w + bq[j].w, slope);
+            }
+            if (P.out_mul || P.relu_mask) {
 #pragma unroll
-              for (int j = 0; j < 4; j++) {
-                const float4 bq = ldg4_here(L.bias + n0 + 4 * j);
-                float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (HAS_SCALE) sq = ldg4_here(L.scale + n0 + 4 * j);
-                v[4 * j] = act_f(__uint_as_float(a[4 * j]) * sq.x + bq.x, slope);
-                v[4 * j + 1] = act_f(__uint_as_float(a[4 * j + 1]) * sq.y + bq.y, slope);
-                v[4 * j + 2] = act_f(__uint_as_float(a[4 * j + 2]) * sq.z + bq.z, slope);
-                v[4 * j + 3] = act_f(__uint_as_float(a[4 * j + 3]) * sq.w + bq.w, slope);
-              }
-              if (P.out_mul || P.relu_mask) {
-#pragma unroll
-                for (int j = 0; j < 16; j++) {
-                  const int n = n0 + j;
-                  if (n < P.n_out) {
-                    if (P.out_mul) v[j] *= __ldg(P.out_mul + n);
-                    if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v[j] = fmaxf(v[j], 0.f);
-                  }
+              for (int j = 0; j < 32; j++) {
+                const int n = n0 + j;
+                if (n < P.n_out) {
+                  if (P.out_mul) v[j] *= __ldg(P.out_mul + n);
+                  if (P.relu_mask && __ldg(P.relu_mask + n) != 0.f) v[j] = fmaxf(v[j], 0.f);
                 }
               }
-              if (live) {
-                if (P.Y) {
+            }
+            if (live) {
+              if (P.Y) {
 #pragma unroll
-                  for (int j = 0; j < 16; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
-                }
-                if (P.fast_out) {
+                for (int j = 0; j < 32; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
+              }
+              if (P.fast_out) {
 #pragma unroll
-                  for (int j = 0; j < 16; j++) {
-                    const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
-                    if (code != 0xFF) {
-                      s_base_out[code & 0x7F][(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
-                      csum += (double)v[j];
-                    }
+                for (int j = 0; j < 32; j++) {
+                  const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
+                  if (code != 0xFF) {
+                    s_base_out[code & 0x7F][(long long)o_off[n0 + j] + ((code & 0x80) ? opos1 : opos0)] = v[j];
+                    csum += (double)v[j];
                   }
                 }
               }
