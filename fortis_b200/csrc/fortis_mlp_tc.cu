@@ -75,7 +75,8 @@ constexpr int kMaxChunks = 12;              // 768 / 64
 constexpr int kMaxK = 768;
 constexpr int kMaxLayers = 8;
 constexpr int kEpiThreads = 256;
-constexpr int kThreads = kEpiThreads + (kRegRealloc ? 128 : 64);   // + TMA warp + MMA warp (+ two idle warps: register re-allocation works per warpgroup)
+constexpr int kIssuers = 2;                 // MMA-issuing warps: issuer w owns accumulator w and every chunk that lands in it
+constexpr int kThreads = kEpiThreads + (kRegRealloc ? 128 : 96);   // + TMA warp + two MMA warps (+ an idle warp: register re-allocation works per warpgroup)
 constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
 constexpr int kBarBytes = 256;
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kEpiThreads); }
     for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kEpiThreads);
-    for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, 1);
+    for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, kIssuers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -277,25 +278,38 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
         }
-    } else if (warp == 9) {
-      // ---------------------------------------------------------------- MMA issuer (whole warp, one lane issues)
+    } else if (warp < 9 + kIssuers) {
+      // ---------------------------------------------------------------- MMA issuers (whole warps, one lane issues)
+      // Two warps issue: a 128 x 64 x 16 MMA keeps the tensor pipe busy for 32 cycles, less than one warp needs to wait
+      // for a stage, issue sixteen MMAs and commit.  Chunks alternate between the two accumulators, so issuer w simply
+      // owns accumulator w and all chunks that land in it; the pipe sees one in-order stream.  Both walk the same
+      // chunk / stage sequence and skip what is not theirs.
+      const uint32_t me = (uint32_t)(warp - 9);
       uint32_t s = 0, ph = 0, acc_it = 0, lay_it = 0;
       const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
-      PROF_DECL(blockIdx.x == 0 && lane == 0);
+      PROF_DECL(blockIdx.x == 0 && lane == 0 && me == 0);
       for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
         for (int l = 0; l < P.nlayers; l++, lay_it++) {
           const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
           const uint32_t lph = lay_it & 1;
+          bool first = true, any = false;
           for (int c = 0; c < nchunks; c++, acc_it++) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-            const bool lastc = c == nchunks - 1;
+            if (b != me) {                                    // the other issuer's chunk: step over its stages
+              s += (uint32_t)nkb;
+              while (s >= (uint32_t)kStages) { s -= kStages; ph ^= 1; }
+              continue;
+            }
+            any = true;
+            // this issuer's last chunk of the layer: no later chunk lands in accumulator `me`
+            const bool mine_last = c + kIssuers >= nchunks;
             PROF_ADD(0);
             wait_bar(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
             PROF_ADD(2);
             tc_fence_after();
             const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
             for (int kb = 0; kb < nkb; kb++) {
-              if (c == 0) {                                   // K-block kb of this layer's A is in tensor memory
+              if (first) {                                    // K-block kb of this layer's A is in tensor memory
                 PROF_ADD(0);
                 wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
                 PROF_ADD(1);
@@ -314,18 +328,21 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               for (int j = 1; j < kStageK / 16; j++)
                 tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
               tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
-              if (lastc) {
-                // the layer's last MMAs on K-block kb: once they retire, those columns of A may be overwritten with
-                // the next layer's input.  Blocks this layer does not have are signalled with the last one, which
-                // keeps every barrier at one phase per layer.
+              if (mine_last) {
+                // this issuer's last MMAs on K-block kb in this layer: once both issuers' have retired, those columns
+                // of A may be overwritten with the next layer's input.  Blocks the layer does not have are signalled
+                // with the last one, which keeps every barrier at one phase per layer.
                 if (kb < kMaxKBlocks - 1) tc_commit(bar_a_dead + 8 * kb);
                 if (kb == nkb - 1)
                   for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) tc_commit(bar_a_dead + 8 * k2);
               }
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
+            first = false;
             tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
           }
+          if (!any)                                           // a one-chunk layer: the idle issuer still closes the phase
+            for (int k2 = 0; k2 < kMaxKBlocks - 1; k2++) mbar_arrive_elect(bar_a_dead + 8 * k2);
         }
     }
   } else {
