@@ -49,7 +49,9 @@ namespace {
 
 constexpr int kTileM = 128;
 constexpr int kChunkN = 64;                 // output features per accumulator
-constexpr int kStageK = 256;                // k extent of one weight stage: four 64-wide swizzled sub-tiles, ONE TMA
+constexpr int kBlockK = 256;                // K-block: granularity of the layer hand-off and of the padding of K
+constexpr int kStageK = kBlockK;            // k extent of one weight stage: four 64-wide swizzled sub-tiles, ONE TMA per stage
+constexpr int kSubStages = kBlockK / kStageK;        // stages per K-block (halving the stage to 16 KB was measured: no gain)
 constexpr int kStageBytes = kChunkN * kStageK * 2;   // 32 KB
 constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 KB
 // Two builds of the same kernel.  Shallow ring (default): 3 weight stages, 8 output chunks parked in shared memory and
@@ -67,7 +69,7 @@ constexpr bool kInlineWait = true;
 #else
 constexpr bool kInlineWait = false;
 #endif
-constexpr int kStages = kRegRealloc ? 4 : 3;
+constexpr int kStages = (kRegRealloc ? 4 : 3) * kSubStages;
 constexpr int kSmemChunks = kRegRealloc ? 6 : 8;   // parked chunks held in shared memory; the rest in registers
 constexpr int kRegsProducer = 40, kRegsRow = 232;  // 168 at launch; 2 x 128 x 232 + 128 x 40 = 64 K registers
 constexpr int kMaxKBlocks = 3;                     // 768 / 256: K-blocks of a layer's A, each with its own hand-off barriers
@@ -79,7 +81,7 @@ constexpr int kIssuers = 2;                 // MMA-issuing warps: issuer w owns 
 constexpr int kThreads = kEpiThreads + (kRegRealloc ? 128 : 96);   // + TMA warp + two MMA warps (+ an idle warp: register re-allocation works per warpgroup)
 constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
-constexpr int kBarBytes = 256;
+constexpr int kBarBytes = 384;             // barriers in the first 256 bytes, then the tensor-memory base, the abort flag and the checksum scratch
 constexpr int kFastIn = 256, kFastOut = 128;          // widest model input / output the fast I/O tables hold
 constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5 + 2 * kMaxArrays * 8;   // uint32 offset + uint8 code per slot / store, array bases
 constexpr int kSmemBytes = kParkBytes + kRingBytes + kBarBytes + kTabBytes;   // the base must be 1024-byte aligned
@@ -192,13 +194,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   }
   const uint32_t ring = base + kParkBytes;                      // kStages x 32 KB
   const uint32_t bars = ring + kRingBytes;
-  // barrier block (256 B): full [kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2]
-  // (at most 136 bytes); tmem base 144, abort flag 148, checksum scratch [160,224)
+  // barrier block: full [kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2] within the
+  // first 256 bytes; tmem base 256, abort flag 260, checksum scratch [272,336)
+  static_assert(8 * (2 * kStages + 9) <= 256, "the barriers must fit the first 256 bytes of the barrier block");
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
   const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
-  uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 144);
-  volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 148);
+  uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 256);
+  volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 260);
   uint32_t* s_off = (uint32_t*)(smem + kParkBytes + kRingBytes + kBarBytes);          // [kFastIn] input slot offsets
   uint32_t* o_off = s_off + kFastIn;                                                  // [kFastOut] store offsets
   uint8_t* s_code = (uint8_t*)(o_off + kFastOut);                                     // array | class << 7, 0xFF: none
@@ -266,15 +269,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       bool stop = false;
       for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
         for (int l = 0; l < P.nlayers && !stop; l++) {
-          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const CUtensorMap* map = &P.maps[l];
           for (int c = 0; c < nchunks && !stop; c++)
-            for (int kb = 0; kb < nkb; kb++) {
+            for (int ks = 0; ks < nkb * kSubStages; ks++) {
               PROF_ADD(17);
               if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
               PROF_ADD(16);
               mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, kb * (kStageK / 64), bar_full + 8 * s);
+              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), bar_full + 8 * s);
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
         }
@@ -290,14 +293,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       PROF_DECL(blockIdx.x == 0 && lane == 0 && me == 0);
       for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
         for (int l = 0; l < P.nlayers; l++, lay_it++) {
-          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kStageK;
+          const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const uint32_t lph = lay_it & 1;
           bool first = true, any = false;
           for (int c = 0; c < nchunks; c++, acc_it++) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-            if (b != me) {                                    // the other issuer's chunk: step over its stages
-              s += (uint32_t)nkb;
-              while (s >= (uint32_t)kStages) { s -= kStages; ph ^= 1; }
+            if (b != me) {
+              // The other issuer's chunk.  Its stages are stepped over one by one, each after its weights have landed:
+              // a parity wait can only tell the current phase of a barrier from the previous one, so an issuer must
+              // see every phase of a stage barrier complete before it waits for the next one (the ring can be exactly
+              // one chunk long, which would put this issuer a whole lap ahead of the other).
+              for (int ks = 0; ks < nkb * kSubStages; ks++) {
+                wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+                if (++s == kStages) { s = 0; ph ^= 1; }
+              }
               continue;
             }
             any = true;
@@ -314,35 +323,41 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
                 PROF_ADD(1);
               }
-              PROF_ADD(0);
-              wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
-              PROF_ADD(3);
-              tc_fence_after();
-              // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
-              // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
-              const uint32_t sb = ring + s * kStageBytes;
-              const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
-              const uint32_t a0 = tmem + kb * (kStageK / 2);
-              tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)kb);
 #pragma unroll
-              for (int j = 1; j < kStageK / 16; j++)
-                tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
-              tc_commit(bar_empty + 8 * s);                   // stage reusable once these MMAs have read it
+              for (int sub = 0; sub < kSubStages; sub++) {
+                PROF_ADD(0);
+                wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+                PROF_ADD(3);
+                tc_fence_after();
+                // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
+                // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
+                const uint32_t sb = ring + s * kStageBytes;
+                const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
+                const uint32_t a0 = tmem + kb * (kBlockK / 2) + sub * (kStageK / 2);
+                tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)(kb | sub));
+#pragma unroll
+                for (int j = 1; j < kStageK / 16; j++)
+                  tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
+                tc_commit(bar_empty + 8 * s);                 // stage reusable once these MMAs have read it
+                if (++s == kStages) { s = 0; ph ^= 1; }
+              }
               if (mine_last) {
                 // this issuer's last MMAs on K-block kb in this layer: once both issuers' have retired, those columns
                 // of A may be overwritten with the next layer's input.  Blocks the layer does not have are signalled
                 // with the last one, which keeps every barrier at one phase per layer.
-                if (kb < kMaxKBlocks - 1) tc_commit(bar_a_dead + 8 * kb);
-                if (kb == nkb - 1)
-                  for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) tc_commit(bar_a_dead + 8 * k2);
+                // (a one-chunk layer has one working issuer, which then signals for both)
+                for (int rep = 0; rep < (nchunks < kIssuers ? kIssuers : 1); rep++) {
+                  if (kb < kMaxKBlocks - 1) tc_commit(bar_a_dead + 8 * kb);
+                  if (kb == nkb - 1)
+                    for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) tc_commit(bar_a_dead + 8 * k2);
+                }
               }
-              if (++s == kStages) { s = 0; ph ^= 1; }
             }
             first = false;
             tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
           }
-          if (!any)                                           // a one-chunk layer: the idle issuer still closes the phase
-            for (int k2 = 0; k2 < kMaxKBlocks - 1; k2++) mbar_arrive_elect(bar_a_dead + 8 * k2);
+          if (!any)                                           // a one-chunk layer: the idle issuer still sees the layer's phases complete
+            for (int kb = 0; kb < nkb; kb++) wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
         }
     }
   } else {
@@ -355,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     double csum = 0.0;
     PROF_DECL(blockIdx.x == 0 && threadIdx.x == 0);
     const int per0 = P.layer[0].K / 2;                        // model inputs per half row (padded)
-    const bool can_prefetch = P.layer[0].K == kStageK;        // one K-block of inputs: 64 packed registers per thread
+    const bool can_prefetch = P.layer[0].K == kBlockK;        // one K-block of inputs: 64 packed registers per thread
 
     // position of row `row_` in the host arrays, once per stride class of the gather
     auto locate_in = [&](long long row_, bool& live_, long long& p0, long long& p1) {
@@ -394,8 +409,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     auto release_layer0 = [&]() {
       tmem_st_wait();
       tc_fence_before();
+      // block 0 last: a waiter that has seen block 0's phase complete has thereby seen the others'
 #pragma unroll
-      for (int k = 0; k < kMaxKBlocks; k++) mbar_arrive(bar_a_ready + 8 * k);
+      for (int k = kMaxKBlocks - 1; k >= 0; k--) mbar_arrive(bar_a_ready + 8 * k);
     };
 
     bool prefetched = false;
@@ -418,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       prefetched = false;
       for (int l = 0; l < P.nlayers; l++, lay_it++) {
         const TcLayer& L = P.layer[l];
-        const int nchunks = L.N / kChunkN, nkb = L.K / kStageK;
+        const int nchunks = L.N / kChunkN, nkb = L.K / kBlockK;
         const bool last = l == P.nlayers - 1;
         const float slope = L.slope;
         const uint32_t lph = lay_it & 1;
@@ -492,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           // this layer's last MMAs on it have retired: the MMA warp signals that per block while the last chunk is
           // still being computed, so blocks 0 and 1 are moved during the last chunk's MMAs and the next layer's first
           // MMAs run while the last chunk's epilogue and block are finished.
-          const int nkb2 = L.N / kStageK;
+          const int nkb2 = L.N / kBlockK;
           // blocks before `wall` only need this layer's MMAs on the same block retired; from `wall` on a block holds
           // the last chunk or columns the layer reads to its end, so everything has to have retired
           const int wall = (nkb2 < nkb ? nkb2 : nkb) - 1;
@@ -551,7 +567,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           const bool do_pre = can_prefetch && tile + gridDim.x < ntiles;
           // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
           // has been moved), in the park's thread-private layout, so no other thread ever touches them.
-          static_assert(kStageK / 2 / 32 == 4 && kSmemChunks >= 4, "the prefetch uses four park slots of 32 inputs per half row");
+          static_assert(kBlockK / 2 / 32 == 4 && kSmemChunks >= 4, "the prefetch uses four park slots of 32 inputs per half row");
           if (do_pre) {
             const long long nrow = (tile + gridDim.x) * kTileM + r;
             bool lv; long long p0, p1;
@@ -642,7 +658,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     }
     if (P.partials) {
       // per-CTA checksum partial in a fixed order: shuffle tree per warp, then warp results in index order
-      double* wsum = (double*)(smem + kParkBytes + kRingBytes + 160);
+      double* wsum = (double*)(smem + kParkBytes + kRingBytes + 272);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) csum += __shfl_down_sync(0xffffffffu, csum, o);
       if (lane == 0) wsum[warp] = csum;
@@ -735,9 +751,9 @@ bool tc_model_supported(const ModelHost& M, std::string* why) {
   if ((int)M.layers.size() > kMaxLayers) return no("more than 8 layers");
   for (size_t l = 0; l < M.layers.size(); l++) {
     const LayerHost& L = M.layers[l];
-    if (round_up(L.cin, kStageK) > kMaxK) return no("a layer input is wider than 768");
+    if (round_up(L.cin, kBlockK) > kMaxK) return no("a layer input is wider than 768");
     if (L.act == ACT_LEAKY && !(L.slope >= 0.f && L.slope <= 1.f)) return no("LeakyReLU slope outside [0, 1]");
-    const int npad = l + 1 < M.layers.size() ? round_up(L.cout, kStageK) : round_up(L.cout, kChunkN);
+    const int npad = l + 1 < M.layers.size() ? round_up(L.cout, kBlockK) : round_up(L.cout, kChunkN);
     if (npad > kMaxK) return no("a layer output is wider than 768");
   }
   return true;
@@ -771,8 +787,8 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
   auto fail = [&](const std::string& w) { if (err) *err = w; tc_model_destroy(m); return (TcModel*)nullptr; };
   for (int l = 0; l < m->nlayers; l++) {
     const LayerHost& L = M.layers[l];
-    const int K = round_up(L.cin, kStageK);
-    const int N = l + 1 < m->nlayers ? round_up(L.cout, kStageK) : round_up(L.cout, kChunkN);
+    const int K = round_up(L.cin, kBlockK);
+    const int N = l + 1 < m->nlayers ? round_up(L.cout, kBlockK) : round_up(L.cout, kChunkN);
     std::vector<uint16_t> wb((size_t)N * K, 0);
     std::vector<float> bias(N, 0.f), scale(N, 1.f);
     for (int n = 0; n < L.cout; n++) {
