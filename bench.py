@@ -530,7 +530,7 @@ class Bench:
                 except Exception as ex:
                     incumbent = {"unavailable": repr(ex)}
             tc = prec != "fp32"
-            launches_per_step = (len(wl["layers"]) + (1 if tc else 0)) if is_conv else 2 if (tc or kind == "stencil") else (3 + len(wl["layers"]))
+            launches_per_step = (len(wl["layers"]) + (1 if tc else 0)) if is_conv else 1 if tc else 2 if kind == "stencil" else (3 + len(wl["layers"]))
             line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
                     "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
                     "vs_baseline": None,

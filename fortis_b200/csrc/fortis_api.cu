@@ -137,6 +137,7 @@ struct Session {
   bool nopin = false;
 
   double *d_partials = nullptr, *d_sum = nullptr;
+  unsigned int* d_done = nullptr;             // CTA completion counter of the in-kernel checksum fold
   int* d_status = nullptr;
   long long partials_cap = 0;
 
@@ -369,6 +370,8 @@ void ensure_aux(long long npartials) {
   if (!s.d_sum) {
     s.d_sum = (double*)pool_alloc(sizeof(double));
     s.d_status = (int*)pool_alloc(sizeof(int));
+    s.d_done = (unsigned int*)pool_alloc(sizeof(unsigned int));
+    cudaMemset(s.d_done, 0, sizeof(unsigned int));
     cudaMemset(s.d_sum, 0, sizeof(double));
     cudaMemset(s.d_status, 0, sizeof(int));
   }
@@ -612,10 +615,10 @@ void run_step_kernels(const StepArgs& A) {
     L.g = g;
     ensure_aux(tc_grid(rows));
     L.partials = (fuse_out && s.want_checksum) ? s.d_partials : nullptr;
+    L.sum = L.partials ? s.d_sum : nullptr; L.done = s.d_done;
     L.status = s.d_status;
     std::string err;
     if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
-    if (L.partials) launch_fold(s.d_partials, tc_grid(rows), s.d_sum, 1, st);
     if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);
     return;
   }
@@ -981,7 +984,7 @@ void fortis_reset(void) {
   free_plan(s.G); free_plan(s.S);
   free_model_dev();
   pool_free(s.din); pool_free(s.dout); pool_free(s.act0); pool_free(s.act1);
-  pool_free(s.d_partials); pool_free(s.d_sum); pool_free(s.d_status);
+  pool_free(s.d_partials); pool_free(s.d_sum); pool_free(s.d_status); pool_free(s.d_done);
   if (s.X_pinned) cudaFreeHost(s.X_pinned);
   if (s.Y_pinned) cudaFreeHost(s.Y_pinned);
   if (s.reg_in) cudaHostUnregister((void*)s.reg_in);

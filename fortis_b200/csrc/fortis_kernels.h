@@ -73,6 +73,7 @@ struct TcLaunch {
   const float* X;                                    // (rows, n_in) when there is no gather plan
   float* Y;                                          // (rows, n_out) when there is no scatter plan (may be set with SP too)
   double* partials;                                  // per-CTA checksum partials (size >= tc_grid())
+  double* sum; unsigned int* done;                   // optional: fold the partials into *sum inside the kernel (done: zeroed counter)
   int* status;                                       // device word: 0 ok, else the code of the wait that gave up
 };
 int tc_grid(long long nrows);

@@ -121,6 +121,8 @@ struct TcParams {
   RowGeom g;
   long long nrows;
   double* partials;
+  double* sum;                           // with partials: the last CTA to finish folds them into *sum (accumulating), in index order
+  unsigned int* done;                    // CTA completion counter for that fold (zero between launches)
   int* status;
   long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
   // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
@@ -667,6 +669,18 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         double t = 0.0;
         for (int w = 0; w < 8; w++) t += wsum[w];
         P.partials[blockIdx.x] = t;
+        if (P.sum) {
+          // the last CTA to get here adds all partials to the step checksum, in CTA order (so the result does not
+          // depend on which CTA was last); it also re-arms the counter for the next launch
+          __threadfence();
+          if (atomicAdd(P.done, 1u) == gridDim.x - 1) {
+            __threadfence();
+            double total = *P.sum;
+            for (unsigned i = 0; i < gridDim.x; i++) total += __ldcg(P.partials + i);
+            *P.sum = total;
+            *P.done = 0u;
+          }
+        }
       }
     }
   }
@@ -857,7 +871,7 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   P.GP = L.GP; P.slots = L.slots; P.TG = L.TG; P.X = L.X;
   P.SP = L.SP; P.stores = L.stores; P.TS = L.TS; P.Y = L.Y;
   P.slot_head = L.slot_head; P.store_next = L.store_next;
-  P.g = L.g; P.nrows = nrows; P.partials = L.partials; P.status = L.status;
+  P.g = L.g; P.nrows = nrows; P.partials = L.partials; P.sum = L.sum; P.done = L.done; P.status = L.status;
   P.fast_in = L.fast_in && m->n_in <= kFastIn; P.fast_out = L.fast_out && m->n_out <= kFastOut;
   for (int i = 0; i < 2; i++) {
     P.cin[i] = StrideClass{L.cin[i][0], L.cin[i][1], L.cin[i][2]};
