@@ -120,6 +120,7 @@ struct Session {
   float *d_in_div = nullptr, *d_out_mul = nullptr, *d_relu_mask = nullptr;
   bool small_ok = false;
   TcModel* tc = nullptr;
+  F32TcModel* f32 = nullptr;                   // fp32 precision on the tensor cores (split TF32), large batches
   ConvModel* conv = nullptr;
   int conv_shape[4] = {0, 0, 0, 0};
 
@@ -187,6 +188,7 @@ void free_model_dev() {
   pool_free(s.d_in_div); pool_free(s.d_out_mul); pool_free(s.d_relu_mask);
   s.d_in_div = s.d_out_mul = s.d_relu_mask = nullptr;
   if (s.tc) { tc_model_destroy(s.tc); s.tc = nullptr; }
+  if (s.f32) { f32tc_destroy(s.f32); s.f32 = nullptr; }
   if (s.conv) { conv_model_destroy(s.conv); s.conv = nullptr; }
   s.model_on_dev = false;
   s.small_ok = false;
@@ -320,6 +322,11 @@ void ensure_model() {
                                     s.model.out_mul.empty() ? nullptr : s.model.out_mul.data(), img.data());
       if (cuda_ok(small_mlp_upload(img.data(), nf, st), "small-MLP constant upload")) s.small_ok = true;
       cudaStreamSynchronize(st);
+    }
+    if (s.precision == PREC_F32) {
+      std::string err;
+      s.f32 = f32tc_create(s.model, &err);                       // optional: without it every batch takes the FFMA kernels
+      if (!s.f32) std::fprintf(stderr, "fortis: fp32 layers stay on the FFMA kernels (%s)\n", err.c_str());
     }
     if (s.precision != PREC_F32) {
       std::string err;
@@ -520,6 +527,8 @@ void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
 // ---------------------------------------------------------------------------------------------------------------
 // the step
 // ---------------------------------------------------------------------------------------------------------------
+constexpr long long kF32TcMinRows = 512;     // below this the per-layer FFMA kernels win on latency
+
 struct StepArgs {
   bool use_gather = false;      // model input comes from the gather plan (else din)
   bool fuse_scatter = false;    // outputs go straight to the host arrays (all planes)
@@ -636,6 +645,29 @@ void run_step_kernels(const StepArgs& A) {
     if (A.fuse_scatter && s.want_checksum) { ensure_aux(L.grid); L.partials = s.d_partials; }
     launch_small_mlp(nl, dims.data(), L, st);
     if (L.partials) launch_fold(s.d_partials, L.grid, s.d_sum, 1, st);
+    return;
+  }
+  if (s.f32 && rows >= kF32TcMinRows) {
+    // fp32 on the tensor cores: one split-TF32 kernel per layer, gather fused into the first layer's operand load and
+    // scatter (+ checksum) into the last epilogue when the descriptors are table-driven, activations feature-major
+    F32TcLaunch L{};
+    const bool fuse_in = A.use_gather && fuse && s.G.fast && s.model.n_in() <= 768;
+    const bool fuse_out = A.fuse_scatter && fuse && s.S.fast && s.model.n_out() <= 256;
+    if (fuse_in) { L.fast_in = 1; L.slots = (const Access*)s.G.items; L.TG = A.TG; std::memcpy(L.cin, s.G.cls, sizeof L.cin); }
+    else {
+      if (A.use_gather) launch_gather(s.G.hdr, (const Access*)s.G.items, s.G.h.n, A.TG, g, s.din, st);
+      L.X = s.din;
+    }
+    if (fuse_out) { L.fast_out = 1; L.store_by_slot = s.S.store_by_slot; L.TS = A.TS; std::memcpy(L.cout, s.S.cls, sizeof L.cout); }
+    else L.Y = s.dout;
+    L.g = g;
+    L.act[0] = s.act0; L.act[1] = s.act1; L.act_ld = s.buf_rows;
+    ensure_aux(f32tc_grid(rows));
+    if (fuse_out && s.want_checksum) { L.partials = s.d_partials; L.sum = s.d_sum; L.done = s.d_done; }
+    L.status = s.d_status;
+    std::string err;
+    if (!f32tc_forward(s.f32, L, st, &err)) throw std::runtime_error(err);
+    if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);
     return;
   }
   // generic fp32 path: gather kernel -> one FFMA kernel per layer -> scatter kernel
@@ -1216,6 +1248,14 @@ void fortis_gemm(float* Aa, float* A, long Ao, long As0, long As1, long At0, lon
     std::fprintf(stderr, "fortis_gemm: operands must be dense row-major (A %ldx%ld strides %ld,%ld; W %ldx%ld strides %ld,%ld; C %ldx%ld strides %ld,%ld)\n",
                  B, K, At0, At1, N, K, Wt0, Wt1, B, N, Ct0, Ct1);
     return;
+  }
+  if (B >= kF32TcMinRows) {
+    // large batch: the tensor-core kernel (three TF32 MMAs per product, fp32-class accuracy)
+    S();
+    ensure_aux(1);
+    std::string err;
+    if (f32tc_gemm(A + Ao, W + Wo, C + Co, B, (int)N, (int)K, S().d_status, stream(), &err)) return;
+    std::fprintf(stderr, "fortis_gemm: %s; using the FFMA kernel\n", err.c_str());
   }
   launch_linear_f32(A + Ao, W + Wo, nullptr, C + Co, B, (int)N, (int)K, ACT_NONE, 0.f, nullptr, nullptr, nullptr, stream());
 }

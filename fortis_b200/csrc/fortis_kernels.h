@@ -79,6 +79,26 @@ struct TcLaunch {
 int tc_grid(long long nrows);
 bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err);
 
+// ---- fp32-class Linear layers on the tensor cores, three TF32 MMAs per product (fortis_mlp_f32tc.cu) ----------------
+struct F32TcModel;                                     // split weights (W_hi, W_lo), TMA tensor maps, biases
+bool f32tc_supported(const ModelHost& M, std::string* why);
+F32TcModel* f32tc_create(const ModelHost& M, std::string* err);
+void f32tc_destroy(F32TcModel* m);
+struct F32TcLaunch {
+  int fast_in; const Access* slots; ArrayTable TG; long long cin[2][3];   // gather fused into layer 0 (table-driven) ...
+  const float* X;                                                          // ... or a materialised (rows, n_in) input
+  int fast_out; const Access* store_by_slot; ArrayTable TS; long long cout[2][3];   // scatter fused into the last epilogue ...
+  float* Y;                                                                // ... or a (rows, n_out) output
+  RowGeom g;
+  float* act[2]; long long act_ld;                   // two feature-major activation buffers [max width][act_ld], act_ld >= rows
+  double* partials; double* sum; unsigned int* done; // optional checksum of the fused scatter (partials: f32tc_grid() doubles)
+  int* status;
+};
+int f32tc_grid(long long nrows);
+bool f32tc_forward(F32TcModel* m, const F32TcLaunch& L, cudaStream_t s, std::string* err);
+// C[M][N] = A[M][K] . W[N][K]^T, row-major device operands (the memref entry fortis_gemm)
+bool f32tc_gemm(const float* A, const float* W, float* C, long long M, int N, int K, int* status, cudaStream_t s, std::string* err);
+
 // ---- conv3d network (fortis_conv3d.cu) -------------------------------------------------------------------------
 struct ConvModel;
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);

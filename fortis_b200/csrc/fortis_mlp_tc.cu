@@ -196,11 +196,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   }
   const uint32_t ring = base + kParkBytes;                      // kStages x 32 KB
   const uint32_t bars = ring + kRingBytes;
-  // barrier block: full [kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2] within the
-  // first 256 bytes; tmem base 256, abort flag 260, checksum scratch [272,336)
-  static_assert(8 * (2 * kStages + 9) <= 256, "the barriers must fit the first 256 bytes of the barrier block");
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages;
-  const uint32_t bar_acc_full = bars + 16 * kStages, bar_acc_empty = bar_acc_full + 16;
+  // barrier block: full [kIssuers][kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2]
+  // within the first 256 bytes; tmem base 256, abort flag 260, checksum scratch [272,336).
+  // Every stage has one "full" barrier PER ISSUER: a parity wait can only tell a barrier's current phase from the
+  // previous one, so each barrier needs a single waiter that sees every one of its phases; the TMA warp arms the
+  // barrier of the issuer that will consume the stage.
+  static_assert(8 * ((kIssuers + 1) * kStages + 9) <= 256, "the barriers must fit the first 256 bytes of the barrier block");
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kIssuers * kStages;
+  const uint32_t bar_acc_full = bar_empty + 8 * kStages, bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
   uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 256);
   volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 260);
@@ -217,7 +220,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   const long long ntiles = (P.nrows + kTileM - 1) / kTileM;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int s = 0; s < kIssuers * kStages; s++) mbar_init(bar_full + 8 * s, 1);
+    for (int s = 0; s < kStages; s++) mbar_init(bar_empty + 8 * s, 1);
     for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kEpiThreads); }
     for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kEpiThreads);
     for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, kIssuers);
@@ -266,22 +270,24 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     if constexpr (kRegRealloc) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
     if (warp == 8) {
       // ---------------------------------------------------------------- TMA producer (whole warp, one lane issues)
-      uint32_t s = 0, ph = 0;
+      uint32_t s = 0, ph = 0, acc_it = 0;
       PROF_DECL(blockIdx.x == 0 && lane == 0);
       bool stop = false;
       for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
         for (int l = 0; l < P.nlayers && !stop; l++) {
           const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const CUtensorMap* map = &P.maps[l];
-          for (int c = 0; c < nchunks && !stop; c++)
+          for (int c = 0; c < nchunks && !stop; c++, acc_it++) {
+            const uint32_t full_c = bar_full + 8 * kStages * (acc_it & 1);      // the barriers of the issuer that owns this chunk
             for (int ks = 0; ks < nkb * kSubStages; ks++) {
               PROF_ADD(17);
               if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
               PROF_ADD(16);
-              mbar_expect_tx(bar_full + 8 * s, kStageBytes);
-              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), bar_full + 8 * s);
+              mbar_expect_tx(full_c + 8 * s, kStageBytes);
+              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), full_c + 8 * s);
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
+          }
         }
     } else if (warp < 9 + kIssuers) {
       // ---------------------------------------------------------------- MMA issuers (whole warps, one lane issues)
@@ -290,7 +296,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       // owns accumulator w and all chunks that land in it; the pipe sees one in-order stream.  Both walk the same
       // chunk / stage sequence and skip what is not theirs.
       const uint32_t me = (uint32_t)(warp - 9);
-      uint32_t s = 0, ph = 0, acc_it = 0, lay_it = 0;
+      const uint32_t my_full = bar_full + 8 * kStages * me;
+      uint32_t s = 0, full_par = 0, acc_it = 0, lay_it = 0;     // full_par: bit s = parity of this issuer's next phase of stage s
       const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
       PROF_DECL(blockIdx.x == 0 && lane == 0 && me == 0);
       for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
@@ -300,15 +307,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           bool first = true, any = false;
           for (int c = 0; c < nchunks; c++, acc_it++) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
-            if (b != me) {
-              // The other issuer's chunk.  Its stages are stepped over one by one, each after its weights have landed:
-              // a parity wait can only tell the current phase of a barrier from the previous one, so an issuer must
-              // see every phase of a stage barrier complete before it waits for the next one (the ring can be exactly
-              // one chunk long, which would put this issuer a whole lap ahead of the other).
-              for (int ks = 0; ks < nkb * kSubStages; ks++) {
-                wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
-                if (++s == kStages) { s = 0; ph ^= 1; }
-              }
+            if (b != me) {                                    // the other issuer's chunk: step over its stages
+              s = (s + (uint32_t)(nkb * kSubStages)) % kStages;
               continue;
             }
             any = true;
@@ -328,7 +328,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
               for (int sub = 0; sub < kSubStages; sub++) {
                 PROF_ADD(0);
-                wait_bar(bar_full + 8 * s, ph, abort_flag, P.status, ST_FULL);
+                wait_bar(my_full + 8 * s, (full_par >> s) & 1u, abort_flag, P.status, ST_FULL);
+                full_par ^= 1u << s;
                 PROF_ADD(3);
                 tc_fence_after();
                 // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
@@ -341,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 for (int j = 1; j < kStageK / 16; j++)
                   tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
                 tc_commit(bar_empty + 8 * s);                 // stage reusable once these MMAs have read it
-                if (++s == kStages) { s = 0; ph ^= 1; }
+                if (++s == kStages) s = 0;
               }
               if (mine_last) {
                 // this issuer's last MMAs on K-block kb in this layer: once both issuers' have retired, those columns

@@ -67,11 +67,18 @@ def build_ref_rt(verbose=True):
         return out if os.path.exists(out) else None
     os.makedirs(out_dir, exist_ok=True)
     if _stale(out, [rt, fft]):
-        cmd = ["nvcc", "-O2", "-lineinfo"] + ARCH + ["-shared", "-Xcompiler", "-fPIC", "-x", "cu", rt, fft, "-o", out,
-               "-lcublas", "-lcudnn", "-lcufft", "-lcudart"]
-        if verbose:
-            print(" ".join(cmd))
-        subprocess.run(cmd, check=True)
+        # fortis_rt.c is C (its entry names must stay unmangled: fortis_fft.cu and generated code call them), so it goes
+        # through gcc; the .cu file through nvcc, which also links
+        cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+        obj = os.path.join(out_dir, "fortis_rt.o")
+        cmds = [["gcc", "-O2", "-fPIC", "-I" + cuda_inc, "-c", rt, "-o", obj],
+                ["nvcc", "-O2", "-lineinfo"] + ARCH + ["-shared", "-Xcompiler", "-fPIC", fft, obj, "-o", out,
+                 "-lcublas", "-lcudnn", "-lcufft", "-lcudart"]]
+        for cmd in cmds:
+            if verbose:
+                print(" ".join(cmd))
+            subprocess.run(cmd, check=True)
+        os.remove(obj)
     return out
 
 

@@ -473,3 +473,69 @@ def test_gemm_entry_refuses_strided_operands(host):
                   C.data_ptr(), C.data_ptr(), 0, Bn, N, N, 1, Bn, N, K)
     host.sync()
     assert float(C.min()) == -3.0 and float(C.max()) == -3.0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# fp32 on the tensor cores (three TF32 MMAs per product): batches of 512 rows and more
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("Bn,N,K", [(4096, 300, 200), (777, 64, 33), (513, 768, 768)])
+def test_gemm_entry_large_batch(host, Bn, N, K):
+    """fortis_gemm at batch sizes the split-TF32 kernel takes, shapes that are multiples of no tile; against fp64."""
+    rng = np.random.default_rng(14)
+    A = torch.from_numpy(rng.normal(size=(Bn, K)).astype(np.float32)).cuda()
+    W = torch.from_numpy(rng.normal(size=(N, K)).astype(np.float32)).cuda()
+    C = torch.full((Bn, N), float("nan"), dtype=torch.float32, device="cuda")
+    L = host.L
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    L.fortis_gemm.argtypes = [vp, vp, cl, cl, cl, cl, cl] * 3 + [cl, cl, cl]
+    for _ in range(2):                      # the second call takes the cached split of W
+        L.fortis_gemm(A.data_ptr(), A.data_ptr(), 0, Bn, K, K, 1, W.data_ptr(), W.data_ptr(), 0, N, K, K, 1,
+                      C.data_ptr(), C.data_ptr(), 0, Bn, N, N, 1, Bn, N, K)
+        host.sync()
+        want = A.cpu().numpy().astype(np.float64) @ W.cpu().numpy().astype(np.float64).T
+        got = C.cpu().numpy()
+        assert np.isfinite(got).all()
+        assert fo.rel_l2(got, want) < 2e-6
+    assert L.fortis_device_status() == 0
+
+
+def test_array_form_fp32_large_batch_with_norms_and_mask(host):
+    """mlp_forward_batched(in, out) on 3,000 rows in fp32: row-major input and output around the tensor-core layers,
+    with the input divide, the output multiply and the masked final ReLU."""
+    rows, dims = 3000, [30, 100, 50, 7]
+    layers = fortis_b200.mlp_layers(dims, seed=21, act="leaky", slope=0.15, bias="uniform", scale=0.2)
+    rng = np.random.default_rng(22)
+    in_div, out_mul = (rng.random(30) + 0.5).astype(np.float32), (rng.random(7) + 0.5).astype(np.float32)
+    mask = np.array([0, 1, 0, 0, 1, 1, 0], np.float32)
+    X = rng.normal(size=(rows, 30)).astype(np.float32)
+    host.load_model(fortis_b200.write_blob(layers, in_div=in_div, out_mul=out_mul, relu_mask=mask))
+    host.L.fortis_begin(rows)
+    Y = np.zeros((rows, 7), np.float32)
+    host.forward_batched(X, Y)
+    want = fo.mlp_forward(layers, X, in_norms=in_div, out_norms=out_mul)
+    want[:, mask != 0] = np.maximum(want[:, mask != 0], 0)
+    assert fo.rel_l2(Y, want) < FP32_TOL
+    assert host.L.fortis_device_status() == 0
+
+
+def test_reference_runtime_gemm_agrees(host):
+    """Second checker for fortis_gemm: the reference's own runtime (runtime/fortis_rt.c compiled unchanged under
+    oracle/_ref: cuBLAS SGEMM on pre-transposed weights) on the same operands."""
+    so = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libfortis_ref_rt.so")
+    if not os.path.exists(so):
+        pytest.skip("oracle/_ref/libfortis_ref_rt.so was not built (needs the reference checkout at build time)")
+    ref = ctypes.CDLL(so, mode=ctypes.RTLD_LOCAL | os.RTLD_DEEPBIND)
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    for fn in (ref.fortis_gemm, host.L.fortis_gemm):
+        fn.argtypes = [vp, vp, cl, cl, cl, cl, cl] * 3 + [cl, cl, cl]
+        fn.restype = None
+    rng = np.random.default_rng(33)
+    for (Bn, N, K) in [(64, 40, 24), (2048, 768, 244)]:
+        A = torch.from_numpy(rng.normal(size=(Bn, K)).astype(np.float32)).cuda()
+        W = torch.from_numpy(rng.normal(size=(N, K)).astype(np.float32)).cuda()
+        C0, C1 = torch.zeros((Bn, N), device="cuda"), torch.zeros((Bn, N), device="cuda")
+        for fn, C in ((ref.fortis_gemm, C0), (host.L.fortis_gemm, C1)):
+            fn(A.data_ptr(), A.data_ptr(), 0, Bn, K, K, 1, W.data_ptr(), W.data_ptr(), 0, N, K, K, 1, C.data_ptr(), C.data_ptr(), 0, Bn, N, N, 1, Bn, N, K)
+        torch.cuda.synchronize()
+        host.sync()
+        assert fo.rel_l2(C1.cpu().numpy(), C0.cpu().numpy()) < 2e-6
