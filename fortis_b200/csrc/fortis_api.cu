@@ -118,7 +118,7 @@ struct Session {
   ModelHost model;
   std::vector<float*> dW, dB;
   float *d_in_div = nullptr, *d_out_mul = nullptr, *d_relu_mask = nullptr;
-  bool small_ok = false;
+  bool small_ok = false, stencil_ok = false;
   TcModel* tc = nullptr;
   F32TcModel* f32 = nullptr;                   // fp32 precision on the tensor cores (split TF32), large batches
   ConvModel* conv = nullptr;
@@ -191,7 +191,7 @@ void free_model_dev() {
   if (s.f32) { f32tc_destroy(s.f32); s.f32 = nullptr; }
   if (s.conv) { conv_model_destroy(s.conv); s.conv = nullptr; }
   s.model_on_dev = false;
-  s.small_ok = false;
+  s.small_ok = false; s.stencil_ok = false;
 }
 
 void upload_plan(PlanDev& P) {
@@ -322,6 +322,13 @@ void ensure_model() {
                                     s.model.out_mul.empty() ? nullptr : s.model.out_mul.data(), img.data());
       if (cuda_ok(small_mlp_upload(img.data(), nf, st), "small-MLP constant upload")) s.small_ok = true;
       cudaStreamSynchronize(st);
+    }
+    if (s.precision == PREC_F32 && stencil_mlp_supported(nl, dims.data()) && s.model.relu_mask.empty()) {
+      std::vector<const float*> W, B;
+      for (auto& L : s.model.layers) { W.push_back(L.W.data()); B.push_back(L.b.data()); }
+      if (cuda_ok(stencil_mlp_upload(nl, dims.data(), W.data(), B.data(), s.model.in_div.empty() ? nullptr : s.model.in_div.data(),
+                                     s.model.out_mul.empty() ? nullptr : s.model.out_mul.data(), st), "stencil-MLP constant upload"))
+        s.stencil_ok = true;
     }
     if (s.precision == PREC_F32) {
       std::string err;
@@ -592,6 +599,41 @@ void scatter_with_checksum(const StepArgs& A, const RowGeom& g) {
   if (partials) launch_fold(s.d_partials, grid, s.d_sum, 1, st);
 }
 
+// Operands of the packed-FMA stencil kernel: a fused step whose gather is the 3x3 stencil of three fp32 fields in
+// field-major, j-major, i-fastest slot order with unit i stride, without lifted expressions, and whose stores are fp32
+// with unit i stride.
+bool stencil_operands(const StepArgs& A, const RowGeom& g, StencilLaunch* L) {
+  Session& s = S();
+  std::memset(L, 0, sizeof *L);
+  const IoPlanHost& G = s.G.h;
+  const IoPlanHost& Sc = s.S.h;
+  if (G.prog.nops || !G.scalars.empty() || Sc.prog.nops || !Sc.scalars.empty() || G.slots.size() != 27 || g.kk0 != 0) return false;
+  if (Sc.stores.empty() || Sc.stores.size() > 4) return false;
+  const Access& c0 = G.slots[4];
+  for (int f = 0; f < 3; f++) {
+    const Access& c = G.slots[f * 9 + 4];
+    if (c.elt != 0 || c.si != 1 || c.sj != c0.sj || c.sk != c0.sk) return false;
+    for (int dj = 0; dj < 3; dj++)
+      for (int di = 0; di < 3; di++) {
+        const Access& a = G.slots[f * 9 + dj * 3 + di];
+        if (a.array != c.array || a.elt != 0 || a.si != 1 || a.sj != c.sj || a.sk != c.sk || a.off0 - c.off0 != (di - 1) + (dj - 1) * c.sj) return false;
+      }
+    L->in[f] = (const float*)A.TG.base[c.array] + c.off0;
+  }
+  const Access& o0 = Sc.stores[0].a;
+  for (size_t q = 0; q < Sc.stores.size(); q++) {
+    const Access& a = Sc.stores[q].a;
+    if (a.elt != 0 || a.si != 1 || a.sj != o0.sj || a.sk != o0.sk || Sc.stores[q].slot > 3) return false;
+    L->out[q] = (float*)A.TS.base[a.array] + a.off0;
+    L->out_slot[q] = Sc.stores[q].slot;
+  }
+  L->nstores = (int)Sc.stores.size();
+  L->sj_in = c0.sj; L->sk_in = c0.sk; L->sj_out = o0.sj; L->sk_out = o0.sk;
+  L->ni = g.ni; L->nj = (int)(g.count / g.ni); L->nk = g.nk;
+  if ((long long)L->ni * L->nj != g.count) return false;
+  return true;
+}
+
 void run_step_kernels(const StepArgs& A) {
   Session& s = S();
   cudaStream_t st = stream();
@@ -630,6 +672,22 @@ void run_step_kernels(const StepArgs& A) {
     if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
     if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);
     return;
+  }
+  if (fused_gather && A.fuse_scatter && s.stencil_ok) {
+    StencilLaunch SL;
+    if (stencil_operands(A, g, &SL)) {
+      std::vector<int> dims{s.model.n_in()};
+      bool relu_only = true;
+      for (int l = 0; l < nl; l++) {
+        const LayerHost& L = s.model.layers[l];
+        dims.push_back(L.cout);
+        SL.slope[l] = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;
+        if (l < nl - 1 && L.act != ACT_RELU) relu_only = false;
+      }
+      SL.has_in_div = !s.model.in_div.empty(); SL.has_out_mul = !s.model.out_mul.empty();
+      if (s.want_checksum) { ensure_aux(stencil_mlp_grid(SL)); SL.partials = s.d_partials; SL.sum = s.d_sum; SL.done = s.d_done; }
+      if (launch_stencil_mlp(nl, dims.data(), relu_only, SL, st)) return;
+    }
   }
   if (fused_gather && s.small_ok) {
     std::vector<int> dims{s.model.n_in()};

@@ -53,6 +53,22 @@ int small_mlp_pack(int nlayers, const int* dims, const float* const* W, const fl
 cudaError_t small_mlp_upload(const float* host, int nfloats, cudaStream_t s);
 void launch_small_mlp(int nlayers, const int* dims, const SmallMlpLaunch& L, cudaStream_t s);
 
+// ---- 3x3-stencil hosts: packed-FMA fused kernel (fortis_stencil_mlp.cu) ---------------------------------------
+struct StencilLaunch {
+  const float* in[3];             // per field: the element the CENTRE tap of point (0, 0) of plane 0 reads
+  float* out[4]; int out_slot[4]; int nstores;      // per store: the element point (0, 0, 0) writes, and which model output
+  long long sj_in, sk_in, sj_out, sk_out;           // element strides of the j index and of the plane (i has stride 1)
+  int ni, nj, nk;                 // interior extent
+  int has_in_div, has_out_mul;
+  float slope[3];                 // act(v) = max(v, v * slope) per layer (ignored for hidden layers of an all-ReLU net)
+  double* partials; double* sum; unsigned int* done;   // optional checksum (partials: stencil_mlp_grid() doubles)
+};
+bool stencil_mlp_supported(int nlayers, const int* dims);     // 27 inputs, hidden widths <= 32 (equal after padding), <= 4 outputs
+cudaError_t stencil_mlp_upload(int nlayers, const int* dims, const float* const* W, const float* const* b, const float* in_div,
+                               const float* out_mul, cudaStream_t s);
+int stencil_mlp_grid(const StencilLaunch& S);
+bool launch_stencil_mlp(int nlayers, const int* dims, bool relu_only, const StencilLaunch& S, cudaStream_t st);
+
 // ---- tensor-core fused MLP (fortis_mlp_tc.cu) ----------------------------------------------------------------
 struct ModelHost;
 struct TcModel;                                        // packed bf16 weights, TMA tensor maps, biases, scales
