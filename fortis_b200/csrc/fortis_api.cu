@@ -56,6 +56,25 @@ cudaStream_t stream() {
   return g_stream;
 }
 
+// Copy streams of the overlapped staging path: column chunks travel host -> device on one, device -> host on the other,
+// while the step kernels run on the persistent stream.
+constexpr int kMaxChunks = 16;
+cudaStream_t g_h2d = nullptr, g_d2h = nullptr;
+cudaEvent_t g_ev_in[kMaxChunks] = {}, g_ev_k[kMaxChunks] = {}, g_ev_fork = nullptr, g_ev_join_in = nullptr, g_ev_join_out = nullptr;
+bool ensure_copy_streams() {
+  if (g_h2d) return true;
+  if (cudaStreamCreateWithFlags(&g_h2d, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&g_d2h, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); g_h2d = g_d2h = nullptr; return false; }
+  for (int i = 0; i < kMaxChunks; i++) {
+    cudaEventCreateWithFlags(&g_ev_in[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&g_ev_k[i], cudaEventDisableTiming);
+  }
+  cudaEventCreateWithFlags(&g_ev_fork, cudaEventDisableTiming);
+  cudaEventCreateWithFlags(&g_ev_join_in, cudaEventDisableTiming);
+  cudaEventCreateWithFlags(&g_ev_join_out, cudaEventDisableTiming);
+  return true;
+}
+
 // The policy restates runtime/fortis_rt.c:14-40 (it IS the contract of fortis_alloc / fortis_free): 256 slots, best
 // fit among released buffers, cudaMalloc on a miss, release every unused buffer and retry once, 0 + message on failure.
 constexpr int kPool = 256;
@@ -145,6 +164,9 @@ struct Session {
   cudaGraphExec_t gexec = nullptr;
   std::string gkey;
   int ncalls = 0;
+  cudaGraphExec_t ov_gexec = nullptr;        // the chunked staging pipeline of a step over host arrays, as one graph
+  std::string ov_key;
+  int ov_calls = 0;
 };
 Session* g_S = nullptr;
 Session& S() {
@@ -178,6 +200,9 @@ void drop_graph() {
   if (s.gexec) { cudaGraphExecDestroy(s.gexec); s.gexec = nullptr; }
   s.gkey.clear();
   s.ncalls = 0;
+  if (s.ov_gexec) { cudaGraphExecDestroy(s.ov_gexec); s.ov_gexec = nullptr; }
+  s.ov_key.clear();
+  s.ov_calls = 0;
 }
 
 void free_model_dev() {
@@ -912,6 +937,123 @@ bool ranges_overlap(const void* a, size_t na, const void* b, size_t nb) {
   return a0 < b0 + nb && b0 < a0 + na;
 }
 
+// Overlapped staging of a fused step over HOST arrays (the reference's per-call H2D of every plane and D2H of every
+// visited rectangle, driver/fortis_gather_emit.py:66-68, 91-96, serialises copies and kernels on one stream).  For
+// column layouts (one loop over the arrays' first, unit-stride dimension, no plane loop) the column range is cut into
+// chunks: chunk c's slices of the input arrays go up on the H2D stream, the step kernels run on chunk c as soon as they
+// have landed, and chunk c's slices of the stored arrays come back on the D2H stream while chunk c+1 computes and
+// chunk c+2 uploads.  Returns false when the call is not of that shape (the caller then takes the serial path).
+bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
+  Session& s = S();
+  if (s.loop.kdist || s.loop.has_outer || s.loop.nk != 1 || !s.fuse || rows < 4096 || std::getenv("FORTIS_NO_OVERLAP")) return false;
+  const long long ncol = rows;
+  bool any_host = false;
+  auto column_array = [&](const ArrayInfo& a) { return a.vdims.empty() && !a.shape.empty() && a.shape[0] == ncol && a.total % ncol == 0; };
+  for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+    const ArrayInfo& a = s.G.h.arrays[ai];
+    if (!a.used) continue;
+    if (!column_array(a)) return false;
+    if (!is_device_ptr(gptrs[ai])) any_host = true;
+  }
+  for (auto& x : s.G.h.slots) if (x.si != 1) return false;
+  for (auto& x : s.G.h.scalars) if (x.si != 1) return false;
+  for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++) {
+    const ArrayInfo& a = s.S.h.arrays[ai];
+    if (!a.used) continue;
+    if (!column_array(a) || !s.S.h.written[ai]) return false;       // arrays a scatter only reads would need a whole upload
+    if (!is_device_ptr(sptrs[ai])) any_host = true;
+  }
+  for (auto& t : s.S.h.stores) if (t.a.si != 1) return false;
+  if (!any_host || !ensure_copy_streams()) return false;
+
+  cudaStream_t st = stream();
+  // The pipeline is a fixed sequence of copies, kernels and event edges for a given set of array addresses: from the
+  // second call on it is replayed as one CUDA graph (some 150 API calls per step otherwise, which would leave the GPU
+  // waiting for the host).  Call 1 runs eagerly (it pins the arrays and sizes every buffer), call 2 is captured.
+  std::string key((const char*)&rows, sizeof rows);
+  key.append((const char*)gptrs, sizeof(void*) * s.G.h.arrays.size());
+  key.append((const char*)sptrs, sizeof(void*) * s.S.h.arrays.size());
+  if (s.ov_gexec && key == s.ov_key) {
+    cuda_ok(cudaGraphLaunch(s.ov_gexec, st), "cudaGraphLaunch");
+    if (!s.async) cudaStreamSynchronize(st);
+    return true;
+  }
+  if (key != s.ov_key) {
+    if (s.ov_gexec) { cudaGraphExecDestroy(s.ov_gexec); s.ov_gexec = nullptr; }
+    s.ov_key = key; s.ov_calls = 0;
+  }
+  int args[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  StepArgs A;
+  A.use_gather = true; A.fuse_scatter = true;
+  // pins the arrays, sizes the staging buffers; the copies themselves are issued per chunk below
+  bind_arrays(s.G, gptrs, args, 0, false, false, &A.TG);
+  bind_arrays(s.S, sptrs, args, 0, false, false, &A.TS);
+  const ArrayTable TG0 = A.TG, TS0 = A.TS;
+  int nchunks = (int)(ncol / 4096 < 8 ? ncol / 4096 : 8);
+  if (nchunks < 1) nchunks = 1;
+  const long long per = ((ncol + nchunks - 1) / nchunks + 127) / 128 * 128;     // whole 128-row tiles
+
+  bool capturing = (++s.ov_calls == 2) && !std::getenv("FORTIS_NO_STAGING_GRAPH");
+  if (capturing && cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); capturing = false; }
+  if (capturing) fortis_capturing = 1;
+  bool threw = false; std::string what;
+  try {
+    // fork: both copy streams start behind everything already on the persistent stream (the previous step included)
+    cudaEventRecord(g_ev_fork, st);
+    cudaStreamWaitEvent(g_h2d, g_ev_fork, 0);
+    cudaStreamWaitEvent(g_d2h, g_ev_fork, 0);
+    int c = 0;
+    for (long long c0 = 0; c0 < ncol; c0 += per, c++) {
+      const long long n = ncol - c0 < per ? ncol - c0 : per;
+      for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+        const ArrayInfo& a = s.G.h.arrays[ai];
+        if (!a.used) continue;
+        const size_t es = elt_size(a.elt);
+        if (!s.G.on_dev[ai])
+          cuda_ok(cudaMemcpy2DAsync((char*)s.G.stage[ai] + c0 * es, (size_t)ncol * es, (const char*)gptrs[ai] + c0 * es, (size_t)ncol * es,
+                                    (size_t)n * es, (size_t)(a.total / ncol), cudaMemcpyHostToDevice, g_h2d), "H2D of a column chunk");
+        A.TG.base[ai] = (char*)TG0.base[ai] + c0 * es;
+      }
+      cudaEventRecord(g_ev_in[c], g_h2d);
+      cudaStreamWaitEvent(st, g_ev_in[c], 0);
+      for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++)
+        if (s.S.h.arrays[ai].used) A.TS.base[ai] = (char*)TS0.base[ai] + c0 * elt_size(s.S.h.arrays[ai].elt);
+      A.rows = n;
+      run_step_kernels(A);
+      cudaEventRecord(g_ev_k[c], st);
+      cudaStreamWaitEvent(g_d2h, g_ev_k[c], 0);
+      for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++) {
+        const ArrayInfo& a = s.S.h.arrays[ai];
+        if (!a.used || s.S.on_dev[ai]) continue;
+        const size_t es = elt_size(a.elt);
+        cuda_ok(cudaMemcpy2DAsync((char*)sptrs[ai] + c0 * es, (size_t)ncol * es, (const char*)s.S.stage[ai] + c0 * es, (size_t)ncol * es,
+                                  (size_t)n * es, (size_t)(a.total / ncol), cudaMemcpyDeviceToHost, g_d2h), "D2H of a column chunk");
+      }
+    }
+    // join: the persistent stream continues behind the last upload and the last download
+    cudaEventRecord(g_ev_join_in, g_h2d);
+    cudaStreamWaitEvent(st, g_ev_join_in, 0);
+    cudaEventRecord(g_ev_join_out, g_d2h);
+    cudaStreamWaitEvent(st, g_ev_join_out, 0);
+  } catch (const std::exception& e) { threw = true; what = e.what(); }
+  if (capturing) {
+    fortis_capturing = 0;
+    cudaGraph_t gr = nullptr;
+    const bool ok = cudaStreamEndCapture(st, &gr) == cudaSuccess && !threw && cudaGraphInstantiate(&s.ov_gexec, gr, 0) == cudaSuccess;
+    if (gr) cudaGraphDestroy(gr);
+    if (ok) cuda_ok(cudaGraphLaunch(s.ov_gexec, st), "cudaGraphLaunch");
+    else {
+      s.ov_gexec = nullptr; cudaGetLastError();
+      if (threw) throw std::runtime_error(what);
+      std::fprintf(stderr, "fortis: capture of the staging pipeline failed, running eagerly\n");
+      s.ov_calls = 2;                                   // do not try again for this set of arrays
+      return overlapped_step(gptrs, sptrs, rows);
+    }
+  } else if (threw) throw std::runtime_error(what);
+  if (!s.async) cudaStreamSynchronize(st);
+  return true;
+}
+
 // The fused step: gather -> forward -> scatter of every plane in one launch.  `iargs` are the enclosing-loop
 // indices (1-based) that select the plane of arrays with "v" subscripts when the loop is NOT k-distributed; a
 // k-distributed loop takes none (all planes klo .. klo+nk-1 are processed).
@@ -938,6 +1080,7 @@ void do_step(const int* iargs, int nint, void* const* gptrs, int ng, void* const
       throw std::runtime_error("fortis_step: the descriptors select a plane by " + std::to_string(need) +
                                " enclosing-loop index argument(s) and the loop is not k-distributed; pass them first");
   }
+  if (overlapped_step(gptrs, sptrs, rows)) return;
   cudaStream_t st = stream();
   int args[8];
   for (int i = 0; i < 8; i++) args[i] = i < nint ? iargs[i] : 1;
@@ -1057,6 +1200,8 @@ int fortis_set_option(const char* key, const char* value) {
   else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
   else if (k == "async") { s.async = v != "0"; }
   else if (k == "checksum") { s.want_checksum = v != "0"; drop_graph(); }
+  else if (k == "test_wait_limit") { g_tc_test.wait_limit = (unsigned int)std::strtoul(v.c_str(), nullptr, 10); drop_graph(); }
+  else if (k == "test_skip_stage") { g_tc_test.skip_stage = v != "0"; drop_graph(); }
   else if (k == "conv_shape") {
     if (std::sscanf(v.c_str(), "%d,%d,%d,%d", &s.conv_shape[0], &s.conv_shape[1], &s.conv_shape[2], &s.conv_shape[3]) != 4)
       throw std::runtime_error("conv_shape must be N,D,H,W");
@@ -1067,6 +1212,7 @@ int fortis_set_option(const char* key, const char* value) {
 }
 
 void fortis_reset(void) {
+  g_tc_test = TcTestKnobs{0u, 0};
   if (!g_S) return;
   if (g_stream) cudaStreamSynchronize(g_stream);
   Session& s = S();
@@ -1460,6 +1606,13 @@ int fortis_device_status(void) {
   cudaStreamSynchronize(stream());
   cudaMemcpy(&v, s.d_status, sizeof(int), cudaMemcpyDeviceToHost);
   if (v == 0 && s.conv) v = conv_model_status(s.conv);
+  if (v != 0) {
+    // reading a failure clears it (and re-arms the in-kernel checksum fold, which an aborted launch may have left
+    // half way), so that the next step starts clean
+    cudaMemset(s.d_status, 0, sizeof(int));
+    if (s.d_done) cudaMemset(s.d_done, 0, sizeof(unsigned int));
+    if (s.conv) conv_model_clear_status(s.conv);
+  }
   return v;
   FORTIS_CATCH(return -1)
 }

@@ -163,6 +163,7 @@ void conv_model_destroy(ConvModel* m) {
 }
 
 int conv_model_status(ConvModel* m) { return m && m->tcm ? conv_tc_status(m->tcm) : 0; }
+void conv_model_clear_status(ConvModel* m) { if (m && m->tcm) conv_tc_clear_status(m->tcm); }
 
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err) {
   (void)s;

@@ -101,6 +101,8 @@ struct ConvTcParams {
   long long P;                 // padded rows
   float slope;                 // act(v) = max(v, v * slope)
   int* status;
+  unsigned int wait_limit;     // polls before a barrier wait gives up
+  int test_skip_stage;         // test only: the first pair's leader never loads its first activation stage
   long long* prof;             // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
 };
 
@@ -177,10 +179,11 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
         // rows on both sides, so every coordinate is in bounds.
         const int y0 = (int)(q0 + (long long)(kd - 1) * Hp * Wp - Wp) + P.front;
         cprof_add(P.prof, 7, &pt, pw);
-        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY)) { stop = true; break; }
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY, P.wait_limit)) { stop = true; break; }
         cprof_add(P.prof, 6, &pt, pw);
         if (crank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * P.nbox * P.box_rows * kC * 2);
-        for (int bx = 0; bx < P.nbox; bx++)
+        const bool skip = P.test_skip_stage && blockIdx.x == 0 && tp == pair0 && kd == 0;     // test only: the stage never completes
+        for (int bx = 0; bx < P.nbox && !skip; bx++)
           tma_load_2d_pair(ring + s * P.stage_bytes + bx * P.box_rows * kC * 2, &P.amap, 0, y0 + bx * P.box_rows, full0 + 8 * s);
         if (++s == (uint32_t)P.nstages) { s = 0; ph ^= 1; }
       }
@@ -193,18 +196,18 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       const uint64_t desc_hi = make_kmajor_sw128_desc(0) & 0xFFFFFFFF00000000ull;
       const bool pw = blockIdx.x == 0 && lane == 0;
       long long pt = clock64();
-      mbar_wait(bar_w, 0, abort_flag, P.status, CST_WEIGHTS);
+      mbar_wait(bar_w, 0, abort_flag, P.status, CST_WEIGHTS, P.wait_limit);
       cprof_add(P.prof, 3, &pt, pw);
       for (long long tp = pair0; tp < npairs; tp += pair_step, acc_it++) {
         const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
         cprof_add(P.prof, 2, &pt, pw);
-        mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY);
+        mbar_wait(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, CST_ACC_EMPTY, P.wait_limit);
         cprof_add(P.prof, 0, &pt, pw);
         tc_fence_after();
         const uint32_t d_tmem = tmem + b * kAccStride;
         for (int kd = 0; kd < 3; kd++) {
           cprof_add(P.prof, 2, &pt, pw);
-          mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL);
+          mbar_wait(bar_full + 8 * s, ph, abort_flag, P.status, CST_FULL, P.wait_limit);
           cprof_add(P.prof, 1, &pt, pw);
           tc_fence_after();
           const uint32_t sa = ring + s * P.stage_bytes;
@@ -271,7 +274,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       locate(tp + pair_step, np, nwrites, ninterior, nwp, nhp, ndp, nn);
       const bool nuse_skip = !LAST && P.skip != nullptr && ninterior;
       cprof_add(P.prof, 10, &pt, pw);
-      mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL);
+      mbar_wait(bar_acc_full + 8 * b, aph, abort_flag, P.status, CST_ACC_FULL, P.wait_limit);
       cprof_add(P.prof, 8, &pt, pw);
       tc_fence_after();
       const uint32_t accb = lane_addr + b * kAccStride + c0;
@@ -576,6 +579,8 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
     P_.skip = (L.flags & LFLAG_ADD_SKIP) ? m->buf[skip] + m->front * kC : nullptr;
     P_.out = m->buf[dst] + m->front * kC; P_.y = y; P_.F = L.cout; P_.front = (int)m->front;
     P_.stage_bytes = geom.stage_bytes; P_.nstages = geom.nstages; P_.box_rows = geom.box_rows; P_.nbox = geom.nbox;
+    P_.wait_limit = g_tc_test.wait_limit ? g_tc_test.wait_limit : kWaitLimit;
+    P_.test_skip_stage = g_tc_test.skip_stage;
     P_.D = D; P_.H = H; P_.W = W; P_.P = P; P_.slope = slope_of(L); P_.status = m->status; P_.prof = (want_prof && l == 2) ? dprof : nullptr;
     const cudaError_t le = m->f16 ? (l == nl - 1 ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<4, kEdgeC, true, true>, P_)
                                      : l == 0    ? cudaLaunchKernelEx(&cfg, conv3d_tc_kernel<1, kC, false, true>, P_)
@@ -597,6 +602,10 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("tensor-core conv launch: ") + cudaGetErrorString(e); return false; }
   return true;
+}
+
+void conv_tc_clear_status(ConvTcModel* m) {
+  if (m && m->status) cudaMemset(m->status, 0, sizeof(int));
 }
 
 int conv_tc_status(ConvTcModel* m) {

@@ -69,6 +69,12 @@ cudaError_t stencil_mlp_upload(int nlayers, const int* dims, const float* const*
 int stencil_mlp_grid(const StencilLaunch& S);
 bool launch_stencil_mlp(int nlayers, const int* dims, bool relu_only, const StencilLaunch& S, cudaStream_t st);
 
+// Test knobs of the tensor-core kernels (set through fortis_set_option "test_wait_limit" / "test_skip_stage"; both 0
+// in normal operation): a short poll limit for the bounded barrier waits, and "the first CTA's TMA warp does not load
+// its first stage", which makes a wait run out so that the give-up path can be exercised without hanging anything.
+struct TcTestKnobs { unsigned int wait_limit; int skip_stage; };
+extern TcTestKnobs g_tc_test;
+
 // ---- tensor-core fused MLP (fortis_mlp_tc.cu) ----------------------------------------------------------------
 struct ModelHost;
 struct TcModel;                                        // packed bf16 weights, TMA tensor maps, biases, scales
@@ -119,7 +125,8 @@ bool f32tc_gemm(const float* A, const float* W, float* C, long long M, int N, in
 struct ConvModel;
 ConvModel* conv_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
 void conv_model_destroy(ConvModel* m);
-int conv_model_status(ConvModel* m);        // 0, or the code of a bounded wait that gave up in the tensor-core conv kernel
+int conv_model_status(ConvModel* m);
+void conv_model_clear_status(ConvModel* m);        // 0, or the code of a bounded wait that gave up in the tensor-core conv kernel
 // x (N,D,H,W,Cin) fp32 NDHWC on the device -> y (N,D,H,W,Cout)
 bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 // single layer, NCDHW fp32 (the memref ABI of runtime/fortis_rt.c:128-131)
@@ -133,6 +140,7 @@ ConvTcModel* conv_tc_create(const ModelHost& M, bool f16, std::string* err);
 void conv_tc_destroy(ConvTcModel* m);
 bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 int conv_tc_status(ConvTcModel* m);
+void conv_tc_clear_status(ConvTcModel* m);
 
 void launch_checksum(const void* data, long long n, int elt, double* partials, double* out, int accumulate, cudaStream_t s);
 void launch_fold(const double* partials, int n, double* out, int accumulate, cudaStream_t s);

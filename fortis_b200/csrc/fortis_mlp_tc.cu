@@ -124,6 +124,8 @@ struct TcParams {
   double* sum;                           // with partials: the last CTA to finish folds them into *sum (accumulating), in index order
   unsigned int* done;                    // CTA completion counter for that fold (zero between launches)
   int* status;
+  unsigned int wait_limit;               // polls before a barrier wait gives up
+  int test_skip_stage;                   // test only: CTA 0 never loads its first weight stage
   long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
   // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
   // (array, class, constant offset) triples are unpacked into shared memory once per CTA
@@ -177,9 +179,9 @@ __device__ __forceinline__ float4 ldg4_here(const float* p) {
 #endif
 
 // the kernel's bounded barrier wait: inlined where warpgroups get different register budgets (a call would stop that)
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit) {
   if constexpr (kRegRealloc || kInlineWait) return mbar_wait_inline(bar, parity, abort_flag, status, code);
-  else return mbar_wait(bar, parity, abort_flag, status, code);
+  else return mbar_wait(bar, parity, abort_flag, status, code, limit);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -281,10 +283,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             const uint32_t full_c = bar_full + 8 * kStages * (acc_it & 1);      // the barriers of the issuer that owns this chunk
             for (int ks = 0; ks < nkb * kSubStages; ks++) {
               PROF_ADD(17);
-              if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY)) { stop = true; break; }
+              if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY, P.wait_limit)) { stop = true; break; }
               PROF_ADD(16);
-              mbar_expect_tx(full_c + 8 * s, kStageBytes);
-              tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), full_c + 8 * s);
+              const bool skip = P.test_skip_stage && blockIdx.x == 0 && tile == 0 && l == 0 && c == 0 && ks == 0;   // test only
+              if (!skip) {
+                mbar_expect_tx(full_c + 8 * s, kStageBytes);
+                tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), full_c + 8 * s);
+              }
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
           }
@@ -315,20 +320,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             // this issuer's last chunk of the layer: no later chunk lands in accumulator `me`
             const bool mine_last = c + kIssuers >= nchunks;
             PROF_ADD(0);
-            wait_bar(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY);
+            wait_bar(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY, P.wait_limit);
             PROF_ADD(2);
             tc_fence_after();
             const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
             for (int kb = 0; kb < nkb; kb++) {
               if (first) {                                    // K-block kb of this layer's A is in tensor memory
                 PROF_ADD(0);
-                wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
+                wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY, P.wait_limit);
                 PROF_ADD(1);
               }
 #pragma unroll
               for (int sub = 0; sub < kSubStages; sub++) {
                 PROF_ADD(0);
-                wait_bar(my_full + 8 * s, (full_par >> s) & 1u, abort_flag, P.status, ST_FULL);
+                wait_bar(my_full + 8 * s, (full_par >> s) & 1u, abort_flag, P.status, ST_FULL, P.wait_limit);
                 full_par ^= 1u << s;
                 PROF_ADD(3);
                 tc_fence_after();
@@ -360,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
           }
           if (!any)                                           // a one-chunk layer: the idle issuer still sees the layer's phases complete
-            for (int kb = 0; kb < nkb; kb++) wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY);
+            for (int kb = 0; kb < nkb; kb++) wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY, P.wait_limit);
         }
     }
   } else {
@@ -453,7 +458,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
             for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
             PROF_ADD(11);
-            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL, P.wait_limit);
             PROF_ADD(10);
             tc_fence_after();
             uint32_t a[32];
@@ -540,8 +545,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             mbar_arrive(bar_a_ready + 8 * kb2);
           };
           PROF_ADD(11);
-          if (0 < wall) { wait_bar(bar_a_dead + 0, lph, abort_flag, P.status, ST_A_DEAD); tc_fence_after(); move_block(std::integral_constant<int, 0>{}); }
-          if (1 < wall) { wait_bar(bar_a_dead + 8, lph, abort_flag, P.status, ST_A_DEAD); tc_fence_after(); move_block(std::integral_constant<int, 1>{}); }
+          if (0 < wall) { wait_bar(bar_a_dead + 0, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit); tc_fence_after(); move_block(std::integral_constant<int, 0>{}); }
+          if (1 < wall) { wait_bar(bar_a_dead + 8, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit); tc_fence_after(); move_block(std::integral_constant<int, 1>{}); }
           {
             uint32_t pk[16];
             chunk_epilogue(lastc, pk);                        // waits for the layer's last accumulator: every MMA has retired
@@ -587,7 +592,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           }
           for (int c = 0; c < nchunks; c++) {
             if (c == nchunks - 1 && do_pre) {
-              wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD);
+              wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit);
               tc_fence_after();
 #pragma unroll 1
               for (int g = 0; g < 4; g++) {
@@ -610,7 +615,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
             for (int j = 0; j < 8; j++) bq[j] = __ldg(reinterpret_cast<const float4*>(L.bias + n0) + j);
             PROF_ADD(13);
-            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL);
+            wait_bar(bar_acc_full + 8 * b, aph, abort_flag, P.status, ST_ACC_FULL, P.wait_limit);
             PROF_ADD(14);
             tc_fence_after();
             uint32_t a[32];
@@ -750,6 +755,8 @@ float e4m3_round(float v) {
 
 }  // namespace
 
+TcTestKnobs g_tc_test = {0u, 0};
+
 struct TcModel {
   int nlayers = 0, n_in = 0, n_out = 0;
   std::vector<void*> w;            // bf16 [N][K] padded
@@ -879,6 +886,8 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
     P.cout[i] = StrideClass{L.cout[i][0], L.cout[i][1], L.cout[i][2]};
   }
   P.store_by_slot = L.store_by_slot;
+  P.wait_limit = g_tc_test.wait_limit ? g_tc_test.wait_limit : kWaitLimit;
+  P.test_skip_stage = g_tc_test.skip_stage;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(nrows);

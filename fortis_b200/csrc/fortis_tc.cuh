@@ -37,8 +37,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // bounded wait: returns false (and raises the abort flag, records `code`) when the limit is reached
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t i = 0; i < kWaitLimit; i++) {
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; i++) {
     if (*abort_flag) return false;
     if (mbar_try_wait(bar, parity)) return true;
   }
@@ -46,9 +46,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
   atomicCAS(status, 0, code);
   return false;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          uint32_t limit = kWaitLimit) {
   if (mbar_try_wait(bar, parity)) return true;          // the common case costs one instruction
-  return mbar_wait_slow(bar, parity, abort_flag, status, code);
+  return mbar_wait_slow(bar, parity, abort_flag, status, code, limit);
 }
 
 // The same wait without a function call, for kernels whose warpgroups run with different register budgets (setmaxnreg):

@@ -89,9 +89,6 @@ def boundary(NI, NK, NO, in_elt="f64", out_elt="f64", pre=None, post=None):
 # -----------------------------------------------------------------------------------------------------------------
 # random descriptor sets (differential testing: every case is valid by construction, sizes stay small)
 # -----------------------------------------------------------------------------------------------------------------
-_UNARY = ("sqrtf", "expf", "tanhf")
-
-
 def _random_expr(rng, scalars, depth=0):
     """A fully parenthesised C expression over tv, declared scalars and literals, safe for any finite tv in
     (-4, 4): divisions have denominators bounded away from zero, sqrt sees a non-negative operand."""
@@ -121,8 +118,9 @@ def _random_expr(rng, scalars, depth=0):
 
 
 def random_case(rng, max_arrays=4, max_slots=24, max_out=6):
-    """A random gather / scatter / loop / kdist set plus array shapes.  Returns (G, S, Lp, K, nargs) where nargs is
-    the number of enclosing-loop integer arguments the non-distributed form takes (0 or 1)."""
+    """A random gather / scatter / loop / kdist set plus array shapes.  Returns (G, S, Lp, K, nargs, planes): nargs is the
+    number of enclosing-loop integer arguments the non-distributed form takes (0 or 1), planes the extent of the plane
+    dimension those arguments index."""
     two_d = rng.random() < 0.7
     ni = int(rng.integers(3, 40))
     nj = int(rng.integers(2, 12)) if two_d else 1
@@ -171,4 +169,4 @@ def random_case(rng, max_arrays=4, max_slots=24, max_out=6):
     nk = planes if kdist else 1
     Lp = _loop(ni * nj * nk, halo + 1, ni, (halo + 1, halo + nj) if two_d else None, n, nout)
     K = {"ok": True, "loop": {"lo": 1, "hi": planes}, "nk": planes} if kdist else None
-    return G, S, Lp, K, (1 if (has_v and not kdist) else 0)
+    return G, S, Lp, K, (1 if (has_v and not kdist) else 0), planes

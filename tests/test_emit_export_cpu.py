@@ -106,10 +106,10 @@ def test_random_descriptor_cases_are_valid_for_planner_and_oracle():
     lib = fortis_b200.load()
     rng = np.random.default_rng(2024)
     for case in range(40):
-        G, S, Lp, K, nargs = D.random_case(rng)
+        G, S, Lp, K, nargs, planes = D.random_case(rng)
         P = fo.loop_params(Lp, K)
         arrays = [np.asfortranarray(rng.uniform(-2, 2, size=a["shape"]).astype(fo._NP[a["elt"]])) for a in G["arrays"]]
-        args = (int(rng.integers(1, G["arrays"][0]["shape"][-1] + 1)),) if nargs else ()
+        args = (int(rng.integers(1, planes + 1)),) if nargs else ()
         X = fo.gather(G, Lp, K, arrays, args=args)
         assert X.shape == (P["count"] * P["nk"], G["n"]) and np.isfinite(X).all(), case
         geom = (ctypes.c_longlong * 8)()

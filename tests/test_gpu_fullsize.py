@@ -200,3 +200,31 @@ def test_conv_config_full_size_bf16_adds_nothing_to_bf16_arithmetic(host):
 def test_conv_config_full_size_bf16_bar(host):
     e, _ = conv_bf16_full(host)
     assert e <= HALF_TOL
+
+
+@pytest.mark.parametrize("precision", ["bf16", "fp32"])
+def test_column_config_full_size_host_arrays_chunked_staging(host, precision, monkeypatch):
+    """The same step with HOST arrays: column chunks go up, compute and come back on three streams.  The result must be
+    bit-identical to the device-resident step (the chunks are whole tiles of the same kernels), call after call, and
+    identical to the serial staging path."""
+    wl = W.column(49152)
+    want = column_step(host, wl, precision)              # device-resident
+    outs = [np.full_like(a, np.nan) for a in wl["sout"]]
+    for _ in range(2):                                   # the second call is ordered behind the first one's copies
+        host.step(wl["gin"], outs)
+        host.sync()
+        for a, b in zip(outs, want):
+            assert a.tobytes(order="F") == b.tobytes(order="F")
+        for a in outs:
+            a.fill(np.nan)
+    host.step_checksum()
+    host.step(wl["gin"], outs)
+    cs = host.step_checksum()
+    total = float(sum(a.astype(np.float64).sum() for a in outs))
+    assert abs(cs - total) <= 1e-9 * float(sum(np.abs(a).astype(np.float64).sum() for a in outs))
+    monkeypatch.setenv("FORTIS_NO_OVERLAP", "1")         # the serial path: whole arrays up, step, whole arrays back
+    outs2 = [np.full_like(a, np.nan) for a in wl["sout"]]
+    host.step(wl["gin"], outs2)
+    host.sync()
+    for a, b in zip(outs2, want):
+        assert a.tobytes(order="F") == b.tobytes(order="F")
