@@ -335,6 +335,45 @@ class Bench:
             total = float(t.item())
         return total, ms
 
+    def link_floor(self, nin, nout, chunks=6, reps=5):
+        """What the host link itself allows for one step's traffic, measured with plain pinned-memory copies and no
+        kernel: the upload alone, the download alone, and both as a pipeline of `chunks` pieces in which piece c's
+        download runs beside piece c+1's upload.  The end-to-end step cannot be faster than the pipelined figure."""
+        torch = self.torch
+        hin, hout = torch.empty(nin, dtype=torch.uint8).pin_memory(), torch.empty(nout, dtype=torch.uint8).pin_memory()
+        din, dout = torch.empty(nin, dtype=torch.uint8, device="cuda"), torch.empty(nout, dtype=torch.uint8, device="cuda")
+        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+        def pipe(up, down, n):
+            cur = torch.cuda.current_stream()
+            s1.wait_stream(cur)
+            s2.wait_stream(cur)
+            ci, co = nin // n, nout // n
+            for c in range(n):
+                if up:
+                    with torch.cuda.stream(s1):
+                        din[c * ci:(c + 1) * ci].copy_(hin[c * ci:(c + 1) * ci], non_blocking=True)
+                s2.wait_stream(s1)
+                if down:
+                    with torch.cuda.stream(s2):
+                        hout[c * co:(c + 1) * co].copy_(dout[c * co:(c + 1) * co], non_blocking=True)
+            cur.wait_stream(s1)
+            cur.wait_stream(s2)
+
+        def ms(fn):
+            fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps
+
+        up, down, both = ms(lambda: pipe(True, False, 1)), ms(lambda: pipe(False, True, 1)), ms(lambda: pipe(True, True, chunks))
+        return {"h2d_ms": up, "h2d_gbs": nin / up / 1e6, "d2h_ms": down, "d2h_gbs": nout / down / 1e6, "pipelined_ms": both, "chunks": chunks}
+
     def gather_floats(self, v):
         """Every rank's value of `v` (list of floats) on every rank."""
         if self.dist is None:
@@ -487,6 +526,9 @@ class Bench:
             e_total, _ = self.timed(e_fn, e_steps, 3, device_only=False)
             e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
                    "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
+            e2e["ms_per_step"] = e_total / e_steps
+            e2e["link"] = self.link_floor(e2e["h2d_bytes_per_step"], e2e["d2h_bytes_per_step"])
+            e2e["frac_of_link"] = e2e["link"]["pipelined_ms"] / e2e["ms_per_step"]
         cs_global = cs_local
         if self.dist is not None:
             t = torch.tensor([cs_local], dtype=torch.float64, device="cuda")

@@ -155,6 +155,8 @@ struct Session {
   int gather_args[8] = {};
   const void *reg_in = nullptr, *reg_out = nullptr;
   bool nopin = false;
+  int host_access = 0;                        // host arrays of a step: 0 staged by copies, 1 outputs written by the kernels
+                                              // into the mapped host pages, 2 inputs read from them as well
 
   double *d_partials = nullptr, *d_sum = nullptr;
   unsigned int* d_done = nullptr;             // CTA completion counter of the in-kernel checksum fold
@@ -174,6 +176,10 @@ Session& S() {
     g_S = new Session();
     // option environment variables apply however the descriptors and the model arrive
     if (std::getenv("FORTIS_GRAPH")) g_S->graph = true;                              // driver/fortis_shim.py:84
+    if (const char* m = std::getenv("FORTIS_HOST_ACCESS")) {
+      const std::string v(m);
+      g_S->host_access = v == "mapped" ? 2 : v == "mapped_out" ? 1 : 0;
+    }
   }
   return *g_S;
 }
@@ -442,6 +448,12 @@ void pin_policy(PlanDev& P, int ai, const void* H, size_t bytes) {
 
 size_t elt_size(int elt) { return elt ? 8 : 4; }
 
+// does this plan's side of a step address pinned host arrays in place (option host_access)?
+bool maps_host(const PlanDev& P) {
+  const int m = S().host_access;
+  return m == 2 || (m == 1 && P.h.is_scatter);
+}
+
 long long plane_off_args(const ArrayInfo& a, const int* args, int nargs) {
   long long off = 0;
   for (auto& t : a.vterms) {
@@ -468,13 +480,20 @@ void bind_arrays(PlanDev& P, void* const* ptrs, const int* args, int nargs, bool
     P.on_dev[ai] = is_device_ptr(H);
     if (P.on_dev[ai]) { T->base[ai] = H + first * es; continue; }
     const long long need = planes ? a.plane * s.loop.nk : a.plane;
+    pin_policy(P, (int)ai, H, (size_t)a.total * es);
+    if (maps_host(P) && P.reg[ai] == H) {
+      // The kernels address the pinned host pages themselves: loads and stores cross the bus inside the launch, no
+      // staging copy on either side.
+      void* dp = nullptr;
+      if (cudaHostGetDevicePointer(&dp, H, 0) == cudaSuccess && dp) { P.on_dev[ai] = true; T->base[ai] = (char*)dp + first * es; continue; }
+      cudaGetLastError();
+    }
     if (P.stage_elems[ai] < need) {
       pool_free(P.stage[ai]);
       P.stage[ai] = pool_alloc(need * (long long)es);
       if (!P.stage[ai]) throw std::runtime_error("out of device memory staging array " + a.name);
       P.stage_elems[ai] = need;
     }
-    pin_policy(P, (int)ai, H, (size_t)a.total * es);
     const bool written = P.h.is_scatter && ai < P.h.written.size() && P.h.written[ai];
     if (a.used && (!written) && upload_readonly)
       cuda_ok(cudaMemcpyAsync(P.stage[ai], H + first * es, (size_t)need * es, cudaMemcpyHostToDevice, st), "H2D of a host array");
@@ -953,7 +972,7 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
     const ArrayInfo& a = s.G.h.arrays[ai];
     if (!a.used) continue;
     if (!column_array(a)) return false;
-    if (!is_device_ptr(gptrs[ai])) any_host = true;
+    if (!is_device_ptr(gptrs[ai]) && !maps_host(s.G)) any_host = true;
   }
   for (auto& x : s.G.h.slots) if (x.si != 1) return false;
   for (auto& x : s.G.h.scalars) if (x.si != 1) return false;
@@ -961,7 +980,7 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
     const ArrayInfo& a = s.S.h.arrays[ai];
     if (!a.used) continue;
     if (!column_array(a) || !s.S.h.written[ai]) return false;       // arrays a scatter only reads would need a whole upload
-    if (!is_device_ptr(sptrs[ai])) any_host = true;
+    if (!is_device_ptr(sptrs[ai]) && !maps_host(s.S)) any_host = true;
   }
   for (auto& t : s.S.h.stores) if (t.a.si != 1) return false;
   if (!any_host || !ensure_copy_streams()) return false;
@@ -988,10 +1007,52 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
   // pins the arrays, sizes the staging buffers; the copies themselves are issued per chunk below
   bind_arrays(s.G, gptrs, args, 0, false, false, &A.TG);
   bind_arrays(s.S, sptrs, args, 0, false, false, &A.TS);
+  // Per-column vectors (one element per column) are not staged at all: a copy of a few hundred KB costs a copy's
+  // latency (7-10 us each, and copies of one direction run one after another whatever their stream), which for a dozen
+  // vectors is a tenth of the step.  The kernels load and store them through the pinned host pages instead; their
+  // bytes cross the bus inside the launches, beside the chunk copies.
+  auto map_vectors = [&](PlanDev& P, void* const* ptrs, ArrayTable& T) {
+    for (size_t ai = 0; ai < P.h.arrays.size(); ai++) {
+      const ArrayInfo& a = P.h.arrays[ai];
+      if (!a.used || P.on_dev[ai] || a.total != ncol || P.reg[ai] != ptrs[ai]) continue;
+      void* dp = nullptr;
+      if (cudaHostGetDevicePointer(&dp, ptrs[ai], 0) == cudaSuccess && dp) { P.on_dev[ai] = true; T.base[ai] = dp; }
+      else cudaGetLastError();
+    }
+  };
+  if (!std::getenv("FORTIS_STAGE_VECTORS")) { map_vectors(s.G, gptrs, A.TG); map_vectors(s.S, sptrs, A.TS); }
   const ArrayTable TG0 = A.TG, TS0 = A.TS;
-  int nchunks = (int)(ncol / 4096 < 8 ? ncol / 4096 : 8);
-  if (nchunks < 1) nchunks = 1;
-  const long long per = ((ncol + nchunks - 1) / nchunks + 127) / 128 * 128;     // whole 128-row tiles
+  // Chunk schedule: large chunks first, small ones last, so that what is left after the last upload (one forward
+  // and one download) is short.  FORTIS_STAGING_CHUNKS overrides it with a list of relative weights ("2,2,2,1,1").
+  std::vector<long long> weights;
+  if (const char* e = std::getenv("FORTIS_STAGING_CHUNKS")) {
+    for (const char* q = e; *q;) {
+      char* end = nullptr;
+      const long long w = std::strtoll(q, &end, 10);
+      if (end == q) break;
+      if (w > 0 && (int)weights.size() < kMaxChunks) weights.push_back(w);
+      q = *end == ',' ? end + 1 : end;
+    }
+  }
+  if (weights.empty()) {
+    // measured on a PCIe 5 x16 link: a few large chunks (a copy of under 1 MB pays mostly latency) and a short tail
+    if (ncol >= 40960) weights = {4, 4, 4, 2, 1, 1};
+    else if (ncol >= 16384) weights = {2, 2, 1, 1};
+    else weights = {1, 1};
+  }
+  long long wsum = 0;
+  for (long long w : weights) wsum += w;
+  std::vector<long long> cuts;                 // first column of every chunk, whole 128-row tiles
+  {
+    long long acc = 0;
+    for (long long w : weights) {
+      const long long c0 = (ncol * acc / wsum) / 128 * 128;
+      if (cuts.empty() || c0 > cuts.back()) cuts.push_back(c0);
+      acc += w;
+    }
+  }
+  const int nchunks = (int)cuts.size();
+  cuts.push_back(ncol);
 
   bool capturing = (++s.ov_calls == 2) && !std::getenv("FORTIS_NO_STAGING_GRAPH");
   if (capturing && cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); capturing = false; }
@@ -1002,14 +1063,19 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
     cudaEventRecord(g_ev_fork, st);
     cudaStreamWaitEvent(g_h2d, g_ev_fork, 0);
     cudaStreamWaitEvent(g_d2h, g_ev_fork, 0);
-    int c = 0;
-    for (long long c0 = 0; c0 < ncol; c0 += per, c++) {
-      const long long n = ncol - c0 < per ? ncol - c0 : per;
+    // per-column vectors that could not be mapped travel whole, ahead of the first chunk
+    for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+      const ArrayInfo& a = s.G.h.arrays[ai];
+      if (a.used && !s.G.on_dev[ai] && a.total == ncol)
+        cuda_ok(cudaMemcpyAsync(s.G.stage[ai], gptrs[ai], (size_t)ncol * elt_size(a.elt), cudaMemcpyHostToDevice, g_h2d), "H2D of a column vector");
+    }
+    for (int c = 0; c < nchunks; c++) {
+      const long long c0 = cuts[c], n = cuts[c + 1] - cuts[c];
       for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
         const ArrayInfo& a = s.G.h.arrays[ai];
         if (!a.used) continue;
         const size_t es = elt_size(a.elt);
-        if (!s.G.on_dev[ai])
+        if (!s.G.on_dev[ai] && a.total != ncol)
           cuda_ok(cudaMemcpy2DAsync((char*)s.G.stage[ai] + c0 * es, (size_t)ncol * es, (const char*)gptrs[ai] + c0 * es, (size_t)ncol * es,
                                     (size_t)n * es, (size_t)(a.total / ncol), cudaMemcpyHostToDevice, g_h2d), "H2D of a column chunk");
         A.TG.base[ai] = (char*)TG0.base[ai] + c0 * es;
@@ -1026,9 +1092,16 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
         const ArrayInfo& a = s.S.h.arrays[ai];
         if (!a.used || s.S.on_dev[ai]) continue;
         const size_t es = elt_size(a.elt);
-        cuda_ok(cudaMemcpy2DAsync((char*)sptrs[ai] + c0 * es, (size_t)ncol * es, (const char*)s.S.stage[ai] + c0 * es, (size_t)ncol * es,
-                                  (size_t)n * es, (size_t)(a.total / ncol), cudaMemcpyDeviceToHost, g_d2h), "D2H of a column chunk");
+        if (a.total != ncol)
+          cuda_ok(cudaMemcpy2DAsync((char*)sptrs[ai] + c0 * es, (size_t)ncol * es, (const char*)s.S.stage[ai] + c0 * es, (size_t)ncol * es,
+                                    (size_t)n * es, (size_t)(a.total / ncol), cudaMemcpyDeviceToHost, g_d2h), "D2H of a column chunk");
       }
+    }
+    // unmapped vectors come back whole behind the last chunk
+    for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++) {
+      const ArrayInfo& a = s.S.h.arrays[ai];
+      if (a.used && !s.S.on_dev[ai] && a.total == ncol)
+        cuda_ok(cudaMemcpyAsync(sptrs[ai], s.S.stage[ai], (size_t)ncol * elt_size(a.elt), cudaMemcpyDeviceToHost, g_d2h), "D2H of a column vector");
     }
     // join: the persistent stream continues behind the last upload and the last download
     cudaEventRecord(g_ev_join_in, g_h2d);
@@ -1199,6 +1272,13 @@ int fortis_set_option(const char* key, const char* value) {
   } else if (k == "fuse") { s.fuse = v != "0"; drop_graph(); }
   else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
   else if (k == "async") { s.async = v != "0"; }
+  else if (k == "host_access") {
+    if (v == "copy") s.host_access = 0;
+    else if (v == "mapped_out") s.host_access = 1;
+    else if (v == "mapped") s.host_access = 2;
+    else throw std::runtime_error("host_access must be copy, mapped_out or mapped");
+    drop_graph();
+  }
   else if (k == "checksum") { s.want_checksum = v != "0"; drop_graph(); }
   else if (k == "test_wait_limit") { g_tc_test.wait_limit = (unsigned int)std::strtoul(v.c_str(), nullptr, 10); drop_graph(); }
   else if (k == "test_skip_stage") { g_tc_test.skip_stage = v != "0"; drop_graph(); }

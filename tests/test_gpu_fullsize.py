@@ -210,7 +210,7 @@ def test_column_config_full_size_host_arrays_chunked_staging(host, precision, mo
     wl = W.column(49152)
     want = column_step(host, wl, precision)              # device-resident
     outs = [np.full_like(a, np.nan) for a in wl["sout"]]
-    for _ in range(2):                                   # the second call is ordered behind the first one's copies
+    for _ in range(4):                                   # call 1 eager, call 2 captured, calls 3 and 4 replay the graph
         host.step(wl["gin"], outs)
         host.sync()
         for a, b in zip(outs, want):
@@ -228,3 +228,26 @@ def test_column_config_full_size_host_arrays_chunked_staging(host, precision, mo
     host.sync()
     for a, b in zip(outs2, want):
         assert a.tobytes(order="F") == b.tobytes(order="F")
+
+
+@pytest.mark.parametrize("mode", ["mapped_out", "mapped"])
+def test_column_config_full_size_mapped_host_arrays(host, mode):
+    """host_access = mapped_out / mapped: the kernels store into (and load from) the pinned host pages themselves
+    instead of staging copies.  Same kernels, same tiles: bit-identical to the device-resident step."""
+    wl = W.column(49152)
+    want = column_step(host, wl, "bf16")
+    host.reset()
+    host.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"])
+    host.load_model(fortis_b200.write_blob(wl["layers"]))
+    host.option("precision", "bf16")
+    host.option("host_access", mode)
+    outs = [np.full_like(a, np.nan) for a in wl["sout"]]
+    for _ in range(3):
+        host.step(wl["gin"], outs)
+        host.sync()
+        for a, b in zip(outs, want):
+            assert a.tobytes(order="F") == b.tobytes(order="F")
+        for a in outs:
+            a.fill(np.nan)
+    with pytest.raises(fortis_b200.FortisError):
+        host.option("host_access", "peer")
