@@ -1551,43 +1551,80 @@ static bool dense5(const long* t, long n0, long n1, long n2, long n3, long n4) {
   return true;
 }
 
+// One convolution layer through the memref ABI.  `max_k` > 0 and `unit_stride` reproduce the refusals of the
+// reference entry being replaced (message on stderr, y untouched).
 static void conv3d_entry(const char* who, float* x, long xo, float* w, long wo, float* y, long yo, long N, long C, long Din, long Hin,
                          long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout, long sd, long sh, long sw,
-                         long pd, long ph, long pw, const long* xt, const long* wt, const long* yt) {
+                         long pd, long ph, long pw, const long* xt, const long* wt, const long* yt, bool unit_stride, long max_k,
+                         bool no_pad) {
   if (!dense5(xt, N, C, Din, Hin, Win) || !dense5(wt, F, C, KD, KH, KW) || !dense5(yt, N, F, Dout, Hout, Wout)) {
     std::fprintf(stderr, "%s: operands must be dense NCDHW / FCKKK memrefs\n", who);
     return;
   }
-  if (sd != 1 || sh != 1 || sw != 1 || KD != KH || KD != KW || pd != ph || pd != pw || Dout != Din + 2 * pd - KD + 1 ||
-      Hout != Hin + 2 * ph - KH + 1 || Wout != Win + 2 * pw - KW + 1) {
+  const bool sane = N > 0 && C > 0 && F > 0 && KD > 0 && KH > 0 && KW > 0 && sd > 0 && sh > 0 && sw > 0 && pd >= 0 && ph >= 0 && pw >= 0 &&
+                    Din + 2 * pd >= KD && Hin + 2 * ph >= KH && Win + 2 * pw >= KW &&
+                    Dout == (Din + 2 * pd - KD) / sd + 1 && Hout == (Hin + 2 * ph - KH) / sh + 1 && Wout == (Win + 2 * pw - KW) / sw + 1;
+  if (!sane || (unit_stride && (sd != 1 || sh != 1 || sw != 1)) || (max_k > 0 && (KD > max_k || KH > max_k || KW > max_k)) ||
+      (no_pad && (pd || ph || pw))) {
     std::fprintf(stderr, "%s: unsupported shape\n", who);
     return;
   }
+  const int K[3] = {(int)KD, (int)KH, (int)KW}, st[3] = {(int)sd, (int)sh, (int)sw}, pad[3] = {(int)pd, (int)ph, (int)pw};
   std::string err;
-  if (!conv3d_ncdhw(x + xo, w + wo, y + yo, (int)N, (int)C, (int)Din, (int)Hin, (int)Win, (int)F, (int)KD, (int)pd, stream(), &err))
+  if (!conv3d_ncdhw(x + xo, w + wo, y + yo, (int)N, (int)C, (int)Din, (int)Hin, (int)Win, (int)F, K, st, pad, stream(), &err))
     std::fprintf(stderr, "%s: %s\n", who, err.c_str());
 }
 
+#define FORTIS_MEMREF5_UNUSED \
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4; \
+  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4; \
+  const long xt[5] = {xt0, xt1, xt2, xt3, xt4}, wt[5] = {wt0, wt1, wt2, wt3, wt4}, yt[5] = {yt0, yt1, yt2, yt3, yt4}
+
+// any kernel extent, stride and padding (the reference hands these to cuDNN)
 void fortis_conv3d(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
                    float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
                    long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
                    long sd, long sh, long sw, long pd, long ph, long pw) {
-  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4;
-  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4;
-  const long xt[5] = {xt0, xt1, xt2, xt3, xt4}, wt[5] = {wt0, wt1, wt2, wt3, wt4}, yt[5] = {yt0, yt1, yt2, yt3, yt4};
-  conv3d_entry("fortis_conv3d", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt, yt);
+  FORTIS_MEMREF5_UNUSED;
+  conv3d_entry("fortis_conv3d", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt, yt,
+               false, 0, false);
 }
 
+// stride 1 and kernels up to 5 per axis only, as the reference's direct kernels (runtime/fortis_fft.cu:135); N > 1 is taken
 void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
                    float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
                    long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
                    long sd, long sh, long sw, long pd, long ph, long pw) {
-  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)x4; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)w4;
-  (void)ya; (void)y0; (void)y1; (void)y2; (void)y3; (void)y4;
-  const long xt[5] = {xt0, xt1, xt2, xt3, xt4}, wt[5] = {wt0, wt1, wt2, wt3, wt4}, yt[5] = {yt0, yt1, yt2, yt3, yt4};
-  conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt, yt);
+  FORTIS_MEMREF5_UNUSED;
+  conv3d_entry("fortis_conv3d_direct", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt,
+               wt, yt, true, 5, false);
+}
+
+// The entry the compiler picks for kernels of 5^3 taps and more (compiler/FortisFuse.cpp, runtime/fortis_fft.cu:66-79:
+// stride 1, no padding).  The result is the same convolution; here it is computed directly, in fp32, by the implicit
+// GEMM (no transform, no spectrum buffers, no round-off of a forward and an inverse FFT).
+void fortis_conv3d_fft(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
+                   long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
+                   long sd, long sh, long sw, long pd, long ph, long pw) {
+  FORTIS_MEMREF5_UNUSED;
+  conv3d_entry("fortis_conv3d_fft", x, xo, w, wo, y, yo, N, C, Din, Hin, Win, F, KD, KH, KW, Dout, Hout, Wout, sd, sh, sw, pd, ph, pw, xt, wt,
+               yt, true, 0, true);
+}
+
+// NCHW convolution (runtime/fortis_rt.c:108-127): the D = KD = 1 case of the same kernel
+void fortis_conv2d(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long xt0, long xt1, long xt2, long xt3,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long wt0, long wt1, long wt2, long wt3,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long yt0, long yt1, long yt2, long yt3,
+                   long N, long C, long Hin, long Win, long F, long KH, long KW, long Hout, long Wout, long sh, long sw, long ph, long pw) {
+  (void)xa; (void)x0; (void)x1; (void)x2; (void)x3; (void)wa; (void)w0; (void)w1; (void)w2; (void)w3; (void)ya; (void)y0; (void)y1; (void)y2; (void)y3;
+  // a dense 4-d memref is a dense 5-d one with a unit depth axis (its stride never multiplies anything but 0)
+  const long xt[5] = {xt0, xt1, Hin * Win, xt2, xt3}, wt[5] = {wt0, wt1, KH * KW, wt2, wt3}, yt[5] = {yt0, yt1, Hout * Wout, yt2, yt3};
+  conv3d_entry("fortis_conv2d", x, xo, w, wo, y, yo, N, C, 1, Hin, Win, F, 1, KH, KW, 1, Hout, Wout, 1, sh, sw, 0, ph, pw, xt, wt, yt, false, 0,
+               false);
 }
 
 int fortis_copy_to_host(void* dst, const void* dev, long nbytes) {

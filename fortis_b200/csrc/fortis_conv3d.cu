@@ -1,9 +1,11 @@
-// conv3d (cross-correlation, stride 1, zero padding) as an implicit GEMM on the CUDA cores, fp32, with bias,
-// residual add and activation fused into the epilogue; plus the network driver for stacks of such layers.
+// conv3d / conv2d (cross-correlation, zero padding, any kernel extent, stride and padding per axis) as an implicit GEMM
+// on the CUDA cores, fp32, with bias, residual add and activation fused into the epilogue; plus the network driver for
+// stacks of such layers.
 //
-// Replaces the reference's cuDNN lowering fortis_conv3d (runtime/fortis_rt.c:128-156: descriptors rebuilt every
-// call, heuristic algorithm, workspace from the pool, bias / activation / residual as further kernels:
-// compiler/FortisFuse.cpp:626-655, 687-760) and its library-free direct kernels (runtime/fortis_fft.cu:91-201).
+// Replaces the reference's cuDNN lowerings fortis_conv2d / fortis_conv3d (runtime/fortis_rt.c:108-156: descriptors
+// rebuilt every call, heuristic algorithm, workspace from the pool, bias / activation / residual as further kernels:
+// compiler/FortisFuse.cpp:626-655, 687-760), its library-free direct kernels (runtime/fortis_fft.cu:91-201) and its
+// cuFFT convolution for large kernels (runtime/fortis_fft.cu:15-79); a 2-D convolution is the D = KD = 1 case.
 //
 // GEMM view: rows = output voxels (n, d, h, w), columns = output channels, reduction = taps x input channels.
 // A block owns 64 voxels x 64 channels; per (tap, 16 input channels) slice the activations (gathered with the
@@ -24,7 +26,8 @@ namespace fortis {
 namespace {
 
 struct ConvGeom {
-  int N, D, H, W, C, F, K, pad;
+  int N, D, H, W, C, F;
+  int KD, KH, KW, pd, ph, pw, sd, sh, sw;
   int Do, Ho, Wo;
   long long xs_n, xs_d, xs_h, xs_w, xs_c;     // element strides of x
   long long ys_n, ys_d, ys_h, ys_w, ys_c;     // element strides of y (and of the residual)
@@ -57,10 +60,10 @@ __global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict
   for (int i = 0; i < 4; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-  const int ntaps = g.K * g.K * g.K;
+  const int ntaps = g.KD * g.KH * g.KW;
   for (int tap = 0; tap < ntaps; tap++) {
-    const int kd = tap / (g.K * g.K), kh = (tap / g.K) % g.K, kw = tap % g.K;
-    const int id = od + kd - g.pad, ih = oh + kh - g.pad, iw = ow + kw - g.pad;
+    const int kd = tap / (g.KH * g.KW), kh = (tap / g.KW) % g.KH, kw = tap % g.KW;
+    const int id = od * g.sd + kd - g.pd, ih = oh * g.sh + kh - g.ph, iw = ow * g.sw + kw - g.pw;
     const bool inb = vlive && id >= 0 && id < g.D && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
     const float* xp = x + (long long)on * g.xs_n + (long long)id * g.xs_d + (long long)ih * g.xs_h + (long long)iw * g.xs_w;
     for (int c0 = 0; c0 < g.C; c0 += CBK) {
@@ -222,7 +225,8 @@ bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, i
         if (m->buf[b] != src && b != skip_buf) { dst = m->buf[b]; dst_buf = b; break; }
     }
     ConvGeom g;
-    g.N = N; g.D = D; g.H = H; g.W = W; g.C = L.cin; g.F = L.cout; g.K = L.ksize; g.pad = L.pad;
+    g.N = N; g.D = D; g.H = H; g.W = W; g.C = L.cin; g.F = L.cout;
+    g.KD = g.KH = g.KW = L.ksize; g.pd = g.ph = g.pw = L.pad; g.sd = g.sh = g.sw = 1;
     g.Do = D; g.Ho = H; g.Wo = W;
     g.xs_c = 1; g.xs_w = L.cin; g.xs_h = (long long)W * L.cin; g.xs_d = (long long)H * W * L.cin; g.xs_n = (long long)D * H * W * L.cin;
     g.ys_c = 1; g.ys_w = L.cout; g.ys_h = (long long)W * L.cout; g.ys_d = (long long)H * W * L.cout; g.ys_n = (long long)D * H * W * L.cout;
@@ -238,21 +242,22 @@ bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, i
 }
 
 // single layer, NCDHW fp32, weights in the torch layout on the device (memref ABI of runtime/fortis_rt.c:128-131)
-bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, int K, int pad,
-                  cudaStream_t s, std::string* err) {
+bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, const int K[3],
+                  const int stride[3], const int pad[3], cudaStream_t s, std::string* err) {
   // weights are constants of the caller: repack each distinct (pointer, shape) once, as the reference caches its
   // transposed GEMM weights (runtime/fortis_rt.c:55-66)
   // The repack runs as a kernel on the caller's stream (no synchronisation, no host round trip).  The cache holds 64
   // entries; when it is full the oldest entry is replaced and its buffer reused or freed.  A weight seen for the
   // first time needs a buffer: that cannot happen while the stream is being captured into a graph, so such a call
   // is refused (the reference captures on the second call for the same reason: the first call allocates).
-  struct Cached { const float* w; int F, C, K; float* wt; size_t cap; };
+  struct Cached { const float* w; int F, C, taps; float* wt; size_t cap; };
   static std::vector<Cached> cache;
   static size_t victim = 0;
   float* wt = nullptr;
-  for (auto& c : cache) if (c.w == w && c.F == F && c.C == C && c.K == K) wt = c.wt;
+  const int taps = K[0] * K[1] * K[2];
+  for (auto& c : cache) if (c.w == w && c.F == F && c.C == C && c.taps == taps) wt = c.wt;
   if (!wt) {
-    const size_t n = (size_t)F * C * K * K * K;
+    const size_t n = (size_t)F * C * taps;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(s, &cs);
     if (cs != cudaStreamCaptureStatusNone) { if (err) *err = "conv weights seen for the first time during graph capture; run one eager call first"; return false; }
@@ -264,13 +269,14 @@ bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D,
       if (cudaMalloc(&slot->wt, n * 4) != cudaSuccess) { slot->w = nullptr; if (err) *err = "out of device memory for conv weights"; return false; }
       slot->cap = n;
     }
-    slot->w = w; slot->F = F; slot->C = C; slot->K = K;
+    slot->w = w; slot->F = F; slot->C = C; slot->taps = taps;
     wt = slot->wt;
-    repack_weights_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(w, wt, F, C, K * K * K);
+    repack_weights_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(w, wt, F, C, taps);
   }
   ConvGeom g;
-  g.N = N; g.D = D; g.H = H; g.W = W; g.C = C; g.F = F; g.K = K; g.pad = pad;
-  g.Do = D + 2 * pad - K + 1; g.Ho = H + 2 * pad - K + 1; g.Wo = W + 2 * pad - K + 1;
+  g.N = N; g.D = D; g.H = H; g.W = W; g.C = C; g.F = F;
+  g.KD = K[0]; g.KH = K[1]; g.KW = K[2]; g.sd = stride[0]; g.sh = stride[1]; g.sw = stride[2]; g.pd = pad[0]; g.ph = pad[1]; g.pw = pad[2];
+  g.Do = (D + 2 * pad[0] - K[0]) / stride[0] + 1; g.Ho = (H + 2 * pad[1] - K[1]) / stride[1] + 1; g.Wo = (W + 2 * pad[2] - K[2]) / stride[2] + 1;
   g.xs_w = 1; g.xs_h = W; g.xs_d = (long long)H * W; g.xs_c = (long long)D * H * W; g.xs_n = (long long)C * D * H * W;
   g.ys_w = 1; g.ys_h = g.Wo; g.ys_d = (long long)g.Ho * g.Wo; g.ys_c = (long long)g.Do * g.Ho * g.Wo; g.ys_n = (long long)F * g.Do * g.Ho * g.Wo;
   launch_conv(x, wt, nullptr, nullptr, y, g, ACT_NONE, 0.f, s);

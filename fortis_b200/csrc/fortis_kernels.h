@@ -130,8 +130,8 @@ void conv_model_clear_status(ConvModel* m);        // 0, or the code of a bounde
 // x (N,D,H,W,Cin) fp32 NDHWC on the device -> y (N,D,H,W,Cout)
 bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 // single layer, NCDHW fp32 (the memref ABI of runtime/fortis_rt.c:128-131)
-bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, int K, int pad,
-                  cudaStream_t s, std::string* err);
+bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, const int K[3],
+                  const int stride[3], const int pad[3], cudaStream_t s, std::string* err);
 
 // tensor-core conv network (fortis_conv3d_tc.cu): bf16 activations in a zero-padded channels-last volume
 struct ConvTcModel;

@@ -77,9 +77,14 @@ void fortis_gemm(float* Aa, float* A, long Ao, long As0, long As1, long At0, lon
                  float* Wa, float* W, long Wo, long Ws0, long Ws1, long Wt0, long Wt1,
                  float* Ca, float* C, long Co, long Cs0, long Cs1, long Ct0, long Ct1, long B, long N, long K);
 
-/* runtime/fortis_rt.c:128-131 and runtime/fortis_fft.cu:131-135: NCDHW fp32 cross-correlation, memref ABI
- * (allocated, aligned, offset, sizes[5], strides[5]) per operand then 18 longs.  Stride 1 only; other strides
- * print a message and leave y untouched, as the reference's direct kernel does (runtime/fortis_fft.cu:135). */
+/* runtime/fortis_rt.c:128-131, runtime/fortis_fft.cu:131-135 and runtime/fortis_fft.cu:66-70: NCDHW fp32
+ * cross-correlation with zero padding, memref ABI (allocated, aligned, offset, sizes[5], strides[5]) per operand, then
+ * 18 longs.  Operands must be dense; a shape an entry does not take prints "<entry>: unsupported shape" on stderr and
+ * leaves y untouched, as in the reference.
+ *   fortis_conv3d         any kernel extent, stride and padding per axis (the reference's cuDNN lowering)
+ *   fortis_conv3d_direct  stride 1, kernel extents up to 5 (the reference's direct kernels; here N > 1 is taken too)
+ *   fortis_conv3d_fft     stride 1, no padding (the entry the compiler picks for kernels of 5^3 taps and more; the
+ *                         result is computed directly in fp32, without a transform) */
 void fortis_conv3d(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
                    float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
@@ -90,6 +95,18 @@ void fortis_conv3d_direct(float* xa, float* x, long xo, long x0, long x1, long x
                    float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
                    long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
                    long sd, long sh, long sw, long pd, long ph, long pw);
+
+void fortis_conv3d_fft(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long x4, long xt0, long xt1, long xt2, long xt3, long xt4,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long w4, long wt0, long wt1, long wt2, long wt3, long wt4,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long y4, long yt0, long yt1, long yt2, long yt3, long yt4,
+                   long N, long C, long Din, long Hin, long Win, long F, long KD, long KH, long KW, long Dout, long Hout, long Wout,
+                   long sd, long sh, long sw, long pd, long ph, long pw);
+/* runtime/fortis_rt.c:108-111: NCHW fp32 cross-correlation, memref ABI (allocated, aligned, offset, sizes[4],
+ * strides[4]) per operand, then 13 longs; any kernel extent, stride and padding per axis. */
+void fortis_conv2d(float* xa, float* x, long xo, long x0, long x1, long x2, long x3, long xt0, long xt1, long xt2, long xt3,
+                   float* wa, float* w, long wo, long w0, long w1, long w2, long w3, long wt0, long wt1, long wt2, long wt3,
+                   float* ya, float* y, long yo, long y0, long y1, long y2, long y3, long yt0, long yt1, long yt2, long yt3,
+                   long N, long C, long Hin, long Win, long F, long KH, long KW, long Hout, long Wout, long sh, long sw, long ph, long pw);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * 2. Run-time configuration (what fortisc bakes in at build time)
@@ -107,9 +124,19 @@ int fortis_set_vector(const char* name, const void* host_data, long n, int elt);
 /* the model blob (layout in fortis_b200/csrc/fortis_model.h; written by fortis_b200.model.write_blob) */
 int fortis_load_model(const char* path);
 int fortis_load_model_mem(const void* blob, long nbytes);
-/* options: "precision" = "fp32" | "bf16" | "fp8w";  "fuse" = "0" | "1";  "graph" = "0" | "1" (FORTIS_GRAPH);
- * "checksum" = "0" | "1" (accumulate the fp64 sum of everything a fused step scatters);
- * "conv_shape" = "N,D,H,W" (input extent of a conv3d model) */
+/* options:
+ *   "precision"   "fp32" (default; large layers run as three TF32 tensor-core products per fp32 product with IEEE
+ *                 running sums, <= 1e-5) | "bf16" | "fp16" (16-bit operands, fp32 accumulation) | "fp8w" (FP8-E4M3
+ *                 weights with per-channel scales, bf16 activations; MLP models only)
+ *   "fuse"        "0" | "1"   one launch per step where the descriptors allow it (default 1)
+ *   "graph"       "0" | "1"   replay a step as a CUDA graph from its second call (FORTIS_GRAPH)
+ *   "async"       "0" | "1"   return from a step without waiting for the stream (fortis_sync() waits)
+ *   "checksum"    "0" | "1"   accumulate the fp64 sum of everything a fused step scatters
+ *   "host_access" "copy" (default: host arrays are staged by copies; column layouts in chunks, uploads, kernels and
+ *                 downloads overlapped) | "mapped_out" (kernels store into the pinned host pages) | "mapped" (they
+ *                 load from them as well); also FORTIS_HOST_ACCESS
+ *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model
+ * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits (fortis_b200_test.h). */
 int fortis_set_option(const char* key, const char* value);
 /* drop every descriptor, model, buffer registration and captured graph (device pool buffers stay pooled) */
 void fortis_reset(void);

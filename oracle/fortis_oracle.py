@@ -507,6 +507,26 @@ def conv3d_ndhwc(x: np.ndarray, W: np.ndarray, b: Optional[np.ndarray], pad: int
     return y
 
 
+def conv_ncdhw(x: np.ndarray, W: np.ndarray, stride=(1, 1, 1), pad=(0, 0, 0), dtype=np.float32):
+    """The single-layer library rules fortis_conv2d / fortis_conv3d / fortis_conv3d_fft (runtime/fortis_rt.c:108-156,
+    runtime/fortis_fft.cu:66-79): cross-correlation with zero padding, x (N,C,D,H,W), W (F,C,KD,KH,KW), any stride and
+    padding per axis; returns (N,F,D',H',W').  A 2-D convolution is D = KD = 1."""
+    x = np.asarray(x, dtype=dtype)
+    W = np.asarray(W, dtype=dtype)
+    N, C, D, H, Wd = x.shape
+    F, _, KD, KH, KW = W.shape
+    (sd, sh, sw), (pd, ph, pw) = stride, pad
+    xp = np.pad(x, ((0, 0), (0, 0), (pd, pd), (ph, ph), (pw, pw)))
+    Do, Ho, Wo = (D + 2 * pd - KD) // sd + 1, (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
+    y = np.zeros((N, F, Do, Ho, Wo), dtype=dtype)
+    for kd in range(KD):
+        for kh in range(KH):
+            for kw in range(KW):
+                win = xp[:, :, kd:kd + (Do - 1) * sd + 1:sd, kh:kh + (Ho - 1) * sh + 1:sh, kw:kw + (Wo - 1) * sw + 1:sw]
+                y += np.einsum("ncdhw,fc->nfdhw", win, W[:, :, kd, kh, kw])
+    return y
+
+
 def convnet_forward(layers: Sequence[Dict], x: np.ndarray, dtype=np.float32) -> np.ndarray:
     """Sequence of conv3d layers with fused activation and optional residual.  Each layer dict: W, b, act,
     slope, and `save` (remember this layer's output as the skip) / `add` (add the remembered skip after the conv,

@@ -172,3 +172,60 @@ def test_conv_bf16_layer_by_layer_at_tile_and_quadrant_boundaries(host):
     ye = y[0, dp[edge] - 1, hp[edge] - 1, wp[edge] - 1]
     we = want[0, dp[edge] - 1, hp[edge] - 1, wp[edge] - 1]
     assert fo.rel_l2(ye, we) < 1e-3
+
+
+def _memref(t):
+    """(allocated, aligned, offset, sizes..., strides...) of a dense torch tensor."""
+    return [t.data_ptr(), t.data_ptr(), 0] + list(t.shape) + list(t.stride())
+
+
+def _conv_entry(L, name, nd):
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    fn = getattr(L, name)
+    one = [vp, vp, cl] + [cl] * (2 * nd)
+    fn.argtypes = one * 3 + [cl] * (18 if nd == 5 else 13)
+    fn.restype = None
+    return fn
+
+
+def test_single_conv_layers_any_kernel_stride_padding(host, golden_dir):
+    """fortis_conv3d (any kernel extent / stride / padding), fortis_conv2d (the NCHW form) and fortis_conv3d_fft (the
+    entry the compiler picks for 5^3 taps and more: stride 1, no padding) against torch-made vectors and the oracle,
+    fp32 <= 1e-5."""
+    Z = np.load(os.path.join(golden_dir, "conv_general.npz"))
+    L = host.L
+    c3, c2, cf = _conv_entry(L, "fortis_conv3d", 5), _conv_entry(L, "fortis_conv2d", 4), _conv_entry(L, "fortis_conv3d_fft", 5)
+    for name in sorted(k[:-2] for k in Z.files if k.endswith("_y")):
+        x, w, want = Z[name + "_x"], Z[name + "_w"], Z[name + "_y"]
+        sd, sh, sw, pd, ph, pw = [int(v) for v in Z[name + "_sp"]]
+        N, C, D, H, W = x.shape
+        F, _, KD, KH, KW = w.shape
+        _, _, Do, Ho, Wo = want.shape
+        oracle = fo.conv_ncdhw(x, w, (sd, sh, sw), (pd, ph, pw))
+        dx, dw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+        entries = [("fortis_conv3d", c3)]
+        if name.startswith("c3d_valid"):
+            entries.append(("fortis_conv3d_fft", cf))
+        for label, fn in entries:
+            y = torch.full((N, F, Do, Ho, Wo), float("nan"), device="cuda")
+            fn(*_memref(dx), *_memref(dw), *_memref(y), N, C, D, H, W, F, KD, KH, KW, Do, Ho, Wo, sd, sh, sw, pd, ph, pw)
+            host.sync()
+            got = y.cpu().numpy()
+            assert fo.rel_l2(got, want) <= 1e-5, (label, name, fo.rel_l2(got, want))
+            assert fo.rel_l2(got, oracle) <= 1e-5, (label, name)
+        if D == 1 and KD == 1:
+            x4, w4 = dx.view(N, C, H, W), dw.view(F, C, KH, KW)
+            y4 = torch.full((N, F, Ho, Wo), float("nan"), device="cuda")
+            c2(*_memref(x4), *_memref(w4), *_memref(y4), N, C, H, W, F, KH, KW, Ho, Wo, sh, sw, ph, pw)
+            host.sync()
+            assert fo.rel_l2(y4.cpu().numpy().reshape(want.shape), want) <= 1e-5, ("fortis_conv2d", name)
+    # refusals leave y untouched: padding through the transform entry, a strided (non-dense) input view
+    x = torch.randn(1, 2, 8, 8, 8, device="cuda")
+    w = torch.randn(3, 2, 5, 5, 5, device="cuda")
+    y = torch.full((1, 3, 8, 8, 8), -7.0, device="cuda")
+    cf(*_memref(x), *_memref(w), *_memref(y), 1, 2, 8, 8, 8, 3, 5, 5, 5, 8, 8, 8, 1, 1, 1, 2, 2, 2)
+    xs = torch.randn(1, 2, 8, 8, 16, device="cuda")[..., ::2]
+    y2 = torch.full((1, 3, 4, 4, 4), -7.0, device="cuda")
+    c3(*_memref(xs), *_memref(w), *_memref(y2), 1, 2, 8, 8, 8, 3, 5, 5, 5, 4, 4, 4, 1, 1, 1, 0, 0, 0)
+    host.sync()
+    assert float(y.min()) == -7.0 == float(y.max()) and float(y2.min()) == -7.0 == float(y2.max())

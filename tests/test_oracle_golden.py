@@ -125,3 +125,16 @@ def test_c_port_matches_numpy_native(golden_dir):
     from oracle.cport import mlp_forward_c
     got = mlp_forward_c(lib, zb_layers(W), X, in_norms=W["in_norms"], out_norms=W["out_norms"], nthreads=2)
     assert got.tobytes() == ref.tobytes()
+
+
+def test_oracle_single_conv_layers_match_torch_vectors(golden_dir):
+    """conv_ncdhw (the oracle of fortis_conv2d / fortis_conv3d / fortis_conv3d_fft) against outputs torch's CPU
+    convolution wrote for 2-D, strided, non-cubic and 5^3 / 7^3 'valid' layers (tests/golden/make_conv_golden.py)."""
+    Z = np.load(os.path.join(golden_dir, "conv_general.npz"))
+    names = sorted(k[:-2] for k in Z.files if k.endswith("_y"))
+    assert len(names) == 7
+    for name in names:
+        sp = [int(v) for v in Z[name + "_sp"]]
+        y = fo.conv_ncdhw(Z[name + "_x"], Z[name + "_w"], stride=sp[:3], pad=sp[3:], dtype=np.float64)
+        assert y.shape == Z[name + "_y"].shape, name
+        assert fo.rel_l2(y, Z[name + "_y"]) < 2e-7, name
