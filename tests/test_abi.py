@@ -31,7 +31,7 @@ def test_header_lists_the_reference_surface():
     for ref in ("fortis_gather", "fortis_scatter", "mlp_forward", "mlp_forward_batched", "mlp_upload", "mlp_forward_dev",
                 "mlp_download", "fortis_pack", "fortis_unpack", "fortis_model_input", "fortis_model_output", "fortis_begin",
                 "mgpuStreamCreate", "mgpuStreamDestroy", "mgpuStreamSynchronize", "fortis_alloc", "fortis_free",
-                "fortis_gemm", "fortis_conv3d", "fortis_conv3d_direct", "fortis_capturing"):
+                "fortis_gemm", "fortis_conv2d", "fortis_conv3d", "fortis_conv3d_direct", "fortis_conv3d_fft", "fortis_step", "fortis_capturing"):
         assert ref in names
 
 
@@ -59,3 +59,17 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(fl, "HERE", str(tmp_path))
     with pytest.raises(fl.FortisError):
         fl.load()
+
+
+def test_fortran_interface_module_names_exported_entries():
+    """include/fortis_bindc.f90 binds by name: every name= in it must be declared in the C header and exported."""
+    text = open(os.path.join(ROOT, "include", "fortis_bindc.f90")).read()
+    names = re.findall(r"bind\(C,\s*name='(\w+)'\)", text)
+    assert len(names) >= 25 and len(set(names)) == len(names)
+    declared = set(declared_symbols())
+    L = ctypes.CDLL(fortis_b200.lib_path())
+    for n in names:
+        assert n in declared, "%s is not declared in include/fortis_b200.h" % n
+        assert hasattr(L, n), "libfortis_b200.so does not export %s" % n
+    # subroutine / function ... end pairs balance (no Fortran compiler in this image: a structural check only)
+    assert len(re.findall(r"^\s*(subroutine|function)\s", text, re.M)) == len(re.findall(r"^\s*end (subroutine|function)", text, re.M))

@@ -1,4 +1,4 @@
-"""conv3d path (BASELINE config 4's layer types) against the oracle, through the C ABI."""
+"""conv3d path (benchmark configuration 4's layer types) against the oracle, through the C ABI."""
 import ctypes
 import os
 
@@ -42,7 +42,7 @@ def test_superres_net_small(host, shape):
 @pytest.mark.parametrize("shape,blocks", [((2, 9, 7, 5), 2), ((1, 33, 33, 33), 1), ((2, 16, 12, 20), 6)])
 def test_superres_net_bf16_tensor_cores(host, shape, blocks):
     """The same network on the tcgen05 implicit-GEMM kernel (64 -> 64 layers) with bf16 activations.  Checked against
-    the oracle's model of that arithmetic (tight) and against the fp32 oracle (BASELINE's bf16 bar, 5e-3, or what
+    the oracle's model of that arithmetic (tight) and against the fp32 oracle (the stated bf16 bar, 5e-3, or what
     bf16 storage of 2 * blocks + 1 activations costs by itself if that is more)."""
     N, D, H, W = shape
     layers = fortis_b200.conv_layers(3, 64, 3, nblocks=blocks, seed=6)
@@ -62,7 +62,7 @@ def test_superres_net_bf16_tensor_cores(host, shape, blocks):
     e_model, e_exact, m_exact = fo.rel_l2(y, model), fo.rel_l2(y, exact), fo.rel_l2(model, exact)
     print("conv bf16 %s, %d blocks: vs bf16 model %.3e, vs fp32 %.3e (the model itself: %.3e)" % (shape, blocks, e_model, e_exact, m_exact))
     if blocks <= 2:
-        # shallow stacks: the north-star bf16 bar itself, and a tight check against the model of the arithmetic
+        # shallow stacks: the stated bf16 bar itself, and a tight check against the model of the arithmetic
         assert e_model < 2e-3 and e_exact < 5e-3
     else:
         # A deep residual stack amplifies rounding decorrelation (merely accumulating the MODEL in fp32 instead of

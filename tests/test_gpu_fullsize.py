@@ -3,7 +3,7 @@
 The oracle cannot run a whole configuration in seconds, but columns / gridpoints / batch entries are independent, so
 it is run on a fixed sample of them (spread over the first, middle and last tiles, so that every persistent CTA's
 second and third tile and the last, ragged tile are covered) and compared with the same elements of the GPU result.
-Bars are the north-star numbers themselves: fp32 <= 1e-5, 16-bit tensor-core variants <= 5e-3, FP8-E4M3 weights <= 2e-2
+Bars are the stated tolerances themselves: fp32 <= 1e-5, 16-bit tensor-core variants <= 5e-3, FP8-E4M3 weights <= 2e-2
 relative L2 against the fp32 oracle; the comparison with the oracle's model of the reduced-precision arithmetic is an
 additional, tight check that isolates indexing mistakes from rounding.  Where exact arithmetic in the named format
 cannot meet a bar the case is an expected failure with the measured value, never a widened bar.
@@ -113,9 +113,9 @@ def test_sharded_block_fp8_weights_full_size(host):
     assert e_exact <= 1.05 * model_vs_exact + 1e-4
 
 
-@pytest.mark.xfail(strict=True, reason="north-star bar unmet: exact E4M3 weights with per-output-channel absmax scales are "
+@pytest.mark.xfail(strict=True, reason="stated bar unmet: exact E4M3 weights with per-output-channel absmax scales are "
                                        "6e-2 from fp32 on this network (3 mantissa bits = 3.6 % RMS weight error), bar 2e-2")
-def test_fp8_weights_north_star_bar(host):
+def test_fp8_weights_stated_bar(host):
     wl = W.column(4096)
     got = column_step(host, wl, "fp8w")
     e_exact, _ = compare_columns(got, wl, np.arange(4096), "fp8w")
@@ -195,7 +195,7 @@ def test_conv_config_full_size_bf16_adds_nothing_to_bf16_arithmetic(host):
     assert e <= 1.15 * em
 
 
-@pytest.mark.xfail(strict=True, reason="north-star bar unmet in bf16: a 14-layer residual stack with bf16 operands is 8e-3 "
+@pytest.mark.xfail(strict=True, reason="stated bar unmet in bf16: a 14-layer residual stack with bf16 operands is 8e-3 "
                                        "from fp32 in exact arithmetic (the oracle's own bf16 model); precision=fp16 meets 5e-3")
 def test_conv_config_full_size_bf16_bar(host):
     e, _ = conv_bf16_full(host)

@@ -1,6 +1,6 @@
 """Parity of the CUDA path with the oracle, through the C ABI, on a B200.
 
-Bars: gather / scatter bit-exact; fp32 forward <= 1e-5 relative L2 (BASELINE north star).
+Bars: gather / scatter bit-exact; fp32 forward <= 1e-5 relative L2 (the tolerances the benchmark definition states).
 """
 import ctypes
 import json
@@ -171,7 +171,7 @@ def toy_config(ncol=4096):
 
 @pytest.mark.parametrize("resident", [False, True])
 def test_toy_mlp_config(host, resident):
-    """BASELINE config 1: (64,4096) Fortran array -> 64-256-256-64 ReLU MLP -> (64,4096) array + checksum."""
+    """benchmark configuration 1: (64,4096) Fortran array -> 64-256-256-64 ReLU MLP -> (64,4096) array + checksum."""
     G, S, Lp, K, A, layers = toy_config()
     B = np.zeros((64, 4096), np.float32, order="F")
     Bo = B.copy(order="F")
@@ -240,7 +240,7 @@ def test_packed_path_and_runtime_extent(host):
 
 
 def test_column_config_fp32_small(host):
-    """BASELINE config 2's layout at a reduced column count: four (ncol,60) fields + 4 vectors -> 244 features,
+    """benchmark configuration 2's layout at a reduced column count: four (ncol,60) fields + 4 vectors -> 244 features,
     244-768x4-128 LeakyReLU(0.15), outputs into two (ncol,60) arrays and eight vectors.  Ragged ncol."""
     ncol = 1000
     G, S, Lp, K = fo.column_descriptors(ncol, 60)
@@ -262,7 +262,7 @@ def test_column_config_fp32_small(host):
 
 @pytest.mark.parametrize("nx,ny,nz", [(64, 48, 2), (37, 5, 3)])
 def test_stencil_config_fused(host, nx, ny, nz):
-    """BASELINE config 3's layout at reduced extent: 3 fields with a 1-cell halo, 27 -> 20 -> 20 -> 3, in place."""
+    """benchmark configuration 3's layout at reduced extent: 3 fields with a 1-cell halo, 27 -> 20 -> 20 -> 3, in place."""
     G, S, Lp, K = fo.stencil_descriptors(nx, ny, nz)
     rng = np.random.default_rng(3)
     gin = [np.asfortranarray(rng.normal(size=(nx + 2, ny + 2, nz)).astype(np.float32)) for _ in range(3)]

@@ -1,6 +1,6 @@
 """Tensor-core (tcgen05) fused MLP path against the oracle, through the C ABI.
 
-Bars (BASELINE north star): bf16 <= 5e-3, FP8-E4M3 weights <= 2e-2 relative L2 against the fp32 oracle.  The
+Bars (the tolerances the benchmark definition states): bf16 <= 5e-3, FP8-E4M3 weights <= 2e-2 relative L2 against the fp32 oracle.  The
 tests additionally compare with the oracle's model of the reduced-precision arithmetic (bf16 activations, bf16 or
 E4M3 weights, wide accumulation), which isolates indexing / layout mistakes from rounding.
 """
@@ -17,7 +17,7 @@ BF16_TOL, FP8W_TOL, MODEL_TOL = 5e-3, 2e-2, 2e-3
 # These tests run the kernel on N(0,1) inputs and arbitrary layer shapes, where exact arithmetic on bf16 / E4M3
 # operands (the oracle's reduced-precision MODEL) is itself 2.3e-3 (bf16) / 2.6e-2 (E4M3) from fp32 per 244->768 layer
 # and 5.6e-3 / 6.3e-2 over a 5-layer net.  They therefore hold the kernel to the model (MODEL_TOL, tight) and to
-# "adds nothing on top": error vs fp32 <= SLACK x (model vs fp32).  The north-star bars themselves (5e-3 / 2e-2
+# "adds nothing on top": error vs fp32 <= SLACK x (model vs fp32).  The stated bars themselves (5e-3 / 2e-2
 # against fp32) are asserted without any slack on the benchmark configurations in test_gpu_fullsize.py and in
 # test_column_config_fused_step below.
 SLACK = 1.1
@@ -83,7 +83,7 @@ def column_case(ncol, seed=2):
 @pytest.mark.parametrize("precision,tol", [("bf16", BF16_TOL), ("fp16", BF16_TOL), ("fp8w", FP8W_TOL)])
 @pytest.mark.parametrize("resident", [True, False])
 def test_column_config_fused_step(host, precision, tol, resident):
-    """BASELINE config 2's layout (ragged column count): gather fused into layer 0, scatter into the last epilogue."""
+    """benchmark configuration 2's layout (ragged column count): gather fused into layer 0, scatter into the last epilogue."""
     ncol = 1000
     G, S, Lp, K, gin, sout, layers = column_case(ncol)
     ref = [a.copy(order="F") for a in sout]
@@ -104,7 +104,7 @@ def test_column_config_fused_step(host, precision, tol, resident):
         got = sout
     cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
     e_model, e_exact = fo.rel_l2(cat(got), cat(model)), fo.rel_l2(cat(got), cat(ref))
-    # bf16 / fp16: the north-star bar itself.  fp8w: E4M3's own distance from fp32 (the 2e-2 bar is an expected
+    # bf16 / fp16: the stated bar itself.  fp8w: E4M3's own distance from fp32 (the 2e-2 bar is an expected
     # failure of its own in test_gpu_fullsize.py)
     bar = tol if precision != "fp8w" else SLACK * fo.rel_l2(cat(model), cat(ref)) + 1e-4
     assert e_model < MODEL_TOL and e_exact < bar, "vs %s model %.3e, vs fp32 %.3e (bar %.3e)" % (precision, e_model, e_exact, bar)
