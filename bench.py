@@ -438,6 +438,7 @@ class Bench:
             flop = cols * wl0["flop_per_unit"]
             res[mode] = {"columns": cols, "columns_per_rank": SHARD_COLS * len(blocks), "value": cols * steps / (total * 1e-3),
                          "unit": "columns/s", "ms_per_step": total / steps, "tflops": flop * steps / (total * 1e-3) / 1e12,
+                         "value_at_median_step": cols / (max(s[1] for s in spread) * 1e-3),
                          "per_rank_step_ms_min_med_max": spread, "block_checksums": [c for rk in allcs for c in rk]}
         if status() != 0:
             raise SystemExit("device status %d in the sharded run" % status())
