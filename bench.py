@@ -217,8 +217,10 @@ def run_incumbent(args):
     ref = ctypes.CDLL(so, mode=ctypes.RTLD_LOCAL | os.RTLD_DEEPBIND)
     torch.cuda.set_device(0)
     wl = make_workload(args.workload, 0, args.ncol)
+    if wl["kind"] == "conv":
+        return run_incumbent_conv(args, ref, wl)
     if wl["kind"] not in ("column", "toy"):
-        print(json.dumps({"impl": "incumbent", "unavailable": "incumbent leg covers the column MLP workloads"}))
+        print(json.dumps({"impl": "incumbent", "unavailable": "incumbent leg covers the column MLP and conv workloads"}))
         return
     ncol = wl["units"]
     vp, cl = ctypes.c_void_p, ctypes.c_long
@@ -278,6 +280,63 @@ def run_incumbent(args):
                       "dtype": "f32", "checksum": cs, "config": {"workload": wl["label"]},
                       "what": "reference runtime compiled unchanged (fortis_gemm = cuBLAS SGEMM on pre-transposed weights) per layer + "
                               "separate bias/activation kernel; gather (cat) and scatter (copy) as torch kernels; comparison only"}))
+
+
+def run_incumbent_conv(args, ref, wl):
+    """The conv network through the reference runtime's cuDNN lowering: fortis_conv3d (runtime/fortis_rt.c:128-156:
+    NCDHW fp32, descriptors rebuilt and the algorithm chosen on every call, workspace from the pool) per layer, then
+    bias, activation and residual add as separate elementwise kernels (compiler/FortisFuse.cpp:626-655, 687-760), here
+    torch kernels.  The input is resident in NCDHW, as the reference's hosts hold it."""
+    import ctypes
+    import torch
+    vp, cl = ctypes.c_void_p, ctypes.c_long
+    ref.fortis_conv3d.argtypes = ([vp, vp, cl] + [cl] * 10) * 3 + [cl] * 18
+    ref.fortis_conv3d.restype = None
+    ref.mgpuStreamCreate.restype = vp
+    stream = torch.cuda.ExternalStream(ref.mgpuStreamCreate())
+    N, D, H, Wd = wl["shape"]
+    x0 = torch.from_numpy(wl["gin"][0]).cuda().permute(0, 4, 1, 2, 3).contiguous()          # NDHWC -> NCDHW, once
+    Ws = [torch.from_numpy(L["W"]).cuda().contiguous() for L in wl["layers"]]
+    Bs = [torch.from_numpy(L["b"]).cuda().view(1, -1, 1, 1, 1) for L in wl["layers"]]
+    bufs = [torch.empty(N, L["W"].shape[0], D, H, Wd, device="cuda") for L in wl["layers"]]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    mr = lambda t: [t.data_ptr(), t.data_ptr(), 0] + list(t.shape) + list(t.stride())
+
+    def step():
+        x, skip = x0, None
+        for l, L in enumerate(wl["layers"]):
+            F, C = L["W"].shape[:2]
+            y = bufs[l]
+            ref.fortis_conv3d(*mr(x), *mr(Ws[l]), *mr(y), N, C, D, H, Wd, F, 3, 3, 3, D, H, Wd, 1, 1, 1, 1, 1, 1)
+            y.add_(Bs[l])
+            if L.get("add"):
+                y.add_(skip)
+            if L["act"] == "leaky":
+                torch.nn.functional.leaky_relu(y, L["slope"], inplace=True)
+            if L.get("save"):
+                skip = y
+            x = y
+        return x
+
+    steps = max(3, min(args.steps, 10))
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            out = step()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(steps):
+            flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = step()
+            e.record()
+            torch.cuda.synchronize()
+            ms.append(s.elapsed_time(e))
+    med = float(np.median(ms))
+    print(json.dumps({"impl": "incumbent", "value": wl["units"] / (med * 1e-3), "unit": "columns/s", "ms_per_step": med, "steps": steps,
+                      "dtype": "f32", "checksum": float(out.double().sum().item()), "config": {"workload": wl["label"]},
+                      "what": "reference runtime compiled unchanged: fortis_conv3d (cuDNN, descriptors and algorithm search per call) per "
+                              "layer + separate bias / residual / activation kernels (torch); NCDHW input resident; comparison only"}))
 
 
 # -----------------------------------------------------------------------------------------------------------------
@@ -564,7 +623,7 @@ class Bench:
             roof["kernel_ms"] = kernel_ms
             cpu = None if (args.no_cpu or is_conv or world > 1) else time_cpu(wl)      # the CPU baseline is an N = 1 figure
             incumbent = None
-            if kind == "column" and world == 1 and not args.no_incumbent and wl["units"] <= 1 << 18:
+            if kind in ("column", "conv") and world == 1 and not args.no_incumbent and wl["units"] <= 1 << 19:
                 try:
                     out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "incumbent", "--workload", args.workload,
                                           "--steps", "10"] + (["--ncol", str(args.ncol)] if args.ncol else []),
@@ -573,7 +632,12 @@ class Bench:
                 except Exception as ex:
                     incumbent = {"unavailable": repr(ex)}
             tc = prec != "fp32"
-            launches_per_step = (len(wl["layers"]) + (1 if tc else 0)) if is_conv else 1 if tc else 2 if kind == "stencil" else (3 + len(wl["layers"]))
+            # kernels of the library per step: the 16-bit MLP step and the stencil step are one launch (checksum folded
+            # inside); fp32 MLPs of 512 rows and more run one tensor-core launch per layer (gather / scatter fused into
+            # the first / last); smaller ones gather + layers + scatter + fold; conv nets one launch per layer (+ the
+            # input pack on the 16-bit path)
+            launches_per_step = ((len(wl["layers"]) + (1 if tc else 0)) if is_conv else 1 if (tc or kind == "stencil")
+                                 else len(wl["layers"]) if wl["units"] >= 512 else (3 + len(wl["layers"])))
             line = {"metric": "fused-step columns/sec", "value": value, "unit": "columns/s", "n_gpus": world, "steps": args.steps,
                     "warmup": warm, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
                     "vs_baseline": None,

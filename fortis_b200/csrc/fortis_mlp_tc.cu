@@ -60,6 +60,11 @@ constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 
 // warpgroup of their own) and, because a function call stops the compiler from allocating per budget, the barrier waits
 // inlined.  Measured: the inlined waits cost 10 % by themselves (whatever the polling loop looks like), more than
 // the fourth stage returns, so the deep ring is not the default.
+// Weight stages as linear bulk copies of pre-tiled stage images (1, default) or as 3-D tensor copies of the row-major
+// weights (0).
+#ifndef FORTIS_TC_TILED_W
+#define FORTIS_TC_TILED_W 1
+#endif
 #ifndef FORTIS_TC_DEEP_RING
 #define FORTIS_TC_DEEP_RING 0
 #endif
@@ -98,6 +103,7 @@ struct TcLayer {
   float slope;             // branch-free activation: act(v) = max(v, v * slope); none -> 1, ReLU -> 0, LeakyReLU -> slope
   const float* bias;       // [N] padded with zeros
   const float* scale;      // [N] per-output-channel dequantisation scale (fp8 weights) or null
+  const uint8_t* wtiled;   // the weights as consecutive 32 KB stage images, [chunk of 64 features][256-wide K-block]
 };
 
 // Stride class of a fast gather / scatter: element offset of a row = ci*si + cj*sj + kk*sk
@@ -279,6 +285,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         for (int l = 0; l < P.nlayers && !stop; l++) {
           const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const CUtensorMap* map = &P.maps[l];
+          const uint8_t* wtiled = P.layer[l].wtiled;
+          (void)map; (void)wtiled;
           for (int c = 0; c < nchunks && !stop; c++, acc_it++) {
             const uint32_t full_c = bar_full + 8 * kStages * (acc_it & 1);      // the barriers of the issuer that owns this chunk
             for (int ks = 0; ks < nkb * kSubStages; ks++) {
@@ -288,7 +296,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               const bool skip = P.test_skip_stage && blockIdx.x == 0 && tile == 0 && l == 0 && c == 0 && ks == 0;   // test only
               if (!skip) {
                 mbar_expect_tx(full_c + 8 * s, kStageBytes);
+#if FORTIS_TC_TILED_W
+                bulk_load(ring + s * kStageBytes, wtiled + (size_t)(c * (nkb * kSubStages) + ks) * kStageBytes, kStageBytes, full_c + 8 * s);
+#else
                 tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), full_c + 8 * s);
+#endif
               }
               if (++s == kStages) { s = 0; ph ^= 1; }
             }
@@ -802,8 +814,10 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
   (void)s;
   std::string why;
   if (!tc_model_supported(M, &why)) { if (err) *err = why; return nullptr; }
+#if !FORTIS_TC_TILED_W
   EncodeTiledFn enc = encode_fn();
   if (!enc) { if (err) *err = "cuTensorMapEncodeTiled is not available from the driver"; return nullptr; }
+#endif
   TcModel* m = new TcModel();
   m->nlayers = (int)M.layers.size(); m->n_in = M.n_in(); m->n_out = M.n_out();
   auto fail = [&](const std::string& w) { if (err) *err = w; tc_model_destroy(m); return (TcModel*)nullptr; };
@@ -828,10 +842,32 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
         wb[(size_t)n * K + k] = precision == PREC_FP16 ? f32_to_f16(w) : f32_to_bf16(w);
       }
     }
-    void* dw = nullptr; float *db = nullptr, *ds = nullptr;
-    if (cudaMalloc(&dw, wb.size() * 2) != cudaSuccess || cudaMalloc(&db, N * 4) != cudaSuccess) return fail("out of device memory for packed weights");
-    m->w.push_back(dw); m->bias.push_back(db);
-    cudaMemcpy(dw, wb.data(), wb.size() * 2, cudaMemcpyHostToDevice);
+    // The same weights as the stage images the kernel streams: per chunk of 64 features and per 256-wide K-block one
+    // contiguous 32 KB block holding four 64 x 64 sub-tiles in the 128-byte-swizzled K-major layout the MMA descriptor
+    // expects (16-byte piece j of row r sits at piece j ^ (r & 7)), so that a stage is ONE linear bulk copy.
+    std::vector<uint16_t> wt((size_t)N * K, 0);
+    {
+      const int nks = K / kStageK;
+      for (int c = 0; c < N / kChunkN; c++)
+        for (int ks = 0; ks < nks; ks++) {
+          uint16_t* blk = wt.data() + ((size_t)c * nks + ks) * (kStageBytes / 2);
+          for (int t = 0; t < kStageK / 64; t++)
+            for (int r = 0; r < kChunkN; r++)
+              for (int j = 0; j < 8; j++) {
+                const uint16_t* src = wb.data() + (size_t)(c * kChunkN + r) * K + ks * kStageK + t * 64 + j * 8;
+                uint16_t* dst = blk + (size_t)t * (kChunkN * 64) + r * 64 + ((j ^ (r & 7)) * 8);
+                std::memcpy(dst, src, 16);
+              }
+        }
+    }
+    // only the form this build streams goes to the device
+    void *dw = nullptr, *dwt = nullptr; float *db = nullptr, *ds = nullptr;
+    const std::vector<uint16_t>& image = FORTIS_TC_TILED_W ? wt : wb;
+    void** slot = FORTIS_TC_TILED_W ? &dwt : &dw;
+    if (cudaMalloc(slot, image.size() * 2) != cudaSuccess || cudaMalloc(&db, N * 4) != cudaSuccess)
+      return fail("out of device memory for packed weights");
+    m->w.push_back(*slot); m->bias.push_back(db);
+    cudaMemcpy(*slot, image.data(), image.size() * 2, cudaMemcpyHostToDevice);
     cudaMemcpy(db, bias.data(), N * 4, cudaMemcpyHostToDevice);
     if (precision == PREC_FP8W) {
       if (cudaMalloc(&ds, N * 4) != cudaSuccess) return fail("out of device memory for weight scales");
@@ -839,8 +875,9 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     }
     m->scale.push_back(ds);
     TcLayer& T = m->layer[l];
-    T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds;
+    T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds; T.wtiled = (const uint8_t*)dwt;
     T.slope = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;      // act(v) = max(v, v * slope)
+#if !FORTIS_TC_TILED_W
     // W[N][K] viewed as [K/64][N][64]: one box of {64 k, 64 rows, 4 k-blocks} lands in shared memory as four
     // consecutive 64 x 64 sub-tiles, each in the 128-byte-swizzled K-major layout the MMA descriptor expects
     const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
@@ -850,6 +887,7 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     const CUresult r = enc(&m->maps[l], precision == PREC_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+#endif
   }
   auto up = [&](const std::vector<float>& v) -> float* {
     if (v.empty()) return nullptr;
