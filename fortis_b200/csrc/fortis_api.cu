@@ -1671,6 +1671,15 @@ int fortis_step_checksum(double* out) {
 
 // ---- host-only introspection (no CUDA call): lets the CPU test-suite check the descriptor planner and the
 // expression compiler against the oracle
+int fortis_debug_pack_layer(const float* W, const float* b, int cout, int cin, int last, int precision, unsigned short* image,
+                            float* bias, float* scale, int* K, int* N) {
+  FORTIS_TRY
+  if (!W || !b || cout <= 0 || cin <= 0 || cin > 768 || !K || !N) throw std::runtime_error("fortis_debug_pack_layer: bad arguments");
+  if (precision != PREC_BF16 && precision != PREC_FP8W && precision != PREC_FP16) throw std::runtime_error("fortis_debug_pack_layer: precision");
+  return tc_debug_pack_layer(W, b, cout, cin, last, precision, image, bias, scale, K, N);
+  FORTIS_CATCH(return -1)
+}
+
 int fortis_debug_eval_expr(const char* exprs_json, int tv_double, double tv, const double* scalars, const int* scalar_elt,
                            int nscalars, double* out) {
   FORTIS_TRY

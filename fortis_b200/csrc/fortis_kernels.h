@@ -81,6 +81,8 @@ struct TcModel;                                        // packed bf16 weights, T
 enum { PREC_F32 = 0, PREC_BF16 = 1, PREC_FP8W = 2, PREC_FP16 = 3 };
 bool tc_model_supported(const ModelHost& M, std::string* why);
 TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std::string* err);
+int tc_debug_pack_layer(const float* W, const float* b, int cout, int cin, int last, int precision, uint16_t* image, float* bias,
+                        float* scale, int* K, int* N);
 void tc_model_destroy(TcModel* m);
 struct TcLaunch {
   const IoPlanDev* GP; const Access* slots;          // gather plan, or null with X set

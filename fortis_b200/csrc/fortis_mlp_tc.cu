@@ -769,6 +769,64 @@ float e4m3_round(float v) {
 
 TcTestKnobs g_tc_test = {0u, 0};
 
+// One Linear layer converted for the tensor-core kernel: padded, rounded to the 16-bit operand type (FP8 weights: the
+// nearest E4M3 code of w / scale, which bf16 represents exactly), as row-major [N][K] (`rowmajor`, optional) and as
+// the stage images the kernel streams: per chunk of 64 features and per 256-wide K-block one contiguous 32 KB block
+// holding four 64 x 64 sub-tiles in the 128-byte-swizzled K-major layout the MMA descriptor expects (16-byte piece j of
+// row r sits at piece j ^ (r & 7)), so that a stage is ONE linear bulk copy.
+void pack_layer_host(const LayerHost& L, bool last, int precision, PackedLayer* Q, std::vector<uint16_t>* rowmajor) {
+  const int K = round_up(L.cin, kBlockK);
+  const int N = last ? round_up(L.cout, kChunkN) : round_up(L.cout, kBlockK);
+  std::vector<uint16_t> wb((size_t)N * K, 0);
+  Q->K = K; Q->N = N;
+  Q->bias.assign(N, 0.f); Q->scale.assign(N, 1.f);
+  for (int n = 0; n < L.cout; n++) {
+    Q->bias[n] = L.b[n];
+    float sc = 1.f;
+    if (precision == PREC_FP8W) {
+      float amax = 0.f;
+      for (int k = 0; k < L.cin; k++) amax = std::fmax(amax, std::fabs(L.W[(size_t)n * L.cin + k]));
+      sc = amax > 0.f ? amax / 448.0f : 1.0f;
+      Q->scale[n] = sc;
+    }
+    for (int k = 0; k < L.cin; k++) {
+      float w = L.W[(size_t)n * L.cin + k];
+      if (precision == PREC_FP8W) w = e4m3_round(w / sc);
+      wb[(size_t)n * K + k] = precision == PREC_FP16 ? f32_to_f16(w) : f32_to_bf16(w);
+    }
+  }
+  Q->image.assign((size_t)N * K, 0);
+  const int nks = K / kStageK;
+  for (int c = 0; c < N / kChunkN; c++)
+    for (int ks = 0; ks < nks; ks++) {
+      uint16_t* blk = Q->image.data() + ((size_t)c * nks + ks) * (kStageBytes / 2);
+      for (int t = 0; t < kStageK / 64; t++)
+        for (int r = 0; r < kChunkN; r++)
+          for (int j = 0; j < 8; j++) {
+            const uint16_t* src = wb.data() + (size_t)(c * kChunkN + r) * K + ks * kStageK + t * 64 + j * 8;
+            uint16_t* dst = blk + (size_t)t * (kChunkN * 64) + r * 64 + ((j ^ (r & 7)) * 8);
+            std::memcpy(dst, src, 16);
+          }
+    }
+  if (rowmajor) rowmajor->swap(wb);
+}
+
+// host-only: the stage images of one layer, for tests that compare them with the exporter's
+int tc_debug_pack_layer(const float* W, const float* b, int cout, int cin, int last, int precision, uint16_t* image, float* bias,
+                        float* scale, int* K, int* N) {
+  LayerHost L;
+  L.cin = cin; L.cout = cout;
+  L.W.assign(W, W + (size_t)cout * cin);
+  L.b.assign(b, b + cout);
+  PackedLayer Q;
+  pack_layer_host(L, last != 0, precision, &Q, nullptr);
+  *K = Q.K; *N = Q.N;
+  if (image) std::memcpy(image, Q.image.data(), Q.image.size() * 2);
+  if (bias) std::memcpy(bias, Q.bias.data(), Q.bias.size() * 4);
+  if (scale) std::memcpy(scale, Q.scale.data(), Q.scale.size() * 4);
+  return 0;
+}
+
 struct TcModel {
   int nlayers = 0, n_in = 0, n_out = 0;
   std::vector<void*> w;            // bf16 [N][K] padded
@@ -823,43 +881,16 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
   auto fail = [&](const std::string& w) { if (err) *err = w; tc_model_destroy(m); return (TcModel*)nullptr; };
   for (int l = 0; l < m->nlayers; l++) {
     const LayerHost& L = M.layers[l];
-    const int K = round_up(L.cin, kBlockK);
-    const int N = l + 1 < m->nlayers ? round_up(L.cout, kBlockK) : round_up(L.cout, kChunkN);
-    std::vector<uint16_t> wb((size_t)N * K, 0);
-    std::vector<float> bias(N, 0.f), scale(N, 1.f);
-    for (int n = 0; n < L.cout; n++) {
-      bias[n] = L.b[n];
-      float sc = 1.f;
-      if (precision == PREC_FP8W) {
-        float amax = 0.f;
-        for (int k = 0; k < L.cin; k++) amax = std::fmax(amax, std::fabs(L.W[(size_t)n * L.cin + k]));
-        sc = amax > 0.f ? amax / 448.0f : 1.0f;
-        scale[n] = sc;
-      }
-      for (int k = 0; k < L.cin; k++) {
-        float w = L.W[(size_t)n * L.cin + k];
-        if (precision == PREC_FP8W) w = e4m3_round(w / sc);       // E4M3 codes are exact in bf16
-        wb[(size_t)n * K + k] = precision == PREC_FP16 ? f32_to_f16(w) : f32_to_bf16(w);
-      }
-    }
-    // The same weights as the stage images the kernel streams: per chunk of 64 features and per 256-wide K-block one
-    // contiguous 32 KB block holding four 64 x 64 sub-tiles in the 128-byte-swizzled K-major layout the MMA descriptor
-    // expects (16-byte piece j of row r sits at piece j ^ (r & 7)), so that a stage is ONE linear bulk copy.
-    std::vector<uint16_t> wt((size_t)N * K, 0);
-    {
-      const int nks = K / kStageK;
-      for (int c = 0; c < N / kChunkN; c++)
-        for (int ks = 0; ks < nks; ks++) {
-          uint16_t* blk = wt.data() + ((size_t)c * nks + ks) * (kStageBytes / 2);
-          for (int t = 0; t < kStageK / 64; t++)
-            for (int r = 0; r < kChunkN; r++)
-              for (int j = 0; j < 8; j++) {
-                const uint16_t* src = wb.data() + (size_t)(c * kChunkN + r) * K + ks * kStageK + t * 64 + j * 8;
-                uint16_t* dst = blk + (size_t)t * (kChunkN * 64) + r * 64 + ((j ^ (r & 7)) * 8);
-                std::memcpy(dst, src, 16);
-              }
-        }
-    }
+    PackedLayer Q;
+    std::vector<uint16_t> wb;
+    const bool prepacked = FORTIS_TC_TILED_W && M.packed_precision == precision && l < (int)M.packed.size() &&
+                           M.packed[l].K == round_up(L.cin, kBlockK) &&
+                           M.packed[l].N == (l + 1 < m->nlayers ? round_up(L.cout, kBlockK) : round_up(L.cout, kChunkN));
+    if (prepacked) Q = M.packed[l];                        // the blob carries this precision's stage images
+    else pack_layer_host(L, l + 1 == m->nlayers, precision, &Q, &wb);
+    const int K = Q.K, N = Q.N;
+    const std::vector<uint16_t>& wt = Q.image;
+    const std::vector<float>&bias = Q.bias, &scale = Q.scale;
     // only the form this build streams goes to the device
     void *dw = nullptr, *dwt = nullptr; float *db = nullptr, *ds = nullptr;
     const std::vector<uint16_t>& image = FORTIS_TC_TILED_W ? wt : wb;

@@ -12,6 +12,17 @@
 //   f32 in_div[n_in_div]        input is divided by it      (mom6_zb/export_zb.py:13)
 //   f32 out_mul[n_out_mul]      output is multiplied by it  (mom6_zb/export_zb.py:14)
 //   f32 relu_mask[n_relu_mask]  outputs with mask != 0 get a final ReLU (benchmarks/climsim/export_wide.py:24-27)
+//
+// Optional pre-packed section behind it (MLP models): the weights already converted for one tensor-core precision and
+// laid out as the 32 KB stage images the fused kernel streams, so that loading is a copy.
+//   char  tag[8] = "FORTISP1"
+//   u32   precision (1 = bf16, 2 = FP8-E4M3 weights as bf16 codes + per-channel scales, 3 = fp16), nlayers
+//   u64   FNV-1a 64 of every byte in front of the tag: the section belongs to exactly these fp32 weights
+//   per layer:  u32 K_pad, N_pad;  u16 image[N_pad * K_pad];  f32 bias[N_pad];  f32 scale[N_pad]
+//               image: [chunk of 64 features][256-wide K-block] blocks of four 64 x 64 sub-tiles, K-major rows of 128
+//               bytes, 16-byte piece j of row r stored at piece j ^ (r & 7)
+//   u64   FNV-1a 64 of the section from its tag up to here
+// A section whose hashes do not match is an error, one for another precision than the session's is ignored.
 #pragma once
 #include <cstdint>
 #include <cstring>
@@ -30,9 +41,17 @@ struct LayerHost {
   std::vector<float> W, b;
 };
 
+struct PackedLayer {
+  int K = 0, N = 0;                      // padded extents
+  std::vector<uint16_t> image;           // stage images
+  std::vector<float> bias, scale;        // padded; scale is all ones unless the weights are FP8 codes
+};
+
 struct ModelHost {
   std::vector<LayerHost> layers;
   std::vector<float> in_div, out_mul, relu_mask;
+  int packed_precision = -1;             // precision of the pre-packed section, -1 = none
+  std::vector<PackedLayer> packed;
   bool is_mlp() const {
     for (auto& l : layers) if (l.kind != LAYER_LINEAR) return false;
     return !layers.empty();
@@ -44,6 +63,12 @@ struct ModelHost {
   int n_in() const { return layers.empty() ? 0 : layers.front().cin; }
   int n_out() const { return layers.empty() ? 0 : layers.back().cout; }
 };
+
+inline uint64_t fnv1a64(const uint8_t* p, size_t n) {
+  uint64_t h = 1469598103934665603ull;
+  for (size_t i = 0; i < n; i++) { h ^= p[i]; h *= 1099511628211ull; }
+  return h;
+}
 
 inline ModelHost parse_model_blob(const void* data, size_t nbytes) {
   const uint8_t* p = (const uint8_t*)data;
@@ -74,6 +99,31 @@ inline ModelHost parse_model_blob(const void* data, size_t nbytes) {
   if (nid && (int)nid != M.n_in()) throw std::runtime_error("model blob: in_div length != model inputs");
   if (nom && (int)nom != M.n_out()) throw std::runtime_error("model blob: out_mul length != model outputs");
   if (nrm && (int)nrm != M.n_out()) throw std::runtime_error("model blob: relu_mask length != model outputs");
+  if (p == end) return M;
+  // ---- pre-packed section
+  const uint8_t* sec = p;
+  need(8);
+  if (std::memcmp(p, "FORTISP1", 8) != 0) throw std::runtime_error("model blob: unknown data behind the layers");
+  p += 8;
+  auto u64 = [&]() { need(8); uint64_t v; std::memcpy(&v, p, 8); p += 8; return v; };
+  const uint32_t prec = u32(), npl = u32();
+  if (u64() != fnv1a64((const uint8_t*)data, (size_t)(sec - (const uint8_t*)data)))
+    throw std::runtime_error("model blob: the pre-packed section does not belong to these weights (hash mismatch)");
+  if (npl != nl || !M.is_mlp()) throw std::runtime_error("model blob: pre-packed section does not match the layer list");
+  for (uint32_t l = 0; l < npl; l++) {
+    PackedLayer Q;
+    Q.K = (int)u32(); Q.N = (int)u32();
+    if (Q.K < M.layers[l].cin || Q.N < M.layers[l].cout || Q.K % 256 || Q.N % 64 || Q.K > 4096 || Q.N > 4096)
+      throw std::runtime_error("model blob: bad pre-packed layer shape");
+    const size_t n = (size_t)Q.K * Q.N;
+    need(n * 2); Q.image.resize(n); std::memcpy(Q.image.data(), p, n * 2); p += n * 2;
+    floats(Q.bias, (size_t)Q.N); floats(Q.scale, (size_t)Q.N);
+    M.packed.push_back(std::move(Q));
+  }
+  const uint64_t want = fnv1a64(sec, (size_t)(p - sec));
+  if (u64() != want) throw std::runtime_error("model blob: pre-packed section is corrupt (hash mismatch)");
+  if (p != end) throw std::runtime_error("model blob: unknown data behind the pre-packed section");
+  M.packed_precision = (int)prec;
   return M;
 }
 

@@ -14,6 +14,14 @@ int fortis_debug_eval_expr(const char* exprs_json, int tv_double, double tv, con
 int fortis_debug_plan(const char* desc_json, const char* loop_json, const char* kdist_json, int is_scatter, long row,
                       const int* args, int nargs, long long* offsets, int* arrays, int* slots, int cap, long long* geom);
 
+/* Host-only: one Linear layer (W (cout, cin) row-major fp32, b) converted as the tensor-core kernel wants it for
+ * `precision` (1 = bf16, 2 = FP8-E4M3 weights, 3 = fp16): the padded extents in *K / *N and, into the buffers that are
+ * not null, the stage images (N x K 16-bit values), the padded bias and the per-channel scales.  `last` != 0 pads the
+ * output width to 64 instead of 256.  Call once with null buffers to learn K and N.  Used to check that the exporter's
+ * pre-packed blobs (fortis_b200.model.write_blob(prepack=...)) are bit-identical to what the loader would compute. */
+int fortis_debug_pack_layer(const float* W, const float* b, int cout, int cin, int last, int precision, unsigned short* image,
+                            float* bias, float* scale, int* K, int* N);
+
 #ifdef __cplusplus
 }
 #endif

@@ -119,3 +119,43 @@ def test_random_descriptor_cases_are_valid_for_planner_and_oracle():
                                   len(args), offs, arrs, slots, 64, geom)
         assert n == G["n"], (case, lib.fortis_last_error_message())
         assert geom[0] == P["count"] and geom[1] == P["nk"]
+
+
+def test_prepacked_blob_matches_the_loaders_own_packing_and_is_hash_checked():
+    """write_blob(prepack=...) carries the weights already converted and tiled for one tensor-core precision.  The
+    exporter's arithmetic (bf16 / fp16 rounding, E4M3 codes and per-channel scales, padding, 128-byte swizzle of the
+    stage images) must equal the loader's bit for bit, and a section that does not belong to the weights in front of
+    it, or that is damaged, must be refused."""
+    import ctypes
+    import fortis_b200
+    from fortis_b200 import model as M
+    L = fortis_b200.load()
+    fp, ci = ctypes.POINTER(ctypes.c_float), ctypes.c_int
+    L.fortis_debug_pack_layer.argtypes = [fp, fp, ci, ci, ci, ci, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.POINTER(ci), ctypes.POINTER(ci)]
+    rng = np.random.default_rng(0)
+    for prec in ("bf16", "fp16", "fp8w"):
+        for cout, cin, last in ((768, 244, 0), (128, 768, 1), (20, 27, 0), (3, 20, 1)):
+            W = rng.normal(0, 0.1, size=(cout, cin)).astype(np.float32)
+            b = rng.normal(size=cout).astype(np.float32)
+            W[0, :] = 0                                               # a dead channel: scale 1
+            W[1, :5] = [1.0, 2.0, 0.5, 448.0, -448.0]
+            W[2, :4] = [1.9999999, 2.0000002, 0.99999994, 1e-9]       # either side of a binade, and a flush to zero
+            K, N, img, bias, scale = M.pack_layer(W, b, bool(last), prec)
+            k, n = ci(), ci()
+            im2, b2, s2 = np.zeros(K * N, np.uint16), np.zeros(N, np.float32), np.zeros(N, np.float32)
+            rc = L.fortis_debug_pack_layer(W.ctypes.data_as(fp), b.ctypes.data_as(fp), cout, cin, last, M.PRECISIONS[prec],
+                                           im2.ctypes.data, b2.ctypes.data, s2.ctypes.data, ctypes.byref(k), ctypes.byref(n))
+            assert rc == 0 and (k.value, n.value) == (K, N)
+            assert np.array_equal(im2, img) and np.array_equal(b2, bias) and np.array_equal(s2, scale), (prec, cout, cin)
+    layers = M.mlp_layers([27, 20, 20, 3], seed=4, init="uniform", act="relu", bias="uniform")
+    plain, packed = M.write_blob(layers), M.write_blob(layers, prepack="bf16")
+    assert packed.startswith(plain) and packed[len(plain):len(plain) + 8] == b"FORTISP1"
+    load = lambda blob: L.fortis_load_model_mem(ctypes.c_char_p(blob), len(blob))
+    assert load(packed) == 0
+    damaged = bytearray(packed); damaged[len(plain) + 40] ^= 1                      # inside the first stage image
+    assert load(bytes(damaged)) == -1 and b"corrupt" in L.fortis_last_error_message()
+    other = M.write_blob(M.mlp_layers([27, 20, 20, 3], seed=5, init="uniform", act="relu", bias="uniform"))
+    assert load(other + packed[len(plain):]) == -1 and b"does not belong" in L.fortis_last_error_message()
+    assert load(plain + b"junkjunk") == -1
+    L.fortis_reset()

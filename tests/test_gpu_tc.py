@@ -11,6 +11,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 import fortis_b200
+from fortis_b200 import workloads as W
 from oracle import fortis_oracle as fo
 
 BF16_TOL, FP8W_TOL, MODEL_TOL = 5e-3, 2e-2, 2e-3
@@ -151,3 +152,23 @@ def test_relu_mask_and_graph_replay(host):
     host.check()
     assert fo.rel_l2(outs[0], want) < MODEL_TOL
     assert all(o.tobytes() == outs[0].tobytes() for o in outs[1:])      # eager, captured and replayed runs agree
+
+
+@pytest.mark.parametrize("precision", ["bf16", "fp8w", "fp16"])
+def test_prepacked_blob_gives_the_same_bits(host, precision):
+    """A blob that carries the stage images for the session's precision loads by copying; the step must be bit-identical
+    to the one whose weights the loader converted itself, and a section for another precision is ignored."""
+    wl = W.column(2000)
+    outs = []
+    for prepack in (None, precision, "fp16" if precision != "fp16" else "bf16"):
+        host.reset()
+        host.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"])
+        host.load_model(fortis_b200.write_blob(wl["layers"], prepack=prepack))
+        host.option("precision", precision)
+        d_in = [torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda() for a in wl["gin"]]
+        d_out = [torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda() for a in wl["sout"]]
+        host.step(d_in, d_out)
+        host.sync()
+        outs.append(torch.cat(d_out).cpu().numpy())
+    assert outs[0].tobytes() == outs[1].tobytes() == outs[2].tobytes()
+    assert np.abs(outs[0]).max() > 0
