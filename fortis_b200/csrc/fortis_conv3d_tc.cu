@@ -59,9 +59,20 @@ using namespace tc;
 
 namespace {
 
+// How the kw taps are applied.  0 (default): one MMA of N = 3 NOUT per (kd, kh) group on unshifted rows, the shift
+// applied in the epilogue (three accumulator loads, 64 shuffles and a shared-memory exchange per row).  1: one MMA of
+// N = NOUT per tap, the kw shift taken on the A side (the descriptor's start address moves by kw rows, exactly as it
+// moves by kh (W+2) rows), so a tile's accumulator IS the output tile and the epilogue is one accumulator load per
+// row.  Bit-compatible tests pass for both; measured on the 8 x 33^3 network 1 is slower (0.895 vs 0.844 ms): three
+// N = 64 MMAs read the activation slice three times and the kernel becomes bound by shared-memory operand reads.
+#ifndef FORTIS_CONV_SHIFT_A
+#define FORTIS_CONV_SHIFT_A 0
+#endif
+constexpr bool kShiftA = FORTIS_CONV_SHIFT_A != 0;
 constexpr int kC = 64;                       // channels of the tensor-core layers
 constexpr int kTile = 128;                   // rows computed per tile (the MMA's M)
-constexpr int kTileOut = kTile - 2;          // rows written per tile: the first and last computed rows only feed their neighbours
+constexpr int kTileOut = kShiftA ? kTile : kTile - 2;   // rows written per tile (epilogue-side shift: the first and last computed rows only feed their neighbours)
+constexpr int kHalo = kShiftA ? 1 : 0;       // rows in front of and behind a stage's 128 + 2 (W+2) rows, for the kw shift
 constexpr int kRingBytes = 108 * 1024;       // activation ring: nstages stages of (128 + 2 (W+2)) rows each
 constexpr int kMaxStages = 7;
 constexpr int kXchBytes = 2 * 2 * 4 * kC * 4; // rows exchanged between epilogue warps: [tile parity][up | down][quadrant][channel] floats
@@ -71,7 +82,7 @@ constexpr int kConvSmem = kResW + kRingBytes + 256 + kXchBytes;
 constexpr int kAccStride = 256;              // TMEM columns between the two accumulators (each 3 * NOUT wide)
 // the pair's M = 256; operand format code 1 = bf16, 0 = IEEE half (bits 7-9 for A, 10-12 for B)
 template <int NOUT, bool F16> struct ConvIdesc {
-  static constexpr uint32_t value = idesc_bf16(2 * kTile, 3 * NOUT) & ~(F16 ? ((1u << 7) | (1u << 10)) : 0u);
+  static constexpr uint32_t value = idesc_bf16(2 * kTile, kShiftA ? NOUT : 3 * NOUT) & ~(F16 ? ((1u << 7) | (1u << 10)) : 0u);
 };
 // the 16-bit storage format of activations and weights: bf16 (range of fp32, 8 significant bits) or IEEE half (11
 // significant bits, values beyond 65504 overflow)
@@ -116,9 +127,10 @@ __device__ __forceinline__ void cprof_add(long long* prof, int slot, long long* 
 // Launched as clusters of two CTAs (cta_group::2): the leader's MMA warp issues for both.
 template <int KSTEPS, int NOUT, bool LAST, bool F16>
 __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid_constant__ ConvTcParams P) {
-  constexpr uint32_t kIdescN = ConvIdesc<NOUT, F16>::value;            // M = 256 (128 rows per CTA), N = 3 * NOUT
-  constexpr int kHalfRows = 3 * NOUT / 2;                         // weight rows of one (kd, kh) group held by each CTA
-  constexpr int kHalfBytes = kHalfRows * kC * 2;                  // 12 KB (3 KB for the last layer)
+  constexpr uint32_t kIdescN = ConvIdesc<NOUT, F16>::value;            // M = 256 (128 rows per CTA), N = NOUT per tap (or 3 * NOUT per group)
+  constexpr int kWLoads = kShiftA ? 27 : 9;                       // weight tiles: one per tap, or one per (kd, kh) group
+  constexpr int kHalfRows = (kShiftA ? NOUT : 3 * NOUT) / 2;      // weight rows of one tile held by each CTA
+  constexpr int kHalfBytes = kHalfRows * kC * 2;                  // 4 KB per tap (12 KB per group)
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);                           // resident weights at offset 0
   if (base & 1023u) {                                             // same in both CTAs of a pair: both leave
@@ -164,20 +176,20 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     // ---- TMA producer (one per CTA): this CTA's half of the weights once, then per tile 9 activation tiles.
     //      Completion of both CTAs' copies is counted on the LEADER's barriers, which the leader arms for both.
     const uint32_t full0 = map_to_cta(bar_full, 0), w0 = map_to_cta(bar_w, 0);
-    if (crank == 0) mbar_expect_tx(bar_w, 2 * 9 * kHalfBytes);
+    if (crank == 0) mbar_expect_tx(bar_w, 2 * kWLoads * kHalfBytes);
 #pragma unroll 1
-    for (int g = 0; g < 9; g++)
-      tma_load_2d_pair(base + g * kHalfBytes, &P.wmap, 0, g * 3 * NOUT + (int)crank * kHalfRows, w0);
+    for (int g = 0; g < kWLoads; g++)
+      tma_load_2d_pair(base + g * kHalfBytes, &P.wmap, 0, g * 2 * kHalfRows + (int)crank * kHalfRows, w0);
     uint32_t s = 0, ph = 0;
     bool stop = false;
     const bool pw = blockIdx.x == 0 && lane == 0;
     long long pt = clock64();
     for (long long tp = pair0; tp < npairs && !stop; tp += pair_step) {
-      const long long q0 = (2 * tp + crank) * kTileOut - 1;       // first computed row of this CTA's tile
+      const long long q0 = (2 * tp + crank) * kTileOut - (kShiftA ? 0 : 1);       // first computed row of this CTA's tile
       for (int kd = 0; kd < 3; kd++) {
         // rows q0 + (kd-1) Hp Wp - Wp ... + 127 + Wp serve the three kh taps of this kd.  The allocation carries zero
         // rows on both sides, so every coordinate is in bounds.
-        const int y0 = (int)(q0 + (long long)(kd - 1) * Hp * Wp - Wp) + P.front;
+        const int y0 = (int)(q0 + (long long)(kd - 1) * Hp * Wp - Wp - kHalo) + P.front;
         cprof_add(P.prof, 7, &pt, pw);
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, CST_EMPTY, P.wait_limit)) { stop = true; break; }
         cprof_add(P.prof, 6, &pt, pw);
@@ -215,11 +227,23 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
           for (int kh = 0; kh < 3; kh++) {
             // tap row kh reads the stage kh * Wp rows further down: the descriptor's start address moves; the 128-byte
             // swizzle is a function of the shared-memory address, so the shifted view matches what TMA wrote
-            const uint64_t ad = desc_hi | (uint64_t)(((sa + kh * Wp * (kC * 2)) >> 4) & 0x3FFF);
-            const uint64_t bd = desc_hi | (uint64_t)(((base + (kd * 3 + kh) * kHalfBytes) >> 4) & 0x3FFF);
+            if constexpr (kShiftA) {
 #pragma unroll
-            for (int j = 0; j < KSTEPS; j++)
-              tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(kd | kh | j));
+              for (int kw = 0; kw < 3; kw++) {
+                // stage row 0 is input row q0 - (W+2) - 1 of this kd: output row r under tap (kh, kw) reads stage row r + kh (W+2) + kw
+                const uint64_t ad = desc_hi | (uint64_t)(((sa + (kh * Wp + kw) * (kC * 2)) >> 4) & 0x3FFF);
+                const uint64_t bd = desc_hi | (uint64_t)(((base + ((kd * 3 + kh) * 3 + kw) * kHalfBytes) >> 4) & 0x3FFF);
+#pragma unroll
+                for (int j = 0; j < KSTEPS; j++)
+                  tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(kd | kh | kw | j));
+              }
+            } else {
+              const uint64_t ad = desc_hi | (uint64_t)(((sa + kh * Wp * (kC * 2)) >> 4) & 0x3FFF);
+              const uint64_t bd = desc_hi | (uint64_t)(((base + (kd * 3 + kh) * kHalfBytes) >> 4) & 0x3FFF);
+#pragma unroll
+              for (int j = 0; j < KSTEPS; j++)
+                tc_mma_ss_pair<kIdescN>(d_tmem, ad + (uint64_t)(j * 2), bd + (uint64_t)(j * 2), (uint32_t)(kd | kh | j));
+            }
           }
           tc_commit_pair(bar_empty + 8 * s);                      // frees this stage in both CTAs
           if (++s == (uint32_t)P.nstages) { s = 0; ph ^= 1; }
@@ -246,11 +270,13 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
     const bool pw = blockIdx.x == 0 && threadIdx.x == 64;
     long long pt = clock64();
     const uint32_t uW = (uint32_t)Wp, uH = (uint32_t)Hp, uD = (uint32_t)Dp;
-    // row of this thread in tile pair tp_ and whether it is written / an interior voxel (P < 2^31: 32-bit arithmetic)
+    // row of this thread in tile pair tp_ and whether it is written / an interior voxel (P < 2^31: 32-bit arithmetic).
+    // (Advancing the coordinates from tile to tile by additions with carries instead of dividing was measured 6 %
+    // SLOWER over the whole kernel: the divisions sit in front of the accumulator wait, where the warp would idle.)
     auto locate = [&](long long tp_, uint32_t& p_, bool& writes_, bool& interior_, uint32_t& wp_, uint32_t& hp_, uint32_t& dp_, uint32_t& n_) {
-      const int r = quad * 32 + lane;                              // rows 0 and 127 of a tile are computed for their neighbours only
-      const long long pl = (2 * tp_ + crank) * kTileOut + r - 1;
-      writes_ = active && tp_ < npairs && r >= 1 && r <= kTileOut && pl < P.P;
+      const int r = quad * 32 + lane;                              // epilogue-side shift: rows 0 and 127 are computed for their neighbours only
+      const long long pl = (2 * tp_ + crank) * kTileOut + r - (kShiftA ? 0 : 1);
+      writes_ = active && tp_ < npairs && (kShiftA || (r >= 1 && r <= kTileOut)) && pl < P.P;
       p_ = writes_ ? (uint32_t)pl : 0u;
       const uint32_t t1 = p_ / uW, t2 = t1 / uH;
       wp_ = p_ - t1 * uW; hp_ = t1 - t2 * uH; n_ = t2 / uD; dp_ = t2 - n_ * uD;
@@ -278,38 +304,49 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       cprof_add(P.prof, 8, &pt, pw);
       tc_fence_after();
       const uint32_t accb = lane_addr + b * kAccStride + c0;
-      uint32_t a0[CW], a1[CW], a2[CW];
-      if (active) {
-        tmem_ldn(accb, a0);
-        tmem_ldn(accb + NOUT, a1);
-        tmem_ldn(accb + 2 * NOUT, a2);
-        tmem_ld_wait();
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_relaxed(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
-      if (!active) continue;
-      // rows on either side of a warp boundary go through shared memory (the buffer alternates per tile, so one
-      // barrier per tile among the four warps that hold the same channels is enough)
-      float* xu = xch + (acc_it & 1) * (2 * 4 * kC);               // kw = 0 partials of each quadrant's last row
-      float* xd = xu + 4 * kC;                                     // kw = 2 partials of each quadrant's first row
-      if (lane == 31) {
-#pragma unroll
-        for (int i = 0; i < CW; i++) xu[quad * kC + c0 + i] = __uint_as_float(a0[i]);
-      }
-      if (lane == 0) {
-#pragma unroll
-        for (int i = 0; i < CW; i++) xd[quad * kC + c0 + i] = __uint_as_float(a2[i]);
-      }
-      if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
       float v[CW];
+      if constexpr (kShiftA) {
+        uint32_t a1[CW];
+        if (active) { tmem_ldn(accb, a1); tmem_ld_wait(); }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
+        if (!active) continue;
 #pragma unroll
-      for (int i = 0; i < CW; i++) {
-        float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
-        float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
-        if (lane == 0 && quad > 0) up = xu[(quad - 1) * kC + c0 + i];
-        if (lane == 31 && quad < 3) dn = xd[(quad + 1) * kC + c0 + i];
-        v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[i]);
+        for (int i = 0; i < CW; i++) v[i] = __uint_as_float(a1[i]) + bias[i];
+      } else {
+        uint32_t a0[CW], a1[CW], a2[CW];
+        if (active) {
+          tmem_ldn(accb, a0);
+          tmem_ldn(accb + NOUT, a1);
+          tmem_ldn(accb + 2 * NOUT, a2);
+          tmem_ld_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(arr_acc_empty + 8 * b);   // one arrival per warp: the leader may refill this accumulator
+        if (!active) continue;
+        // rows on either side of a warp boundary go through shared memory (the buffer alternates per tile, so one
+        // barrier per tile among the four warps that hold the same channels is enough)
+        float* xu = xch + (acc_it & 1) * (2 * 4 * kC);               // kw = 0 partials of each quadrant's last row
+        float* xd = xu + 4 * kC;                                     // kw = 2 partials of each quadrant's first row
+        if (lane == 31) {
+#pragma unroll
+          for (int i = 0; i < CW; i++) xu[quad * kC + c0 + i] = __uint_as_float(a0[i]);
+        }
+        if (lane == 0) {
+#pragma unroll
+          for (int i = 0; i < CW; i++) xd[quad * kC + c0 + i] = __uint_as_float(a2[i]);
+        }
+        if (half == 0) asm volatile("bar.sync 1, 128;" ::: "memory"); else asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < CW; i++) {
+          float up = __shfl_up_sync(0xffffffffu, __uint_as_float(a0[i]), 1);
+          float dn = __shfl_down_sync(0xffffffffu, __uint_as_float(a2[i]), 1);
+          if (lane == 0 && quad > 0) up = xu[(quad - 1) * kC + c0 + i];
+          if (lane == 31 && quad < 3) dn = xd[(quad + 1) * kC + c0 + i];
+          v[i] = (__uint_as_float(a1[i]) + up) + (dn + bias[i]);
+        }
       }
       if (LAST) {
         if (interior) {
@@ -411,7 +448,7 @@ bool make_map(CUtensorMap* m, void* base, long long rows, int box_rows) {
 // nbox boxes of box_rows (<= 256, multiple of 8) rows
 struct RingGeom { int stage_bytes, nstages, box_rows, nbox; };
 bool ring_geometry(int Wp, RingGeom* g) {
-  const int R = kTile + 2 * Wp;
+  const int R = kTile + 2 * Wp + 2 * kHalo;
   g->nbox = (R + 255) / 256;
   g->box_rows = (((R + g->nbox - 1) / g->nbox) + 7) / 8 * 8;
   g->stage_bytes = ((g->nbox * g->box_rows * kC * 2) + 1023) / 1024 * 1024;
@@ -507,7 +544,7 @@ ConvTcModel* conv_tc_create(const ModelHost& M, bool f16, std::string* err) {
     if (!dw || !db) return fail("out of device memory for conv weights");
     m->w.push_back(dw); m->b.push_back(db);
     CUtensorMap map;
-    if (!make_map(&map, dw, 27 * rows, 3 * rows / 2)) return fail("cuTensorMapEncodeTiled failed for conv weights");
+    if (!make_map(&map, dw, 27 * rows, (kShiftA ? rows : 3 * rows) / 2)) return fail("cuTensorMapEncodeTiled failed for conv weights");
     m->wmaps.push_back(map);
   }
   if (cudaMalloc(&m->status, sizeof(int)) != cudaSuccess) return fail("out of device memory");
