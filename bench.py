@@ -373,9 +373,13 @@ class Bench:
         """Per-step CUDA events on the library's stream.  Returns (max over ranks of the summed step times in ms,
         this rank's per-step times)."""
         torch = self.torch
-        for _ in range(warmup):
+        # the last warm-up step runs BEHIND the barrier: ranks wait there for the slowest one with an idle GPU, and the
+        # first large step after an idle period ran at half speed while the clocks came back (7.2 ms instead of 3.8)
+        for _ in range(max(0, warmup - 1)):
             fn()
         self.barrier()
+        if warmup > 0:
+            fn()
         ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         for s, e in ev:
             with torch.cuda.stream(self.stream):
