@@ -141,6 +141,7 @@ struct Session {
   TcModel* tc = nullptr;
   F32TcModel* f32 = nullptr;                   // fp32 precision on the tensor cores (split TF32), large batches
   ConvModel* conv = nullptr;
+  OpNet* opnet = nullptr;
   int conv_shape[4] = {0, 0, 0, 0};
 
   int precision = PREC_F32;
@@ -221,6 +222,7 @@ void free_model_dev() {
   if (s.tc) { tc_model_destroy(s.tc); s.tc = nullptr; }
   if (s.f32) { f32tc_destroy(s.f32); s.f32 = nullptr; }
   if (s.conv) { conv_model_destroy(s.conv); s.conv = nullptr; }
+  if (s.opnet) { opnet_destroy(s.opnet); s.opnet = nullptr; }
   s.model_on_dev = false;
   s.small_ok = false; s.stencil_ok = false;
 }
@@ -376,8 +378,13 @@ void ensure_model() {
     std::string err;
     s.conv = conv_model_create(s.model, s.precision, st, &err);
     if (!s.conv) throw std::runtime_error("conv3d model: " + err);
+  } else if (s.model.is_opnet()) {
+    if (s.precision != PREC_F32) throw std::runtime_error("networks of 2-D operator layers run in fp32");
+    std::string err;
+    s.opnet = opnet_create(s.model, &err);
+    if (!s.opnet) throw std::runtime_error("2-D network: " + err);
   } else {
-    throw std::runtime_error("a model must be all Linear or all Conv3d layers");
+    throw std::runtime_error("a model must be all Linear, all Conv3d or all 2-D operator layers");
   }
   s.model_on_dev = true;
   drop_graph();
@@ -385,12 +392,23 @@ void ensure_model() {
 
 long long model_rows() {
   Session& s = S();
-  if (s.model.is_conv()) return (long long)s.conv_shape[0] * s.conv_shape[1] * s.conv_shape[2] * s.conv_shape[3];
+  if (s.model.is_conv() || s.model.is_opnet()) return (long long)s.conv_shape[0] * s.conv_shape[1] * s.conv_shape[2] * s.conv_shape[3];
   if (s.planned && (s.G.h.ok || s.S.h.ok || s.have_l)) {
     if (s.begin_count >= 0 && s.have_l && !s.have_l2) return s.begin_count * s.loop.nk;   // run-time extent
     return s.loop.count * s.loop.nk;
   }
   return s.begin_count > 0 ? s.begin_count : 1;
+}
+
+// floats of the model output for `rows` input rows (a 2-D operator network changes the spatial extent)
+long long out_floats(long long rows) {
+  Session& s = S();
+  if (!s.model.is_opnet()) return rows * s.model.n_out();
+  int C = 0, Ho = 0, Wo = 0;
+  if (s.conv_shape[1] != 1) throw std::runtime_error("2-D network: option conv_shape must be N,1,H,W");
+  if (!opnet_shape(s.model, s.conv_shape[2], s.conv_shape[3], &C, &Ho, &Wo, nullptr))
+    throw std::runtime_error("2-D network: a layer's kernel is larger than its input");
+  return (long long)s.conv_shape[0] * C * Ho * Wo;
 }
 
 void ensure_buffers(long long rows) {
@@ -401,7 +419,8 @@ void ensure_buffers(long long rows) {
   for (auto& L : s.model.layers) wmax = L.cout > wmax ? L.cout : wmax;
   const long long nin = s.model.n_in(), nout = s.model.n_out();
   s.din = (float*)pool_alloc(rows * nin * 4);
-  s.dout = (float*)pool_alloc(rows * nout * 4);
+  s.dout = (float*)pool_alloc(out_floats(rows) * 4);
+  (void)nout;
   const bool need_act = s.model.is_mlp() && s.model.layers.size() > 1;
   s.act0 = need_act ? (float*)pool_alloc(rows * wmax * 4) : nullptr;
   s.act1 = need_act && s.model.layers.size() > 2 ? (float*)pool_alloc(rows * wmax * 4) : nullptr;
@@ -688,6 +707,11 @@ void run_step_kernels(const StepArgs& A) {
     std::string err;
     if (!conv_forward(s.conv, s.din, s.dout, s.conv_shape[0], s.conv_shape[1], s.conv_shape[2], s.conv_shape[3], st, &err))
       throw std::runtime_error(err);
+    return;
+  }
+  if (s.model.is_opnet()) {
+    std::string err;
+    if (!opnet_forward(s.opnet, s.din, s.dout, s.conv_shape[0], s.conv_shape[2], s.conv_shape[3], st, &err)) throw std::runtime_error(err);
     return;
   }
   const bool fuse = s.fuse && !A.unfused;
@@ -1435,7 +1459,7 @@ void mlp_download(void* out) {
   long long rows;
   prepare(&rows);
   cudaStreamSynchronize(stream());
-  cuda_ok(cudaMemcpy(out, s.dout, rows * s.model.n_out() * 4, is_device_ptr(out) ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost), "mlp_download");
+  cuda_ok(cudaMemcpy(out, s.dout, out_floats(rows) * 4, is_device_ptr(out) ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost), "mlp_download");
   FORTIS_CATCH(return)
 }
 
@@ -1479,11 +1503,11 @@ void mlp_forward(void* in, void* out) {
     if (!*reg) cudaGetLastError();
   };
   pin(&s.reg_in, in, (size_t)rows * nin * 4);
-  pin(&s.reg_out, out, (size_t)rows * nout * 4);
+  pin(&s.reg_out, out, (size_t)out_floats(rows) * 4);
   cuda_ok(cudaMemcpyAsync(s.din, in, rows * nin * 4, cudaMemcpyDefault, st), "H2D of the input");
   StepArgs A; A.rows = rows;
   run_step(A);
-  cuda_ok(cudaMemcpyAsync(out, s.dout, rows * nout * 4, cudaMemcpyDefault, st), "D2H of the output");
+  cuda_ok(cudaMemcpyAsync(out, s.dout, out_floats(rows) * 4, cudaMemcpyDefault, st), "D2H of the output");
   cudaStreamSynchronize(st);
   FORTIS_CATCH(return)
 }

@@ -28,6 +28,7 @@ namespace {
 struct ConvGeom {
   int N, D, H, W, C, F;
   int KD, KH, KW, pd, ph, pw, sd, sh, sw;
+  int dd, dh, dw;                             // input dilation (1 = none): tap positions that fall between input samples read zero
   int Do, Ho, Wo;
   long long xs_n, xs_d, xs_h, xs_w, xs_c;     // element strides of x
   long long ys_n, ys_d, ys_h, ys_w, ys_c;     // element strides of y (and of the residual)
@@ -63,8 +64,12 @@ __global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict
   const int ntaps = g.KD * g.KH * g.KW;
   for (int tap = 0; tap < ntaps; tap++) {
     const int kd = tap / (g.KH * g.KW), kh = (tap / g.KW) % g.KH, kw = tap % g.KW;
-    const int id = od * g.sd + kd - g.pd, ih = oh * g.sh + kh - g.ph, iw = ow * g.sw + kw - g.pw;
-    const bool inb = vlive && id >= 0 && id < g.D && ih >= 0 && ih < g.H && iw >= 0 && iw < g.W;
+    int id = od * g.sd + kd - g.pd, ih = oh * g.sh + kh - g.ph, iw = ow * g.sw + kw - g.pw;
+    bool inb = vlive && id >= 0 && ih >= 0 && iw >= 0;
+    if (g.dd > 1) { inb = inb && id % g.dd == 0; id /= g.dd; }
+    if (g.dh > 1) { inb = inb && ih % g.dh == 0; ih /= g.dh; }
+    if (g.dw > 1) { inb = inb && iw % g.dw == 0; iw /= g.dw; }
+    inb = inb && id < g.D && ih < g.H && iw < g.W;
     const float* xp = x + (long long)on * g.xs_n + (long long)id * g.xs_d + (long long)ih * g.xs_h + (long long)iw * g.xs_w;
     for (int c0 = 0; c0 < g.C; c0 += CBK) {
 #pragma unroll
@@ -136,9 +141,10 @@ __global__ void repack_weights_kernel(const float* __restrict__ w, float* __rest
   out[i] = w[((size_t)f * C + c) * taps + t];
 }
 
-// torch layout (F, C, K, K, K) -> [tap][C][F]
-std::vector<float> repack_weights(const float* w, int F, int C, int K) {
-  const int taps = K * K * K;
+// torch layout (F, C, taps...) -> [tap][C][F]
+std::vector<float> repack_weights_taps(const float* w, int F, int C, int taps);
+std::vector<float> repack_weights(const float* w, int F, int C, int K) { return repack_weights_taps(w, F, C, K * K * K); }
+std::vector<float> repack_weights_taps(const float* w, int F, int C, int taps) {
   std::vector<float> out((size_t)taps * C * F);
   for (int f = 0; f < F; f++)
     for (int c = 0; c < C; c++)
@@ -146,7 +152,155 @@ std::vector<float> repack_weights(const float* w, int F, int C, int K) {
   return out;
 }
 
+// ---- 2-D operator layers without weights (NCHW): the operator micro-suite's pooling and upsampling
+__global__ void maxpool2d_kernel(const float* __restrict__ x, float* __restrict__ y, long long planes, int H, int W, int KH, int KW,
+                                 int sh, int sw, int Ho, int Wo) {
+  const long long n = planes * Ho * Wo;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int ow = (int)(i % Wo), oh = (int)((i / Wo) % Ho);
+    const long long pl = i / ((long long)Wo * Ho);
+    const float* src = x + pl * H * W;
+    float m = -INFINITY;
+    for (int kh = 0; kh < KH; kh++)
+      for (int kw = 0; kw < KW; kw++) m = fmaxf(m, __ldg(src + (long long)(oh * sh + kh) * W + ow * sw + kw));
+    y[i] = m;
+  }
+}
+
+__global__ void upsample_nearest2d_kernel(const float* __restrict__ x, float* __restrict__ y, long long planes, int H, int W, int fh, int fw) {
+  const int Ho = H * fh, Wo = W * fw;
+  const long long n = planes * Ho * Wo;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int ow = (int)(i % Wo), oh = (int)((i / Wo) % Ho);
+    const long long pl = i / ((long long)Wo * Ho);
+    y[i] = __ldg(x + pl * H * W + (long long)(oh / fh) * W + ow / fw);
+  }
+}
+
 }  // namespace
+
+// ---------------------------------------------------------------------------------------------------------------
+// Networks of 2-D operator layers, NCHW fp32: Conv2d (any kernel, stride, padding; transposed convolutions as the
+// convolution of the dilated input; BatchNorm, explicit padding and channel concatenation of parallel convolutions are
+// folded into the weights by the exporter), MaxPool2d, nearest Upsample.  The counterpart of what the reference's
+// compiler generates for the operator micro-suite (tests/optest.py; compiler/FortisFuse.cpp:309-356 for the pad folding).
+// ---------------------------------------------------------------------------------------------------------------
+struct OpNet {
+  std::vector<LayerHost> meta;
+  std::vector<float*> wt, bias;           // per layer (null for layers without weights)
+  float* buf[2] = {nullptr, nullptr};
+  long long cap = 0;
+};
+
+void opnet_destroy(OpNet* m) {
+  if (!m) return;
+  for (float* p : m->wt) cudaFree(p);
+  for (float* p : m->bias) cudaFree(p);
+  for (float* p : m->buf) cudaFree(p);
+  delete m;
+}
+
+// output extent of one layer; false when the layer does not fit the input
+static bool opnet_layer_shape(const LayerHost& L, int H, int W, int* Ho, int* Wo) {
+  if (L.kind == LAYER_UPSAMPLE2D) { *Ho = H * L.sh; *Wo = W * L.sw; return true; }
+  const int He = (H - 1) * L.dil + 1 + 2 * L.ph + L.eh, We = (W - 1) * L.dil + 1 + 2 * L.pw + L.ew;
+  if (He < L.kh || We < L.kw) return false;
+  *Ho = (He - L.kh) / L.sh + 1; *Wo = (We - L.kw) / L.sw + 1;
+  return true;
+}
+
+bool opnet_shape(const ModelHost& M, int H, int W, int* C, int* Ho, int* Wo, long long* max_elems_per_image) {
+  long long mx = 0;
+  int c = M.n_in();
+  for (auto& L : M.layers) {
+    int h2, w2;
+    if (!opnet_layer_shape(L, H, W, &h2, &w2)) return false;
+    H = h2; W = w2; c = L.cout;
+    const long long e = (long long)c * H * W;
+    mx = e > mx ? e : mx;
+  }
+  *C = c; *Ho = H; *Wo = W;
+  if (max_elems_per_image) *max_elems_per_image = mx;
+  return true;
+}
+
+OpNet* opnet_create(const ModelHost& M, std::string* err) {
+  for (auto& L : M.layers)
+    if (L.kind != LAYER_CONV2D && (L.ph || L.pw || L.dil != 1 || L.eh || L.ew)) {
+      if (err) *err = "pooling and upsampling layers take no padding or dilation";
+      return nullptr;
+    }
+  OpNet* m = new OpNet();
+  for (auto& L : M.layers) {
+    LayerHost meta = L; meta.W.clear(); meta.b.clear();
+    m->meta.push_back(meta);
+    float *dw = nullptr, *db = nullptr;
+    if (L.kind == LAYER_CONV2D) {
+      const std::vector<float> wt = repack_weights_taps(L.W.data(), L.cout, L.cin, L.kh * L.kw);
+      if (cudaMalloc(&dw, wt.size() * 4) != cudaSuccess || cudaMalloc(&db, L.b.size() * 4) != cudaSuccess) {
+        if (err) *err = "out of device memory for conv weights";
+        cudaFree(dw); opnet_destroy(m);
+        return nullptr;
+      }
+      cudaMemcpy(dw, wt.data(), wt.size() * 4, cudaMemcpyHostToDevice);
+      cudaMemcpy(db, L.b.data(), L.b.size() * 4, cudaMemcpyHostToDevice);
+    }
+    m->wt.push_back(dw); m->bias.push_back(db);
+  }
+  return m;
+}
+
+// x (N, Cin, H, W) -> y (N, Cout, Ho, Wo)
+bool opnet_forward(OpNet* m, const float* x, float* y, int N, int H, int W, cudaStream_t s, std::string* err) {
+  if ((long long)N * H * W <= 0) { if (err) *err = "2-D network: set the input extent (option conv_shape = N,1,H,W)"; return false; }
+  // intermediate extents
+  long long mx = 0;
+  {
+    int h = H, w = W;
+    for (size_t l = 0; l + 1 < m->meta.size(); l++) {
+      int h2, w2;
+      if (!opnet_layer_shape(m->meta[l], h, w, &h2, &w2)) { if (err) *err = "2-D network: a layer's kernel is larger than its input"; return false; }
+      h = h2; w = w2;
+      const long long e = (long long)N * m->meta[l].cout * h * w;
+      mx = e > mx ? e : mx;
+    }
+  }
+  if (m->cap < mx) {
+    for (float*& p : m->buf) { cudaFree(p); p = nullptr; }
+    for (float*& p : m->buf)
+      if (cudaMalloc(&p, (size_t)mx * 4) != cudaSuccess) { if (err) *err = "out of device memory for 2-D network activations"; return false; }
+    m->cap = mx;
+  }
+  const float* src = x;
+  int h = H, w = W;
+  const int nl = (int)m->meta.size();
+  for (int l = 0; l < nl; l++) {
+    const LayerHost& L = m->meta[l];
+    float* dst = l == nl - 1 ? y : (src == m->buf[0] ? m->buf[1] : m->buf[0]);
+    int h2, w2;
+    if (!opnet_layer_shape(L, h, w, &h2, &w2)) { if (err) *err = "2-D network: a layer's kernel is larger than its input"; return false; }
+    const long long planes = (long long)N * L.cin, nout = (long long)N * L.cout * h2 * w2;
+    const unsigned blocks = (unsigned)((nout + 255) / 256 < 148 * 16 ? (nout + 255) / 256 : 148 * 16);
+    if (L.kind == LAYER_CONV2D) {
+      ConvGeom g;
+      g.N = N; g.D = 1; g.H = h; g.W = w; g.C = L.cin; g.F = L.cout;
+      g.KD = 1; g.KH = L.kh; g.KW = L.kw; g.pd = 0; g.ph = L.ph; g.pw = L.pw; g.sd = 1; g.sh = L.sh; g.sw = L.sw;
+      g.dd = 1; g.dh = g.dw = L.dil;
+      g.Do = 1; g.Ho = h2; g.Wo = w2;
+      g.xs_w = 1; g.xs_h = w; g.xs_d = (long long)h * w; g.xs_c = (long long)h * w; g.xs_n = (long long)L.cin * h * w;
+      g.ys_w = 1; g.ys_h = w2; g.ys_d = (long long)h2 * w2; g.ys_c = (long long)h2 * w2; g.ys_n = (long long)L.cout * h2 * w2;
+      launch_conv(src, m->wt[l], m->bias[l], nullptr, dst, g, L.act, L.slope, s);
+    } else if (L.kind == LAYER_MAXPOOL2D) {
+      maxpool2d_kernel<<<blocks, 256, 0, s>>>(src, dst, planes, h, w, L.kh, L.kw, L.sh, L.sw, h2, w2);
+    } else {
+      upsample_nearest2d_kernel<<<blocks, 256, 0, s>>>(src, dst, planes, h, w, L.sh, L.sw);
+    }
+    src = dst; h = h2; w = w2;
+  }
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { if (err) *err = std::string("2-D network launch: ") + cudaGetErrorString(e); return false; }
+  return true;
+}
 
 struct ConvModel {
   ConvTcModel* tcm = nullptr;           // bf16 tensor-core network (precision bf16); the fields below serve fp32
@@ -226,7 +380,7 @@ bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, i
     }
     ConvGeom g;
     g.N = N; g.D = D; g.H = H; g.W = W; g.C = L.cin; g.F = L.cout;
-    g.KD = g.KH = g.KW = L.ksize; g.pd = g.ph = g.pw = L.pad; g.sd = g.sh = g.sw = 1;
+    g.KD = g.KH = g.KW = L.ksize; g.pd = g.ph = g.pw = L.pad; g.sd = g.sh = g.sw = 1; g.dd = g.dh = g.dw = 1;
     g.Do = D; g.Ho = H; g.Wo = W;
     g.xs_c = 1; g.xs_w = L.cin; g.xs_h = (long long)W * L.cin; g.xs_d = (long long)H * W * L.cin; g.xs_n = (long long)D * H * W * L.cin;
     g.ys_c = 1; g.ys_w = L.cout; g.ys_h = (long long)W * L.cout; g.ys_d = (long long)H * W * L.cout; g.ys_n = (long long)D * H * W * L.cout;
@@ -276,6 +430,7 @@ bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D,
   ConvGeom g;
   g.N = N; g.D = D; g.H = H; g.W = W; g.C = C; g.F = F;
   g.KD = K[0]; g.KH = K[1]; g.KW = K[2]; g.sd = stride[0]; g.sh = stride[1]; g.sw = stride[2]; g.pd = pad[0]; g.ph = pad[1]; g.pw = pad[2];
+  g.dd = g.dh = g.dw = 1;
   g.Do = (D + 2 * pad[0] - K[0]) / stride[0] + 1; g.Ho = (H + 2 * pad[1] - K[1]) / stride[1] + 1; g.Wo = (W + 2 * pad[2] - K[2]) / stride[2] + 1;
   g.xs_w = 1; g.xs_h = W; g.xs_d = (long long)H * W; g.xs_c = (long long)D * H * W; g.xs_n = (long long)C * D * H * W;
   g.ys_w = 1; g.ys_h = g.Wo; g.ys_d = (long long)g.Ho * g.Wo; g.ys_c = (long long)g.Do * g.Ho * g.Wo; g.ys_n = (long long)F * g.Do * g.Ho * g.Wo;

@@ -132,6 +132,12 @@ void conv_model_clear_status(ConvModel* m);        // 0, or the code of a bounde
 // x (N,D,H,W,Cin) fp32 NDHWC on the device -> y (N,D,H,W,Cout)
 bool conv_forward(ConvModel* m, const float* x, float* y, int N, int D, int H, int W, cudaStream_t s, std::string* err);
 // single layer, NCDHW fp32 (the memref ABI of runtime/fortis_rt.c:128-131)
+// networks of 2-D operator layers (NCHW fp32)
+struct OpNet;
+OpNet* opnet_create(const ModelHost& M, std::string* err);
+void opnet_destroy(OpNet* m);
+bool opnet_shape(const ModelHost& M, int H, int W, int* C, int* Ho, int* Wo, long long* max_elems_per_image);
+bool opnet_forward(OpNet* m, const float* x, float* y, int N, int H, int W, cudaStream_t s, std::string* err);
 bool conv3d_ncdhw(const float* x, const float* w, float* y, int N, int C, int D, int H, int W, int F, const int K[3],
                   const int stride[3], const int pad[3], cudaStream_t s, std::string* err);
 

@@ -9,6 +9,11 @@
 //               f32 slope
 //               f32 W[cout * cin * ksize^3]   (torch layout: Linear (out,in); Conv3d (F,C,KD,KH,KW))
 //               f32 b[cout]
+//   2-D operator layers (kind >= 3; NCHW fp32 networks: the operator micro-suite of tests/optest.py) use this record:
+//               u32 kind (3 = Conv2d, 4 = MaxPool2d, 5 = nearest Upsample), cin, cout, kh, kw, sh, sw, ph, pw,
+//               u32 dil (input dilation: a transposed convolution of stride s is the convolution of the s-dilated
+//                   input with the flipped kernel), eh, ew (extra zero rows / columns behind the input: output_padding),
+//               u32 act;  f32 slope;  Conv2d only: f32 W[cout * cin * kh * kw] (F, C, KH, KW), f32 b[cout]
 //   f32 in_div[n_in_div]        input is divided by it      (mom6_zb/export_zb.py:13)
 //   f32 out_mul[n_out_mul]      output is multiplied by it  (mom6_zb/export_zb.py:14)
 //   f32 relu_mask[n_relu_mask]  outputs with mask != 0 get a final ReLU (benchmarks/climsim/export_wide.py:24-27)
@@ -32,12 +37,13 @@
 
 namespace fortis {
 
-enum { LAYER_LINEAR = 1, LAYER_CONV3D = 2 };
+enum { LAYER_LINEAR = 1, LAYER_CONV3D = 2, LAYER_CONV2D = 3, LAYER_MAXPOOL2D = 4, LAYER_UPSAMPLE2D = 5 };
 enum { LFLAG_SAVE_SKIP = 1, LFLAG_ADD_SKIP = 2 };
 
 struct LayerHost {
   int kind = LAYER_LINEAR, cin = 0, cout = 0, ksize = 1, pad = 0, act = 0, flags = 0;
   float slope = 0.f;
+  int kh = 1, kw = 1, sh = 1, sw = 1, ph = 0, pw = 0, dil = 1, eh = 0, ew = 0;      // 2-D operator layers
   std::vector<float> W, b;
 };
 
@@ -58,6 +64,10 @@ struct ModelHost {
   }
   bool is_conv() const {
     for (auto& l : layers) if (l.kind != LAYER_CONV3D) return false;
+    return !layers.empty();
+  }
+  bool is_opnet() const {                 // a network of 2-D operator layers (NCHW)
+    for (auto& l : layers) if (l.kind < LAYER_CONV2D) return false;
     return !layers.empty();
   }
   int n_in() const { return layers.empty() ? 0 : layers.front().cin; }
@@ -85,7 +95,25 @@ inline ModelHost parse_model_blob(const void* data, size_t nbytes) {
   if (nl == 0 || nl > 64) throw std::runtime_error("model blob: layer count out of range");
   for (uint32_t l = 0; l < nl; l++) {
     LayerHost L;
-    L.kind = (int)u32(); L.cin = (int)u32(); L.cout = (int)u32(); L.ksize = (int)u32(); L.pad = (int)u32();
+    L.kind = (int)u32();
+    if (L.kind >= LAYER_CONV2D && L.kind <= LAYER_UPSAMPLE2D) {
+      L.cin = (int)u32(); L.cout = (int)u32(); L.kh = (int)u32(); L.kw = (int)u32(); L.sh = (int)u32(); L.sw = (int)u32();
+      L.ph = (int)u32(); L.pw = (int)u32(); L.dil = (int)u32(); L.eh = (int)u32(); L.ew = (int)u32(); L.act = (int)u32(); L.slope = f32();
+      auto bad = [&](int v, int lo, int hi) { return v < lo || v > hi; };
+      if (bad(L.cin, 1, 1 << 16) || bad(L.cout, 1, 1 << 16) || bad(L.kh, 1, 31) || bad(L.kw, 1, 31) || bad(L.sh, 1, 16) || bad(L.sw, 1, 16) ||
+          bad(L.ph, 0, 64) || bad(L.pw, 0, 64) || bad(L.dil, 1, 16) || bad(L.eh, 0, 16) || bad(L.ew, 0, 16) || bad(L.act, 0, 2))
+        throw std::runtime_error("model blob: bad 2-D layer shape");
+      if (L.kind == LAYER_CONV2D) {
+        floats(L.W, (size_t)L.cout * L.cin * L.kh * L.kw);
+        floats(L.b, (size_t)L.cout);
+      } else if (L.cin != L.cout || L.act != 0) {
+        throw std::runtime_error("model blob: pooling / upsampling layers keep the channel count and have no activation");
+      }
+      if (l && M.layers.back().cout != L.cin) throw std::runtime_error("model blob: layer widths do not chain");
+      M.layers.push_back(std::move(L));
+      continue;
+    }
+    L.cin = (int)u32(); L.cout = (int)u32(); L.ksize = (int)u32(); L.pad = (int)u32();
     L.act = (int)u32(); L.flags = (int)u32(); L.slope = f32();
     if (L.kind != LAYER_LINEAR && L.kind != LAYER_CONV3D) throw std::runtime_error("model blob: unknown layer kind");
     if (L.cin <= 0 || L.cout <= 0 || L.ksize <= 0 || L.ksize > 7) throw std::runtime_error("model blob: bad layer shape");

@@ -8,7 +8,7 @@ import struct
 import numpy as np
 
 _ACT = {"none": 0, "relu": 1, "leaky": 2}
-LINEAR, CONV3D = 1, 2
+LINEAR, CONV3D, CONV2D, MAXPOOL2D, UPSAMPLE2D = 1, 2, 3, 4, 5
 SAVE_SKIP, ADD_SKIP = 1, 2
 
 
@@ -78,6 +78,34 @@ def pack_layer(W, b, last, precision):
     return K, N, np.ascontiguousarray(img).reshape(-1), bias, scale
 
 
+def _pair(v):
+    return (int(v), int(v)) if np.isscalar(v) else (int(v[0]), int(v[1]))
+
+
+def _op2d_record(L) -> bytes:
+    """One 2-D operator layer (NCHW networks): dict(op='conv2d', W (F,C,KH,KW), b, stride, pad, dil (input dilation),
+    extra (zero rows / columns behind the input), act, slope) | dict(op='maxpool2d', channels, k, stride) |
+    dict(op='upsample2d', channels, scale)."""
+    op = L["op"]
+    if op == "conv2d":
+        W = np.ascontiguousarray(L["W"], dtype=np.float32)
+        if W.ndim != 4:
+            raise ValueError("conv2d weights are (F, C, KH, KW)")
+        cout, cin, kh, kw = W.shape
+        b = np.ascontiguousarray(L["b"] if L.get("b") is not None else np.zeros(cout), dtype=np.float32)
+        (sh, sw), (ph, pw), (eh, ew) = _pair(L.get("stride", 1)), _pair(L.get("pad", 0)), _pair(L.get("extra", 0))
+        head = struct.pack("<13If", CONV2D, cin, cout, kh, kw, sh, sw, ph, pw, int(L.get("dil", 1)), eh, ew,
+                           _ACT[L.get("act", "none")], float(L.get("slope", 0.0)))
+        return head + W.tobytes() + b.tobytes()
+    c = int(L["channels"])
+    if op == "maxpool2d":
+        (kh, kw) = _pair(L["k"])
+        (sh, sw) = _pair(L.get("stride", L["k"]))
+        return struct.pack("<13If", MAXPOOL2D, c, c, kh, kw, sh, sw, 0, 0, 1, 0, 0, 0, 0.0)
+    (fh, fw) = _pair(L["scale"])
+    return struct.pack("<13If", UPSAMPLE2D, c, c, 1, 1, fh, fw, 0, 0, 1, 0, 0, 0, 0.0)
+
+
 def write_blob(layers, in_div=None, out_mul=None, relu_mask=None, prepack=None) -> bytes:
     """layers: dicts with W ((out,in) or (F,C,K,K,K)), b, act ('none'|'relu'|'leaky'), slope, and for conv layers
     pad, save (remember output as skip), add (add skip before the activation).  prepack = 'bf16' | 'fp16' | 'fp8w'
@@ -88,6 +116,9 @@ def write_blob(layers, in_div=None, out_mul=None, relu_mask=None, prepack=None) 
     ind, outm, rm = vec(in_div), vec(out_mul), vec(relu_mask)
     out = [b"FORTISM1", struct.pack("<4I", len(layers), ind.size, outm.size, rm.size)]
     for L in layers:
+        if L.get("op") in ("conv2d", "maxpool2d", "upsample2d"):
+            out.append(_op2d_record(L))
+            continue
         W = np.ascontiguousarray(L["W"], dtype=np.float32)
         kind = CONV3D if W.ndim == 5 else LINEAR
         cout, cin = W.shape[0], W.shape[1]
@@ -104,7 +135,7 @@ def write_blob(layers, in_div=None, out_mul=None, relu_mask=None, prepack=None) 
         return base
     if prepack not in PRECISIONS:
         raise ValueError("prepack must be one of %s" % sorted(PRECISIONS))
-    if any(np.asarray(L["W"]).ndim != 2 for L in layers):
+    if any(L.get("op") or np.asarray(L["W"]).ndim != 2 for L in layers):
         raise ValueError("only MLP models carry a pre-packed section")
     sec = [b"FORTISP1", struct.pack("<2I", PRECISIONS[prepack], len(layers)), struct.pack("<Q", fnv1a64(base))]
     for l, L in enumerate(layers):

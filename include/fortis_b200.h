@@ -135,7 +135,8 @@ int fortis_load_model_mem(const void* blob, long nbytes);
  *   "host_access" "copy" (default: host arrays are staged by copies; column layouts in chunks, uploads, kernels and
  *                 downloads overlapped) | "mapped_out" (kernels store into the pinned host pages) | "mapped" (they
  *                 load from them as well); also FORTIS_HOST_ACCESS
- *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model
+ *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model (NDHWC arrays); "N,1,H,W" for a network of 2-D operator
+ *                 layers (Conv2d / transposed / pooling / upsampling; NCHW arrays in and out of mlp_forward)
  * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits (fortis_b200_test.h). */
 int fortis_set_option(const char* key, const char* value);
 /* drop every descriptor, model, buffer registration and captured graph (device pool buffers stay pooled) */

@@ -527,6 +527,104 @@ def conv_ncdhw(x: np.ndarray, W: np.ndarray, stride=(1, 1, 1), pad=(0, 0, 0), dt
     return y
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# 2-D operators of the reference's micro-suite (tests/optest.py:6-32), NCHW, each by its definition
+# ---------------------------------------------------------------------------------------------------------------
+def conv2d_nchw(x, W, b=None, stride=(1, 1), pad=(0, 0), dil=1, extra=(0, 0), dtype=np.float64):
+    """Cross-correlation (runtime/fortis_rt.c:108-127) of the input dilated by `dil` (zeros between samples), zero-padded
+    by `pad` on both sides and by `extra` more rows / columns behind."""
+    x = np.asarray(x, dtype=dtype)
+    N, C, H, Wd = x.shape
+    xd = np.zeros((N, C, (H - 1) * dil + 1, (Wd - 1) * dil + 1), dtype=dtype)
+    xd[:, :, ::dil, ::dil] = x
+    xd = np.pad(xd, ((0, 0), (0, 0), (pad[0], pad[0] + extra[0]), (pad[1], pad[1] + extra[1])))
+    y = conv_ncdhw(xd[:, :, None], np.asarray(W, dtype=dtype)[:, :, None], stride=(1, stride[0], stride[1]), dtype=dtype)[:, :, 0]
+    return y if b is None else y + np.asarray(b, dtype=dtype)[None, :, None, None]
+
+
+def conv_transpose2d(x, W, b=None, stride=1, pad=(0, 0), opad=(0, 0), dtype=np.float64):
+    """Transposed convolution by its definition: every input sample adds its value times the kernel into the output
+    at stride * position - pad.  W is (Cin, Cout, KH, KW)."""
+    x, W = np.asarray(x, dtype=dtype), np.asarray(W, dtype=dtype)
+    N, C, H, Wd = x.shape
+    _, F, KH, KW = W.shape
+    Ho, Wo = (H - 1) * stride - 2 * pad[0] + KH + opad[0], (Wd - 1) * stride - 2 * pad[1] + KW + opad[1]
+    full = np.zeros((N, F, (H - 1) * stride + KH + opad[0], (Wd - 1) * stride + KW + opad[1]), dtype=dtype)
+    for kh in range(KH):
+        for kw in range(KW):
+            full[:, :, kh:kh + (H - 1) * stride + 1:stride, kw:kw + (Wd - 1) * stride + 1:stride] += np.einsum("nchw,cf->nfhw", x, W[:, :, kh, kw])
+    y = full[:, :, pad[0]:pad[0] + Ho, pad[1]:pad[1] + Wo]
+    return y if b is None else y + np.asarray(b, dtype=dtype)[None, :, None, None]
+
+
+def maxpool2d(x, k, stride=None):
+    k = (k, k) if np.isscalar(k) else k
+    stride = k if stride is None else ((stride, stride) if np.isscalar(stride) else stride)
+    N, C, H, Wd = x.shape
+    Ho, Wo = (H - k[0]) // stride[0] + 1, (Wd - k[1]) // stride[1] + 1
+    y = np.full((N, C, Ho, Wo), -np.inf, dtype=x.dtype)
+    for i in range(k[0]):
+        for j in range(k[1]):
+            y = np.maximum(y, x[:, :, i:i + (Ho - 1) * stride[0] + 1:stride[0], j:j + (Wo - 1) * stride[1] + 1:stride[1]])
+    return y
+
+
+def upsample_nearest2d(x, scale):
+    scale = (scale, scale) if np.isscalar(scale) else scale
+    return np.repeat(np.repeat(x, scale[0], axis=2), scale[1], axis=3)
+
+
+def batchnorm2d(x, gamma, beta, mean, var, eps):
+    sh = (1, -1, 1, 1)
+    return (x - np.reshape(mean, sh)) / np.sqrt(np.reshape(var, sh) + eps) * np.reshape(gamma, sh) + np.reshape(beta, sh)
+
+
+def ops2d_forward(spec, x, dtype=np.float64):
+    """A 2-D network given op by op, unfused: ('conv', W, b, stride, pad) | ('convT', W, b, stride, pad, opad) |
+    ('bn', gamma, beta, mean, var, eps) | ('relu',) | ('leaky', slope) | ('maxpool', k) | ('upsample', scale) |
+    ('pad', p) | ('cat', [spec, spec, ...]) (channel concatenation of sub-networks applied to the same input)."""
+    h = np.asarray(x, dtype=dtype)
+    for op in spec:
+        kind = op[0]
+        if kind == "conv":
+            h = conv2d_nchw(h, op[1], op[2], stride=op[3], pad=op[4], dtype=dtype)
+        elif kind == "convT":
+            h = conv_transpose2d(h, op[1], op[2], stride=op[3], pad=op[4], opad=op[5], dtype=dtype)
+        elif kind == "bn":
+            h = batchnorm2d(h, *op[1:])
+        elif kind == "relu":
+            h = np.maximum(h, 0)
+        elif kind == "leaky":
+            h = np.where(h > 0, h, h * op[1])
+        elif kind == "maxpool":
+            h = maxpool2d(h, op[1])
+        elif kind == "upsample":
+            h = upsample_nearest2d(h, op[1])
+        elif kind == "pad":
+            h = np.pad(h, ((0, 0), (0, 0), (op[1], op[1]), (op[1], op[1])))
+        elif kind == "cat":
+            h = np.concatenate([ops2d_forward(sub, h, dtype) for sub in op[1]], axis=1)
+        else:
+            raise ValueError(kind)
+    return h
+
+
+def opnet_forward(layers, x, dtype=np.float32):
+    """The exported form of such a network (fortis_b200.model.write_blob layer dicts: conv2d with folded BatchNorm /
+    padding / concatenation and dilated-input transposed convolutions, maxpool2d, upsample2d), layer by layer."""
+    h = np.asarray(x, dtype=dtype)
+    for L in layers:
+        if L["op"] == "conv2d":
+            h = conv2d_nchw(h, L["W"], L["b"], stride=L.get("stride", (1, 1)), pad=L.get("pad", (0, 0)), dil=L.get("dil", 1),
+                            extra=L.get("extra", (0, 0)), dtype=dtype)
+            h = act_apply(h, L.get("act", "none"), L.get("slope", 0.0)).astype(dtype)
+        elif L["op"] == "maxpool2d":
+            h = maxpool2d(h, L["k"], L.get("stride"))
+        else:
+            h = upsample_nearest2d(h, L["scale"])
+    return h
+
+
 def convnet_forward(layers: Sequence[Dict], x: np.ndarray, dtype=np.float32) -> np.ndarray:
     """Sequence of conv3d layers with fused activation and optional residual.  Each layer dict: W, b, act,
     slope, and `save` (remember this layer's output as the skip) / `add` (add the remembered skip after the conv,

@@ -159,3 +159,35 @@ def test_prepacked_blob_matches_the_loaders_own_packing_and_is_hash_checked():
     assert load(other + packed[len(plain):]) == -1 and b"does not belong" in L.fortis_last_error_message()
     assert load(plain + b"junkjunk") == -1
     L.fortis_reset()
+
+
+def test_2d_operator_networks_oracle_and_exporter_against_torch_vectors(golden_dir):
+    """The operator types of the reference's micro-suite as 2-D networks (tests/golden/opnet_models.py): the oracle's
+    unfused definitions must reproduce torch's outputs, and so must the EXPORTED form interpreted by the oracle: that
+    checks the exporter's algebra (BatchNorm, padding and concatenation folded into weights, transposed convolutions
+    as convolutions of the dilated input).  The blobs must load."""
+    import ctypes
+    import fortis_b200
+    from fortis_b200 import export as E
+    from fortis_b200 import model as M
+    from oracle import fortis_oracle as fo
+    from tests.golden import opnet_models as OM
+    Z = np.load(os.path.join(golden_dir, "opnet_golden.npz"))
+    L = fortis_b200.load()
+    for name in OM.NAMES:
+        m, spec, x = OM.build(name)
+        want = Z[name + "_y"]
+        assert fo.rel_l2(fo.ops2d_forward(spec, x), want) < 1e-6, name
+        layers = E.layers2d_from_torch(m)
+        got = fo.opnet_forward(layers, x, dtype=np.float64)
+        assert got.shape == want.shape and fo.rel_l2(got, want) < 1e-6, name
+        blob = M.write_blob(layers)
+        assert L.fortis_load_model_mem(ctypes.c_char_p(blob), len(blob)) == 0, L.fortis_last_error_message()
+    L.fortis_reset()
+    # what has no kernel is refused by the exporter, not dropped
+    import torch.nn as nn
+    for bad in (nn.Sequential(nn.Conv2d(1, 2, 3, dilation=2)), nn.Sequential(nn.Conv2d(1, 2, 3), nn.MaxPool2d(2, padding=1)),
+                nn.Sequential(nn.Conv2d(1, 2, 3), nn.Upsample(scale_factor=2, mode="bilinear")), nn.Sequential(nn.ZeroPad2d(1), nn.MaxPool2d(2)),
+                nn.Sequential(nn.Conv2d(1, 2, 3), nn.Sigmoid())):
+        with pytest.raises(ValueError):
+            E.layers2d_from_torch(bad.eval(), in_channels=1)

@@ -229,3 +229,36 @@ def test_single_conv_layers_any_kernel_stride_padding(host, golden_dir):
     c3(*_memref(xs), *_memref(w), *_memref(y2), 1, 2, 8, 8, 8, 3, 5, 5, 5, 4, 4, 4, 1, 1, 1, 0, 0, 0)
     host.sync()
     assert float(y.min()) == -7.0 == float(y.max()) and float(y2.min()) == -7.0 == float(y2.max())
+
+
+def test_2d_operator_networks_through_the_whole_array_entry(host, golden_dir):
+    """Conv2d chains, pooling, nearest upsampling, transposed convolutions (stride 1 and 2), BatchNorm (inference),
+    concatenated parallel convolutions and explicit padding, exported from torch modules and run through mlp_forward on
+    NCHW arrays: <= 1e-5 against torch-made vectors and against the oracle's interpretation of the exported layers."""
+    from fortis_b200 import export as E
+    from tests.golden import opnet_models as OM
+    Z = np.load(os.path.join(golden_dir, "opnet_golden.npz"))
+    for name in OM.NAMES:
+        m, _, x = OM.build(name)
+        want = Z[name + "_y"]
+        layers = E.layers2d_from_torch(m)
+        host.reset()
+        host.load_model(fortis_b200.write_blob(layers))
+        N, C, H, W = x.shape
+        host.option("conv_shape", "%d,1,%d,%d" % (N, H, W))
+        y = np.full(want.shape, np.nan, np.float32)
+        host.forward(np.ascontiguousarray(x), y)
+        assert fo.rel_l2(y, want) <= 1e-5, (name, fo.rel_l2(y, want))
+        assert fo.rel_l2(y, fo.opnet_forward(layers, x)) <= 1e-5, name
+        # device-resident in and out, twice (the second call reuses every buffer)
+        dx, dy = torch.from_numpy(x).cuda(), torch.full(want.shape, float("nan"), device="cuda")
+        for _ in range(2):
+            host.forward(dx, dy)
+            host.sync()
+            assert np.array_equal(dy.cpu().numpy(), y), name
+    host.reset()
+    host.load_model(fortis_b200.write_blob(E.layers2d_from_torch(OM.build("pool")[0])))
+    host.option("conv_shape", "2,1,12,10")
+    with pytest.raises(fortis_b200.FortisError):
+        host.option("precision", "bf16")
+        host.forward(np.zeros((2, 2, 12, 10), np.float32), np.zeros((2, 5, 6, 5), np.float32))
