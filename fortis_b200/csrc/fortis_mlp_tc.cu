@@ -50,7 +50,10 @@ namespace {
 constexpr int kTileM = 128;
 constexpr int kChunkN = 64;                 // output features per accumulator
 constexpr int kBlockK = 256;                // K-block: granularity of the layer hand-off and of the padding of K
-constexpr int kStageK = kBlockK;            // k extent of one weight stage: four 64-wide swizzled sub-tiles, ONE TMA per stage
+#ifndef FORTIS_TC_STAGE_K
+#define FORTIS_TC_STAGE_K 256
+#endif
+constexpr int kStageK = FORTIS_TC_STAGE_K;  // k extent of one weight stage (256 or 128): 64-wide swizzled sub-tiles, ONE copy per stage
 constexpr int kSubStages = kBlockK / kStageK;        // stages per K-block (halving the stage to 16 KB was measured: no gain)
 constexpr int kStageBytes = kChunkN * kStageK * 2;   // 32 KB
 constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 KB
