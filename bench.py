@@ -50,6 +50,7 @@ def parse():
     ap.add_argument("--sharded", action="store_true", help="run the sharded-configuration block also on one GPU")
     ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--trace-e2e", action="store_true", help="print the device timeline (copies and kernels) of one host-array step to stderr")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-incumbent", action="store_true")
     return ap.parse_args()
@@ -437,6 +438,19 @@ class Bench:
         up, down, both = ms(lambda: pipe(True, False, 1)), ms(lambda: pipe(False, True, 1)), ms(lambda: pipe(True, True, chunks))
         return {"h2d_ms": up, "h2d_gbs": nin / up / 1e6, "d2h_ms": down, "d2h_gbs": nout / down / 1e6, "pipelined_ms": both, "chunks": chunks}
 
+    def trace(self, fn):
+        """Device timeline of one call of `fn` (start and duration of every copy and kernel, microseconds), to stderr."""
+        from torch.profiler import ProfilerActivity, profile
+        torch = self.torch
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda e: e.time_range.start)
+        t0 = evs[0].time_range.start if evs else 0
+        for e in evs:
+            sys.stderr.write("%9.1f %8.1f us  %s\n" % (e.time_range.start - t0, e.time_range.end - e.time_range.start, e.name[:70]))
+
     def gather_floats(self, v):
         """Every rank's value of `v` (list of floats) on every rank."""
         if self.dist is None:
@@ -590,6 +604,8 @@ class Bench:
             e_total, _ = self.timed(e_fn, e_steps, 3, device_only=False)
             e2e = {"value": units * e_steps / (e_total * 1e-3), "unit": "columns/s",
                    "h2d_bytes_per_step": int(sum(a.nbytes for a in wl["gin"])), "d2h_bytes_per_step": int(sum(a.nbytes for a in wl["sout"]))}
+            if args.trace_e2e and rank == 0:
+                self.trace(e_fn)
             e2e["ms_per_step"] = e_total / e_steps
             e2e["link"] = self.link_floor(e2e["h2d_bytes_per_step"], e2e["d2h_bytes_per_step"])
             e2e["frac_of_link"] = e2e["link"]["pipelined_ms"] / e2e["ms_per_step"]

@@ -942,6 +942,8 @@ void do_forward_batched(void* in, void* out) {
     s.pack_pending = false;
     return;
   }
+  // a run-time extent of zero (driver/fortis_stub.c: fortis_begin(0), a loop that packs nothing): nothing to do
+  if (s.begin_count == 0 && !in && !out) return;
   // array form  (driver/fortis_shim.py:117-121)
   if (!in || !out) throw std::runtime_error("mlp_forward_batched: no gather or pack is pending and no arrays were given");
   if (is_device_ptr(in)) cuda_ok(cudaMemcpyAsync(s.din, in, rows * nin * 4, cudaMemcpyDeviceToDevice, st), "D2D of the input");

@@ -8,8 +8,8 @@
 // cuFFT convolution for large kernels (runtime/fortis_fft.cu:15-79); a 2-D convolution is the D = KD = 1 case.
 //
 // GEMM view: rows = output voxels (n, d, h, w), columns = output channels, reduction = taps x input channels.
-// A block owns 64 voxels x 64 channels; per (tap, 16 input channels) slice the activations (gathered with the
-// padding applied) and the weights are staged in shared memory; each of the 256 threads accumulates 4 x 4 outputs.
+// A block owns 128 voxels x 64 channels; per (tap, 16 input channels) slice the activations (gathered with the
+// padding applied) and the weights are staged in shared memory; each of the 256 threads accumulates 8 x 4 outputs.
 // Element strides of x and y are parameters, so the same kernel serves NDHWC networks and the NCDHW single-layer
 // entry of the memref ABI.
 #include <cuda_runtime.h>
@@ -34,19 +34,23 @@ struct ConvGeom {
   long long ys_n, ys_d, ys_h, ys_w, ys_c;     // element strides of y (and of the residual)
 };
 
-constexpr int CBM = 64, CBN = 64, CBK = 16;
+constexpr int CBM = 128, CBN = 64, CBK = 16;
 
+// Tile 128 voxels x 64 channels per block of 256 threads, 8 x 4 outputs per thread.  The reduction runs over slices of
+// (one tap, 16 input channels); the next slice's global loads are issued into registers before the current slice is
+// multiplied out of shared memory (double-buffered: one barrier per slice).  Per k step a thread reads three 16-byte
+// words from shared memory for 32 FMAs.
 __global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict__ x, const float* __restrict__ wt,   // wt [tap][C][F]
                                                          const float* __restrict__ bias, const float* __restrict__ residual,
                                                          float* __restrict__ y, ConvGeom g, int act, float slope) {
-  __shared__ float As[CBK][CBM + 4];
-  __shared__ float Ws[CBK][CBN + 4];
+  __shared__ __align__(16) float As[2][CBK][CBM + 4];
+  __shared__ __align__(16) float Ws[2][CBK][CBN + 4];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const long long nvox = (long long)g.N * g.Do * g.Ho * g.Wo;
   const long long m0 = (long long)blockIdx.x * CBM;
   const int f0 = blockIdx.y * CBN;
-  // the voxel this thread loads for the A tile (one voxel, 4 input channels per slice)
-  const int lv = tid & 63, lc = (tid >> 6) * 4;
+  // A tile: this thread loads one voxel, 8 input channels per slice
+  const int lv = tid & 127, lc = (tid >> 7) * 8;
   const long long vox = m0 + lv;
   int on = 0, od = 0, oh = 0, ow = 0;
   const bool vlive = vox < nvox;
@@ -56,13 +60,23 @@ __global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict
     oh = (int)(t % g.Ho); t /= g.Ho;
     od = (int)(t % g.Do); on = (int)(t / g.Do);
   }
-  float acc[4][4];
+  // W tile: 16 input-channel rows x 64 output channels, 4 consecutive output channels per thread
+  const int wr = tid >> 4, wc = (tid & 15) * 4;
+  const bool wvec = (g.F & 3) == 0 && f0 + wc + 3 < g.F;
+  // channels-last input whose every (voxel, 16-channel block) starts on a 16-byte boundary: vector loads
+  const bool avec = g.xs_c == 1 && (g.C % CBK) == 0 && ((g.xs_w | g.xs_h | g.xs_d | g.xs_n) & 3) == 0 &&
+                    (reinterpret_cast<unsigned long long>(x) & 15ull) == 0;
+
+  float acc[8][4];
 #pragma unroll
-  for (int i = 0; i < 4; i++)
+  for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-  const int ntaps = g.KD * g.KH * g.KW;
-  for (int tap = 0; tap < ntaps; tap++) {
+
+  const int ntaps = g.KD * g.KH * g.KW, cblocks = (g.C + CBK - 1) / CBK, nslices = ntaps * cblocks;
+  float pa[8], pw[4];
+  auto fetch = [&](int slice) {
+    const int tap = slice / cblocks, c0 = (slice - tap * cblocks) * CBK;
     const int kd = tap / (g.KH * g.KW), kh = (tap / g.KW) % g.KH, kw = tap % g.KW;
     int id = od * g.sd + kd - g.pd, ih = oh * g.sh + kh - g.ph, iw = ow * g.sw + kw - g.pw;
     bool inb = vlive && id >= 0 && ih >= 0 && iw >= 0;
@@ -71,38 +85,58 @@ __global__ void __launch_bounds__(256) conv3d_f32_kernel(const float* __restrict
     if (g.dw > 1) { inb = inb && iw % g.dw == 0; iw /= g.dw; }
     inb = inb && id < g.D && ih < g.H && iw < g.W;
     const float* xp = x + (long long)on * g.xs_n + (long long)id * g.xs_d + (long long)ih * g.xs_h + (long long)iw * g.xs_w;
-    for (int c0 = 0; c0 < g.C; c0 += CBK) {
+    if (avec) {                                                // channels-last: the thread's 8 channels are 32 contiguous bytes
+      float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
+      if (inb) {
+        q0 = __ldg(reinterpret_cast<const float4*>(xp + c0 + lc));
+        q1 = __ldg(reinterpret_cast<const float4*>(xp + c0 + lc) + 1);
+      }
+      pa[0] = q0.x; pa[1] = q0.y; pa[2] = q0.z; pa[3] = q0.w; pa[4] = q1.x; pa[5] = q1.y; pa[6] = q1.z; pa[7] = q1.w;
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
+      for (int e = 0; e < 8; e++) {
         const int c = c0 + lc + e;
-        As[lc + e][lv] = (inb && c < g.C) ? __ldg(xp + (long long)c * g.xs_c) : 0.f;
+        pa[e] = (inb && c < g.C) ? __ldg(xp + (long long)c * g.xs_c) : 0.f;
       }
-      {
-        const int wr = tid >> 4, wc = (tid & 15) * 4;       // 16 cin rows x 64 couts, 4 couts per thread
-        const int c = c0 + wr;
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          const int f = f0 + wc + e;
-          Ws[wr][wc + e] = (c < g.C && f < g.F) ? __ldg(wt + ((long long)tap * g.C + c) * g.F + f) : 0.f;
-        }
-      }
-      __syncthreads();
-#pragma unroll
-      for (int k = 0; k < CBK; k++) {
-        const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
-        const float4 w = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
-        const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-#pragma unroll
-          for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
-      }
-      __syncthreads();
     }
+    const int c = c0 + wr;
+    const float* wp = wt + ((long long)tap * g.C + c) * g.F + f0 + wc;
+    if (c < g.C && wvec) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(wp));
+      pw[0] = q.x; pw[1] = q.y; pw[2] = q.z; pw[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; e++) pw[e] = (c < g.C && f0 + wc + e < g.F) ? __ldg(wp + e) : 0.f;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int e = 0; e < 8; e++) As[buf][lc + e][lv] = pa[e];
+    *reinterpret_cast<float4*>(&Ws[buf][wr][wc]) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  for (int slice = 0; slice < nslices; slice++) {
+    const int buf = slice & 1;
+    if (slice + 1 < nslices) fetch(slice + 1);                 // in flight while this slice is multiplied
+#pragma unroll
+    for (int k = 0; k < CBK; k++) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 8 + 4]);
+      const float4 w = *reinterpret_cast<const float4*>(&Ws[buf][k][tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    if (slice + 1 < nslices) stash(buf ^ 1);                   // the other buffer was last read before the previous barrier
+    __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const long long v = m0 + ty * 4 + i;
+  for (int i = 0; i < 8; i++) {
+    const long long v = m0 + ty * 8 + i;
     if (v >= nvox) continue;
     long long t = v;
     const int w_ = (int)(t % g.Wo); t /= g.Wo;

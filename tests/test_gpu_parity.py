@@ -539,3 +539,29 @@ def test_reference_runtime_gemm_agrees(host):
         torch.cuda.synchronize()
         host.sync()
         assert fo.rel_l2(C1.cpu().numpy(), C0.cpu().numpy()) < 2e-6
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_empty_and_single_row_batches(host, precision):
+    """A run-time extent of zero (a rank that owns no columns, an empty loop) is a step that does nothing and reports
+    nothing; the next non-empty extent works, down to one row."""
+    layers = fortis_b200.mlp_layers([12, 40, 7], seed=3, act="leaky", slope=0.15)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", precision)
+    host.L.fortis_begin(0)
+    host.forward_batched()
+    host.check()
+    assert host.L.fortis_device_status() == 0
+    rng = np.random.default_rng(5)
+    for count in (1, 0, 3):
+        host.L.fortis_begin(count)
+        X = rng.normal(size=(max(count, 1), 12)).astype(np.float32)
+        for c in range(count):
+            host.L.fortis_pack(X[c].ctypes.data, c)
+        host.forward_batched()
+        Y = np.zeros((max(count, 1), 7), np.float32)
+        for c in range(count):
+            host.L.fortis_unpack(Y[c].ctypes.data, c)
+        host.check()
+        if count:
+            assert fo.rel_l2(Y[:count], fo.mlp_forward(layers, X[:count])) < (FP32_TOL if precision == "fp32" else 5e-3)
