@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfortis_b200.so")
-SOURCES = ["fortis_plan.cpp", "fortis_kernels.cu", "fortis_stencil_mlp.cu", "fortis_mlp_tc.cu", "fortis_mlp_f32tc.cu", "fortis_conv3d.cu", "fortis_conv3d_tc.cu", "fortis_noalloc.cu", "fortis_api.cu"]
+SOURCES = ["fortis_plan.cpp", "fortis_kernels.cu", "fortis_stencil_mlp.cu", "fortis_stencil_tc.cu", "fortis_mlp_tc.cu", "fortis_mlp_f32tc.cu", "fortis_conv3d.cu", "fortis_conv3d_tc.cu", "fortis_noalloc.cu", "fortis_api.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-Wall", "-x", "cu"]
 

@@ -142,6 +142,8 @@ struct Session {
   F32TcModel* f32 = nullptr;                   // fp32 precision on the tensor cores (split TF32), large batches
   ConvModel* conv = nullptr;
   OpNet* opnet = nullptr;
+  StencilTcModel* stencil_tc = nullptr;
+  bool use_stencil_tc = false;                // option "stencil_tc" / FORTIS_STENCIL_TC
   int conv_shape[4] = {0, 0, 0, 0};
 
   int precision = PREC_F32;
@@ -177,6 +179,7 @@ Session& S() {
     g_S = new Session();
     // option environment variables apply however the descriptors and the model arrive
     if (std::getenv("FORTIS_GRAPH")) g_S->graph = true;                              // driver/fortis_shim.py:84
+    if (std::getenv("FORTIS_STENCIL_TC")) g_S->use_stencil_tc = true;
     if (const char* m = std::getenv("FORTIS_HOST_ACCESS")) {
       const std::string v(m);
       g_S->host_access = v == "mapped" ? 2 : v == "mapped_out" ? 1 : 0;
@@ -223,6 +226,7 @@ void free_model_dev() {
   if (s.f32) { f32tc_destroy(s.f32); s.f32 = nullptr; }
   if (s.conv) { conv_model_destroy(s.conv); s.conv = nullptr; }
   if (s.opnet) { opnet_destroy(s.opnet); s.opnet = nullptr; }
+  if (s.stencil_tc) { stencil_tc_destroy(s.stencil_tc); s.stencil_tc = nullptr; }
   s.model_on_dev = false;
   s.small_ok = false; s.stencil_ok = false;
 }
@@ -362,6 +366,13 @@ void ensure_model() {
       if (cuda_ok(stencil_mlp_upload(nl, dims.data(), W.data(), B.data(), s.model.in_div.empty() ? nullptr : s.model.in_div.data(),
                                      s.model.out_mul.empty() ? nullptr : s.model.out_mul.data(), st), "stencil-MLP constant upload"))
         s.stencil_ok = true;
+    }
+    // the tensor-core form of the same step: an option (measured slower than the packed-FMA kernel for nets this narrow)
+    if (s.precision == PREC_F32 && stencil_tc_supported(nl, dims.data()) && s.model.relu_mask.empty()) {
+      std::vector<const float*> W, B;
+      for (auto& L : s.model.layers) { W.push_back(L.W.data()); B.push_back(L.b.data()); }
+      s.stencil_tc = stencil_tc_create(nl, dims.data(), W.data(), B.data(), s.model.in_div.empty() ? nullptr : s.model.in_div.data(),
+                                       s.model.out_mul.empty() ? nullptr : s.model.out_mul.data());
     }
     if (s.precision == PREC_F32) {
       std::string err;
@@ -741,7 +752,7 @@ void run_step_kernels(const StepArgs& A) {
     if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);
     return;
   }
-  if (fused_gather && A.fuse_scatter && s.stencil_ok) {
+  if (fused_gather && A.fuse_scatter && (s.stencil_ok || (s.use_stencil_tc && s.stencil_tc))) {
     StencilLaunch SL;
     if (stencil_operands(A, g, &SL)) {
       std::vector<int> dims{s.model.n_in()};
@@ -753,8 +764,11 @@ void run_step_kernels(const StepArgs& A) {
         if (l < nl - 1 && L.act != ACT_RELU) relu_only = false;
       }
       SL.has_in_div = !s.model.in_div.empty(); SL.has_out_mul = !s.model.out_mul.empty();
-      if (s.want_checksum) { ensure_aux(stencil_mlp_grid(SL)); SL.partials = s.d_partials; SL.sum = s.d_sum; SL.done = s.d_done; }
-      if (launch_stencil_mlp(nl, dims.data(), relu_only, SL, st)) return;
+      const int gmax = stencil_mlp_grid(SL) > stencil_tc_grid(SL) ? stencil_mlp_grid(SL) : stencil_tc_grid(SL);
+      ensure_aux(s.want_checksum ? gmax : 1);
+      if (s.want_checksum) { SL.partials = s.d_partials; SL.sum = s.d_sum; SL.done = s.d_done; }
+      if (s.use_stencil_tc && s.stencil_tc && launch_stencil_tc(s.stencil_tc, SL, s.d_status, st)) return;
+      if (s.stencil_ok && launch_stencil_mlp(nl, dims.data(), relu_only, SL, st)) return;
     }
   }
   if (fused_gather && s.small_ok) {
@@ -1298,6 +1312,7 @@ int fortis_set_option(const char* key, const char* value) {
   } else if (k == "fuse") { s.fuse = v != "0"; drop_graph(); }
   else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
   else if (k == "async") { s.async = v != "0"; }
+  else if (k == "stencil_tc") { s.use_stencil_tc = v != "0"; drop_graph(); }
   else if (k == "host_access") {
     if (v == "copy") s.host_access = 0;
     else if (v == "mapped_out") s.host_access = 1;

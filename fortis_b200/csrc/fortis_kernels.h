@@ -69,6 +69,15 @@ cudaError_t stencil_mlp_upload(int nlayers, const int* dims, const float* const*
 int stencil_mlp_grid(const StencilLaunch& S);
 bool launch_stencil_mlp(int nlayers, const int* dims, bool relu_only, const StencilLaunch& S, cudaStream_t st);
 
+// the same step on the tensor cores (fortis_stencil_tc.cu): three TF32 MMAs per product, rows in tensor memory
+struct StencilTcModel;
+bool stencil_tc_supported(int nlayers, const int* dims);      // 27 inputs, hidden widths <= 32, <= 4 outputs
+StencilTcModel* stencil_tc_create(int nlayers, const int* dims, const float* const* W, const float* const* b, const float* in_div,
+                                  const float* out_mul);
+void stencil_tc_destroy(StencilTcModel* m);
+int stencil_tc_grid(const StencilLaunch& S);
+bool launch_stencil_tc(StencilTcModel* m, const StencilLaunch& S, int* status, cudaStream_t st);
+
 // Test knobs of the tensor-core kernels (set through fortis_set_option "test_wait_limit" / "test_skip_stage"; both 0
 // in normal operation): a short poll limit for the bounded barrier waits, and "the first CTA's TMA warp does not load
 // its first stage", which makes a wait run out so that the give-up path can be exercised without hanging anything.

@@ -135,6 +135,8 @@ int fortis_load_model_mem(const void* blob, long nbytes);
  *   "host_access" "copy" (default: host arrays are staged by copies; column layouts in chunks, uploads, kernels and
  *                 downloads overlapped) | "mapped_out" (kernels store into the pinned host pages) | "mapped" (they
  *                 load from them as well); also FORTIS_HOST_ACCESS
+ *   "stencil_tc"  "0" | "1"   3x3-stencil hosts with narrow MLPs: run the layers as TF32x3 tensor-core products instead
+ *                 of packed FMAs (same <= 1e-5; measured slower for 27-20-20-3, default 0); also FORTIS_STENCIL_TC
  *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model (NDHWC arrays); "N,1,H,W" for a network of 2-D operator
  *                 layers (Conv2d / transposed / pooling / upsampling; NCHW arrays in and out of mlp_forward)
  * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits (fortis_b200_test.h). */

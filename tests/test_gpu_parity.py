@@ -565,3 +565,31 @@ def test_empty_and_single_row_batches(host, precision):
         host.check()
         if count:
             assert fo.rel_l2(Y[:count], fo.mlp_forward(layers, X[:count])) < (FP32_TOL if precision == "fp32" else 5e-3)
+
+
+@pytest.mark.parametrize("dims", [[27, 20, 20, 3], [27, 32, 4], [27, 9, 17, 1]])
+def test_stencil_step_on_tensor_cores_option(host, dims):
+    """Option stencil_tc: the 3x3-stencil step with its layers as TF32x3 tensor-core products (rows in tensor memory,
+    thread = gridpoint end to end).  Same bar as the packed-FMA kernel (<= 1e-5 against the oracle), ragged extents,
+    hidden widths that differ, checksum folded in the launch."""
+    nx, ny, nz = 70, 37, 3
+    G, S, Lp, K = fo.stencil_descriptors(nx, ny, nz, nout=dims[-1])
+    rng = np.random.default_rng(11)
+    gin = [np.asfortranarray(rng.normal(size=(nx + 2, ny + 2, nz)).astype(np.float32)) for _ in range(3)]
+    layers = fortis_b200.mlp_layers(dims, seed=4, init="uniform", act="relu", bias="uniform")
+    ref = [np.zeros((nx + 2, ny + 2, nz), np.float32, order="F") for _ in range(dims[-1])]
+    fo.full_step(G, S, Lp, K, layers, gin, ref)
+    host.configure(gather=G, scatter=S, loop=Lp, kdist=K)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("stencil_tc", 1)
+    host.option("checksum", 1)
+    d_in = [torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda() for a in gin]
+    d_out = [torch.zeros(a.size, dtype=torch.float32, device="cuda") for a in ref]
+    host.step_checksum()
+    host.step(d_in, d_out)
+    host.sync()
+    assert host.L.fortis_device_status() == 0
+    got = np.concatenate([t.cpu().numpy() for t in d_out])
+    want = np.concatenate([a.reshape(-1, order="F") for a in ref])
+    assert fo.rel_l2(got, want) <= FP32_TOL
+    assert abs(host.step_checksum() - float(got.astype(np.float64).sum())) <= 1e-9 * float(np.abs(got).astype(np.float64).sum())
