@@ -177,6 +177,15 @@ __device__ __forceinline__ float4 ldg4_here(const float* p) {
   return v;
 }
 
+// A model input is read once per step: keep it out of L1, which is small beside 224 KB of shared memory and has to hold
+// the bias and scale vectors every chunk epilogue reads (measured in one call against the plain load: 0.2253 -> 0.2232 ms
+// on the 49,152-column configuration).
+__device__ __forceinline__ float ldg_stream(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 // Cycle accounting of the three roles (CTA 0, one lane each), compiled in with -DFORTIS_TC_PROF only: PROF_ADD(slot) adds
 // the time since the previous call to prof[slot].
 #ifdef FORTIS_TC_PROF
@@ -415,11 +424,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           const uint32_t code = s_code[q0 + j];
           v[j] = 0.f;
           if (live_ && code != 0xFF)
-            v[j] = __ldg(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? p1 : p0)));
+            v[j] = ldg_stream(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? p1 : p0)));
         }
       } else {
 #pragma unroll
-        for (int j = 0; j < 32; j++) v[j] = (live_ && q0 + j < P.n_in) ? __ldg(P.X + row_ * P.n_in + q0 + j) : 0.f;
+        for (int j = 0; j < 32; j++) v[j] = (live_ && q0 + j < P.n_in) ? ldg_stream(P.X + row_ * P.n_in + q0 + j) : 0.f;
       }
       if (P.in_div) {
 #pragma unroll
