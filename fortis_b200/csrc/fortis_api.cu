@@ -534,9 +534,9 @@ void bind_arrays(PlanDev& P, void* const* ptrs, const int* args, int nargs, bool
 
 // copy the visited cells of every stored array back to the host (the reference's cudaMemcpy2DAsync rectangles);
 // stores that form one contiguous run in an array (column physics: level after level) are merged into one copy
-void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
+void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane, cudaStream_t on = nullptr, int kk_begin = 0, int kk_end = -1) {
   Session& s = S();
-  cudaStream_t st = stream();
+  cudaStream_t st = on ? on : stream();
   const long long ni = s.loop.ni, nj = s.loop.count / (s.loop.ni > 0 ? s.loop.ni : 1);
   struct Run { int array; long long off, len; };
   std::vector<Run> runs;
@@ -564,7 +564,7 @@ void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
     if (t.a.si != 1 && (t.a.sj == 0 || nj == 1) && dense[{ai, t.a.si}]) continue;
     const bool planes = multi_plane && !a.vdims.empty();
     const int nplanes = planes ? s.loop.nk : 1;
-    for (int kk = 0; kk < nplanes; kk++) {
+    for (int kk = planes ? kk_begin : 0; kk < (planes && kk_end >= 0 ? kk_end : nplanes); kk++) {
       const long long hoff = planes ? (long long)(s.loop.klo - 1 + kk) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
       char* dsrc = (char*)P.stage[ai] + ((long long)kk * a.plane + t.a.off0) * es;
       char* hdst = (char*)P.cur[ai] + (hoff + t.a.off0) * es;
@@ -597,7 +597,7 @@ void download_stores(PlanDev& P, const int* args, int nargs, bool multi_plane) {
     const size_t es = elt_size(a.elt);
     const bool planes = multi_plane && !a.vdims.empty();
     const int nplanes = planes ? s.loop.nk : 1;
-    for (int kk = 0; kk < nplanes; kk++) {
+    for (int kk = planes ? kk_begin : 0; kk < (planes && kk_end >= 0 ? kk_end : nplanes); kk++) {
       const long long hoff = planes ? (long long)(s.loop.klo - 1 + kk) * a.plane : (multi_plane ? 0 : plane_off_args(a, args, nargs));
       cuda_ok(cudaMemcpyAsync((char*)P.cur[r.array] + (hoff + r.off) * es, (char*)P.stage[r.array] + ((long long)kk * a.plane + r.off) * es,
                               (size_t)r.len * es, cudaMemcpyDeviceToHost, st), "D2H of a stored run");
@@ -1167,6 +1167,103 @@ bool overlapped_step(void* const* gptrs, void* const* sptrs, long long rows) {
   return true;
 }
 
+// The same pipelining for k-distributed loops over HOST arrays (stencil hosts: every array carries the distributed
+// loop's plane dimension): plane k+1 goes up while plane k is computed and the visited rectangle of plane k-1 comes
+// back (driver/fortis_gather_emit.py:66-68, 91-96 moves all planes up, then computes, then copies back rectangle by
+// rectangle on one stream).  A plane is contiguous, so the uploads are plain 1-D copies; planes are independent (the
+// stencil is within a plane), so a plane is a step of its own with nk = 1.  Replayed as one graph from the second call.
+bool overlapped_planes_step(void* const* gptrs, void* const* sptrs) {
+  Session& s = S();
+  if (!s.loop.kdist || s.loop.nk < 2 || s.loop.nk > kMaxChunks || !s.fuse || std::getenv("FORTIS_NO_OVERLAP")) return false;
+  bool any_host = false;
+  for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+    const ArrayInfo& a = s.G.h.arrays[ai];
+    if (!a.used) continue;
+    if (a.vdims.empty()) return false;
+    if (!is_device_ptr(gptrs[ai]) && !maps_host(s.G)) any_host = true;
+  }
+  for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++) {
+    const ArrayInfo& a = s.S.h.arrays[ai];
+    if (!a.used) continue;
+    if (a.vdims.empty() || !s.S.h.written[ai]) return false;
+    if (!is_device_ptr(sptrs[ai]) && !maps_host(s.S)) any_host = true;
+  }
+  if (!any_host || !ensure_copy_streams()) return false;
+  cudaStream_t st = stream();
+  const int nk = s.loop.nk;
+  std::string key("planes");
+  key.append((const char*)gptrs, sizeof(void*) * s.G.h.arrays.size());
+  key.append((const char*)sptrs, sizeof(void*) * s.S.h.arrays.size());
+  if (s.ov_gexec && key == s.ov_key) {
+    cuda_ok(cudaGraphLaunch(s.ov_gexec, st), "cudaGraphLaunch");
+    if (!s.async) cudaStreamSynchronize(st);
+    return true;
+  }
+  if (key != s.ov_key) {
+    if (s.ov_gexec) { cudaGraphExecDestroy(s.ov_gexec); s.ov_gexec = nullptr; }
+    s.ov_key = key; s.ov_calls = 0;
+  }
+  int args[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  StepArgs A;
+  A.use_gather = true; A.fuse_scatter = true;
+  bind_arrays(s.G, gptrs, args, 0, true, false, &A.TG);          // pins, sizes the staging of all planes; no copies
+  bind_arrays(s.S, sptrs, args, 0, true, false, &A.TS);
+  const ArrayTable TG0 = A.TG, TS0 = A.TS;
+  const LoopInfo saved = s.loop;
+  bool capturing = (++s.ov_calls == 2) && !std::getenv("FORTIS_NO_STAGING_GRAPH");
+  if (capturing && cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); capturing = false; }
+  if (capturing) fortis_capturing = 1;
+  bool threw = false; std::string what;
+  try {
+    cudaEventRecord(g_ev_fork, st);
+    cudaStreamWaitEvent(g_h2d, g_ev_fork, 0);
+    cudaStreamWaitEvent(g_d2h, g_ev_fork, 0);
+    for (int kk = 0; kk < nk; kk++) {
+      for (size_t ai = 0; ai < s.G.h.arrays.size(); ai++) {
+        const ArrayInfo& a = s.G.h.arrays[ai];
+        if (!a.used) continue;
+        const size_t es = elt_size(a.elt);
+        const long long off = (long long)kk * a.plane;
+        if (!s.G.on_dev[ai])
+          cuda_ok(cudaMemcpyAsync((char*)s.G.stage[ai] + off * es, (const char*)gptrs[ai] + ((long long)(saved.klo - 1) * a.plane + off) * es,
+                                  (size_t)a.plane * es, cudaMemcpyHostToDevice, g_h2d), "H2D of a plane");
+        A.TG.base[ai] = (char*)TG0.base[ai] + off * es;
+      }
+      cudaEventRecord(g_ev_in[kk], g_h2d);
+      cudaStreamWaitEvent(st, g_ev_in[kk], 0);
+      for (size_t ai = 0; ai < s.S.h.arrays.size(); ai++)
+        if (s.S.h.arrays[ai].used) A.TS.base[ai] = (char*)TS0.base[ai] + (long long)kk * s.S.h.arrays[ai].plane * elt_size(s.S.h.arrays[ai].elt);
+      A.rows = saved.count;
+      s.loop.nk = 1;                                   // one plane is a step of its own
+      run_step_kernels(A);
+      s.loop = saved;
+      cudaEventRecord(g_ev_k[kk], st);
+      cudaStreamWaitEvent(g_d2h, g_ev_k[kk], 0);
+      download_stores(s.S, args, 0, true, g_d2h, kk, kk + 1);
+    }
+    cudaEventRecord(g_ev_join_in, g_h2d);
+    cudaStreamWaitEvent(st, g_ev_join_in, 0);
+    cudaEventRecord(g_ev_join_out, g_d2h);
+    cudaStreamWaitEvent(st, g_ev_join_out, 0);
+  } catch (const std::exception& e) { threw = true; what = e.what(); s.loop = saved; }
+  if (capturing) {
+    fortis_capturing = 0;
+    cudaGraph_t gr = nullptr;
+    const bool ok = cudaStreamEndCapture(st, &gr) == cudaSuccess && !threw && cudaGraphInstantiate(&s.ov_gexec, gr, 0) == cudaSuccess;
+    if (gr) cudaGraphDestroy(gr);
+    if (ok) cuda_ok(cudaGraphLaunch(s.ov_gexec, st), "cudaGraphLaunch");
+    else {
+      s.ov_gexec = nullptr; cudaGetLastError();
+      if (threw) throw std::runtime_error(what);
+      std::fprintf(stderr, "fortis: capture of the staging pipeline failed, running eagerly\n");
+      s.ov_calls = 2;
+      return overlapped_planes_step(gptrs, sptrs);
+    }
+  } else if (threw) throw std::runtime_error(what);
+  if (!s.async) cudaStreamSynchronize(st);
+  return true;
+}
+
 // The fused step: gather -> forward -> scatter of every plane in one launch.  `iargs` are the enclosing-loop
 // indices (1-based) that select the plane of arrays with "v" subscripts when the loop is NOT k-distributed; a
 // k-distributed loop takes none (all planes klo .. klo+nk-1 are processed).
@@ -1193,7 +1290,19 @@ void do_step(const int* iargs, int nint, void* const* gptrs, int ng, void* const
       throw std::runtime_error("fortis_step: the descriptors select a plane by " + std::to_string(need) +
                                " enclosing-loop index argument(s) and the loop is not k-distributed; pass them first");
   }
-  if (overlapped_step(gptrs, sptrs, rows)) return;
+  // a device-resident gather array that shares memory with a device-resident stored array forces the unfused sequence
+  // below; the pipelined staging paths run fused kernels, so they are not taken then
+  bool dev_overlap = false;
+  for (size_t gi = 0; gi < s.G.h.arrays.size() && !dev_overlap; gi++) {
+    if (!s.G.h.arrays[gi].used || !is_device_ptr(gptrs[gi])) continue;
+    const ArrayInfo& ga = s.G.h.arrays[gi];
+    for (size_t si = 0; si < s.S.h.arrays.size(); si++) {
+      if (!s.S.h.written[si] || !is_device_ptr(sptrs[si])) continue;
+      const ArrayInfo& sa = s.S.h.arrays[si];
+      if (ranges_overlap(gptrs[gi], (size_t)ga.total * elt_size(ga.elt), sptrs[si], (size_t)sa.total * elt_size(sa.elt))) { dev_overlap = true; break; }
+    }
+  }
+  if (!dev_overlap && (overlapped_step(gptrs, sptrs, rows) || overlapped_planes_step(gptrs, sptrs))) return;
   cudaStream_t st = stream();
   int args[8];
   for (int i = 0; i < 8; i++) args[i] = i < nint ? iargs[i] : 1;

@@ -158,6 +158,39 @@ def test_stencil_config_full_size(host):
     assert abs(cs - total) <= 1e-9 * scale
 
 
+def test_stencil_config_full_size_host_arrays_plane_pipeline(host, monkeypatch):
+    """The stencil step with HOST arrays: plane k+1 goes up while plane k is computed and the visited rectangle of plane
+    k-1 comes back.  Bit-identical to the device-resident step call after call (eager, captured, replayed), halo of the
+    host's arrays untouched, and identical to the serial staging path."""
+    wl = W.stencil()
+    host.configure(gather=wl["G"], scatter=wl["S"], loop=wl["Lp"], kdist=wl["K"])
+    host.load_model(fortis_b200.write_blob(wl["layers"]))
+    host.option("checksum", 1)
+    sentinel = -123.0
+    d_in, d_out = [dev(a) for a in wl["gin"]], [dev(np.full_like(a, sentinel)) for a in wl["sout"]]
+    host.step(d_in, d_out)
+    host.sync()
+    want = [back(t, a) for t, a in zip(d_out, wl["sout"])]
+    host.step_checksum()
+    outs = [np.full_like(a, sentinel) for a in wl["sout"]]
+    for call in range(4):
+        host.step(wl["gin"], outs)
+        host.sync()
+        for a, b in zip(outs, want):
+            assert a.tobytes(order="F") == b.tobytes(order="F"), "call %d" % call
+        cs = host.step_checksum()
+        total = float(sum(a[1:-1, 1:-1].astype(np.float64).sum() for a in outs))
+        assert abs(cs - total) <= 1e-9 * float(sum(np.abs(a[1:-1, 1:-1]).astype(np.float64).sum() for a in outs))
+        for a in outs:
+            a.fill(sentinel)
+    monkeypatch.setenv("FORTIS_NO_OVERLAP", "1")
+    outs2 = [np.full_like(a, sentinel) for a in wl["sout"]]
+    host.step(wl["gin"], outs2)
+    host.sync()
+    for a, b in zip(outs2, want):
+        assert a.tobytes(order="F") == b.tobytes(order="F")
+
+
 @pytest.mark.parametrize("precision,tol", [("fp32", FP32_TOL), ("fp16", HALF_TOL)])
 def test_conv_config_full_size(host, precision, tol):
     """8 x 33^3 x 3, six residual blocks: whole batch entries 0 and 7 against the oracle."""
