@@ -382,8 +382,17 @@ void ensure_model() {
     if (s.precision != PREC_F32) {
       std::string err;
       s.tc = tc_model_create(s.model, s.precision, st, &err);
-      if (!s.tc) throw std::runtime_error("precision " + std::string(s.precision == PREC_BF16 ? "bf16" : s.precision == PREC_FP16 ? "fp16" : "fp8w") +
-                                          " needs the tensor-core kernel, which cannot take this model: " + err);
+      if (!s.tc) {
+        // Layers wider than the fused kernel holds on chip (the reference's width sweep goes to 2048) run layer by layer
+        // on the fp32 tensor-core kernel instead: slower than a 16-bit GEMM would be, and more accurate than asked for.
+        std::string err32;
+        const bool shape = err.find("wider than") != std::string::npos || err.find("layers") != std::string::npos;
+        if (shape) s.f32 = f32tc_create(s.model, &err32);
+        if (!s.f32)
+          throw std::runtime_error("precision " + std::string(s.precision == PREC_BF16 ? "bf16" : s.precision == PREC_FP16 ? "fp16" : "fp8w") +
+                                   " needs the tensor-core kernel, which cannot take this model: " + err);
+        std::fprintf(stderr, "fortis: %s; the layers run one by one on the fp32 (TF32x3) tensor-core kernel\n", err.c_str());
+      }
     }
   } else if (s.model.is_conv()) {
     std::string err;
@@ -727,7 +736,7 @@ void run_step_kernels(const StepArgs& A) {
   }
   const bool fuse = s.fuse && !A.unfused;
   const bool fused_gather = A.use_gather && fuse;
-  if (s.precision != PREC_F32) {
+  if (s.tc) {
     // The tensor-core kernel fuses the gather / scatter when the descriptor is in its table-driven class (fp32
     // arrays, no lifted expressions or scalars, at most two stride classes, <= 256 inputs / <= 128 outputs);
     // other descriptors run the bit-exact standalone gather / scatter kernels around it.

@@ -172,3 +172,23 @@ def test_prepacked_blob_gives_the_same_bits(host, precision):
         outs.append(torch.cat(d_out).cpu().numpy())
     assert outs[0].tobytes() == outs[1].tobytes() == outs[2].tobytes()
     assert np.abs(outs[0]).max() > 0
+
+
+def test_layers_wider_than_the_fused_kernel_run_layer_by_layer(host, capfd):
+    """The reference's width sweep goes to 1024 and 2048 (results_csv/sweep.log): wider than the fused 16-bit kernel
+    keeps on chip.  Under precision bf16 such a model is not refused: its layers run one by one on the fp32 tensor-core
+    kernel, with a message, and meet the fp32 bar."""
+    layers = fortis_b200.mlp_layers([124, 1024, 1024, 128], seed=9)
+    ncol = 700
+    G, S, Lp, K = fo.identity_descriptors(124, 128, ncol)
+    rng = np.random.default_rng(3)
+    a = np.asfortranarray(rng.normal(size=(124, ncol)).astype(np.float32))
+    b = np.zeros((128, ncol), np.float32, order="F")
+    ref = [b.copy(order="F")]
+    fo.full_step(G, S, Lp, K, layers, [a], ref)
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", "bf16")
+    host.step([a], [b])
+    assert fo.rel_l2(b, ref[0]) <= 1e-5
+    assert "one by one" in capfd.readouterr().err
