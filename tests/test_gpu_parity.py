@@ -364,9 +364,11 @@ def test_errors_are_messages_not_crashes(host):
     A = np.zeros((4, 8), np.float32, order="F")
     with pytest.raises(fortis_b200.FortisError):
         host.gather([A, A])                         # wrong number of arrays
-    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([4, 1024, 2], seed=0)))
+    # an activation the 16-bit tensor-core kernel cannot express (its branch-free form needs a slope in [0, 1]): refused
+    # with a message, not run some other way
+    host.load_model(fortis_b200.write_blob(fortis_b200.mlp_layers([4, 16, 2], seed=0, act="leaky", slope=1.5)))
     host.option("precision", "bf16")
-    with pytest.raises(fortis_b200.FortisError):    # no silent fallback when the tensor-core kernel cannot take it
+    with pytest.raises(fortis_b200.FortisError):
         host.step([A], [np.zeros((2, 8), np.float32, order="F")])
 
 
