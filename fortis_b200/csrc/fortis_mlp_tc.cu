@@ -54,7 +54,7 @@ constexpr int kBlockK = 256;                // K-block: granularity of the layer
 #define FORTIS_TC_STAGE_K 256
 #endif
 constexpr int kStageK = FORTIS_TC_STAGE_K;  // k extent of one weight stage (256 or 128): 64-wide swizzled sub-tiles, ONE copy per stage
-constexpr int kSubStages = kBlockK / kStageK;        // stages per K-block (halving the stage to 16 KB was measured: no gain)
+constexpr int kSubStages = kBlockK / kStageK;        // stages per K-block (16 KB stages, -DFORTIS_TC_STAGE_K=128, measured 3-4 % slower)
 constexpr int kStageBytes = kChunkN * kStageK * 2;   // 32 KB
 constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 KB
 // Two builds of the same kernel.  Shallow ring (default): 3 weight stages, 8 output chunks parked in shared memory and
