@@ -11,10 +11,13 @@ What it restates, and where the reference defines it:
   * MLP forward conventions C[B,N] = A[B,K] . W[N,K]^T   runtime/fortis_rt.c:42-48
   * shipped native forward loop order                    mom6_zb/fwd_native_zb.f90:30-78
   * conv3d = cross-correlation, zero padding             runtime/fortis_rt.c:139-147
+  * single convolution layers (2-D, strided, 'valid')    runtime/fortis_rt.c:108-156, runtime/fortis_fft.cu:66-79
+  * 2-D operators of the micro-suite, by definition     tests/optest.py:6-32
 
 Parity pins (see tests/test_oracle_golden.py): the ZB network's x_test -> y_test vector, the README checksum
 stamps for the toy MLP and the conv probe, and gather/scatter outputs produced by compiling the reference's own
-generated kernels for the CPU (tests/golden/make_golden.py).
+generated kernels for the CPU (tests/golden/make_golden.py); single convolution layers and 2-D operator networks
+against outputs of torch's CPU operators (tests/golden/make_conv_golden.py, make_opnet_golden.py).
 
 All float32 arithmetic is done op by op in numpy float32 (round-to-nearest, no fused multiply-add), which is what
 the reference's `-fmad=false` gather/scatter kernels compute.
