@@ -569,6 +569,30 @@ def test_empty_and_single_row_batches(host, precision):
             assert fo.rel_l2(Y[:count], fo.mlp_forward(layers, X[:count])) < (FP32_TOL if precision == "fp32" else 5e-3)
 
 
+@pytest.mark.parametrize("tc", [0, 1])
+def test_stencil_step_with_input_and_output_scales(host, tc):
+    """The stencil step of a model that divides its inputs and multiplies its outputs by per-feature scales (what the
+    ocean nets do: mom6_zb/export_zb.py:13-14), on the packed-FMA kernel and on the tensor-core option."""
+    nx, ny, nz = 45, 23, 2
+    G, S, Lp, K = fo.stencil_descriptors(nx, ny, nz)
+    rng = np.random.default_rng(12)
+    gin = [np.asfortranarray(rng.normal(size=(nx + 2, ny + 2, nz)).astype(np.float32)) for _ in range(3)]
+    layers = fortis_b200.mlp_layers([27, 20, 20, 3], seed=6, init="uniform", act="relu", bias="uniform")
+    in_div = (rng.random(27) + 0.5).astype(np.float32)
+    out_mul = (rng.random(3) + 0.5).astype(np.float32)
+    ref = [np.zeros((nx + 2, ny + 2, nz), np.float32, order="F") for _ in range(3)]
+    fo.full_step(G, S, Lp, K, layers, gin, ref, in_norms=in_div, out_norms=out_mul)
+    host.configure(gather=G, scatter=S, loop=Lp, kdist=K)
+    host.load_model(fortis_b200.write_blob(layers, in_div=in_div, out_mul=out_mul))
+    host.option("stencil_tc", tc)
+    out = [np.zeros((nx + 2, ny + 2, nz), np.float32, order="F") for _ in range(3)]
+    host.step(gin, out)
+    host.sync()
+    assert host.L.fortis_device_status() == 0
+    cat = lambda L: np.concatenate([a.ravel() for a in L])
+    assert fo.rel_l2(cat(out), cat(ref)) <= FP32_TOL
+
+
 @pytest.mark.parametrize("dims", [[27, 20, 20, 3], [27, 32, 4], [27, 9, 17, 1]])
 def test_stencil_step_on_tensor_cores_option(host, dims):
     """Option stencil_tc: the 3x3-stencil step with its layers as TF32x3 tensor-core products (rows in tensor memory,
