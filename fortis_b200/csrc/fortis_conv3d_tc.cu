@@ -132,6 +132,10 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
   constexpr int kHalfRows = (kShiftA ? NOUT : 3 * NOUT) / 2;      // weight rows of one tile held by each CTA
   constexpr int kHalfBytes = kHalfRows * kC * 2;                  // 4 KB per tap (12 KB per group)
   extern __shared__ __align__(1024) uint8_t smem[];
+  // Programmatic dependent launch: the next layer's CTAs may be scheduled as soon as SMs free up.  They set up their
+  // barriers and tensor memory and load their weights while this layer's last tiles finish, and wait (griddep_wait below)
+  // for this grid to complete before they touch an activation buffer.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t base = smem_u32(smem);                           // resident weights at offset 0
   if (base & 1023u) {                                             // same in both CTAs of a pair: both leave
     if (threadIdx.x == 0) atomicCAS(P.status, 0, CST_ALIGN);
@@ -180,6 +184,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
 #pragma unroll 1
     for (int g = 0; g < kWLoads; g++)
       tma_load_2d_pair(base + g * kHalfBytes, &P.wmap, 0, g * 2 * kHalfRows + (int)crank * kHalfRows, w0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");           // the previous layer's output is complete and visible
     uint32_t s = 0, ph = 0;
     bool stop = false;
     const bool pw = blockIdx.x == 0 && lane == 0;
@@ -266,6 +271,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
       const float4 q = __ldg(reinterpret_cast<const float4*>(P.bias + c0) + j);
       bias[4 * j] = q.x; bias[4 * j + 1] = q.y; bias[4 * j + 2] = q.z; bias[4 * j + 3] = q.w;
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");           // before the first read of the residual volume and the first store
     const uint32_t arr_acc_empty = map_to_cta(bar_acc_empty, 0);   // the leader's barrier
     const bool pw = blockIdx.x == 0 && threadIdx.x == 64;
     long long pt = clock64();
@@ -404,6 +410,7 @@ __global__ void __launch_bounds__(kConvThreads, 1) conv3d_tc_kernel(const __grid
 template <bool F16>
 __global__ void __launch_bounds__(256) conv_pack_input_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                                               int N, int D, int H, int W, int C) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the first layer may set up while this kernel runs
   const long long nvox = (long long)N * D * H * W;
   for (long long v = (long long)blockIdx.x * 256 + threadIdx.x; v < nvox; v += (long long)gridDim.x * 256) {
     const int w_ = (int)(v % W), h_ = (int)((v / W) % H), d_ = (int)((v / ((long long)W * H)) % D), n_ = (int)(v / ((long long)W * H * D));
@@ -596,10 +603,13 @@ bool conv_tc_forward(ConvTcModel* m, const float* x, float* y, int N, int D, int
   const int grid = 2 * (int)(npairs < max_pairs ? npairs : max_pairs);          // clusters of two CTAs
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kConvThreads); cfg.dynamicSmemBytes = kConvSmem; cfg.stream = s;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-  cfg.attrs = at; cfg.numAttrs = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;    // a layer may start while the one before it drains
+  at[1].val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = std::getenv("FORTIS_NO_PDL") == nullptr;
+  cfg.attrs = at; cfg.numAttrs = pdl ? 2 : 1;
   static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
   static long long* dprof = nullptr;
   if (want_prof && !dprof) cudaMalloc(&dprof, 16 * sizeof(long long));

@@ -30,6 +30,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -106,6 +107,9 @@ __device__ __forceinline__ float act_slope(float v, float slope) { return fmaxf(
 
 __global__ void __launch_bounds__(kThreadsF, 1) linear_tf32x3_kernel(const __grid_constant__ F32Params P) {
   extern __shared__ __align__(1024) uint8_t smem[];
+  // Programmatic dependent launch: the next layer's CTAs may be scheduled as SMs free up; they set up, start streaming
+  // their weights, and wait (griddepcontrol.wait in the warps that read or write activations) for this grid to finish.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t base = smem_u32(smem);
   if (base & 1023u) {
     if (threadIdx.x == 0) atomicCAS(P.status, 0, FST_ALIGN);
@@ -219,6 +223,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) linear_tf32x3_kernel(const __gri
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ A producers: thread = row of the tile
+    asm volatile("griddepcontrol.wait;" ::: "memory");         // the previous layer's activations are complete and visible
     const int r = (warp - 2) * 32 + lane;
     uint32_t s = 0, ph = 0;
     bool stop = false;
@@ -295,6 +300,7 @@ __global__ void __launch_bounds__(kThreadsF, 1) linear_tf32x3_kernel(const __gri
     }
   } else {
     // ------------------------------------------------------------------ epilogue: thread = row of the tile
+    asm volatile("griddepcontrol.wait;" ::: "memory");         // the buffer written here may still be read by the previous layer
     const int quad = warp & 3;                                // the TMEM lanes this warp may read
     const int r = quad * 32 + lane;
     const uint32_t lane_addr = tmem + ((uint32_t)(quad * 32) << 16);
@@ -572,6 +578,19 @@ int f32tc_grid(long long nrows) {
   return sms;
 }
 
+// one layer, allowed to start while the launch before it in the stream drains (programmatic stream serialisation)
+// (`early` = false for a launch whose WEIGHTS were produced by the kernel in front of it: the weight loads do not wait)
+static bool launch_layer(const F32Params& P, int grid, cudaStream_t s, bool early = true) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreadsF); cfg.dynamicSmemBytes = kSmemF; cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool pdl = std::getenv("FORTIS_NO_PDL") == nullptr;
+  cfg.attrs = at; cfg.numAttrs = (pdl && early) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, linear_tf32x3_kernel, P) == cudaSuccess;
+}
+
 bool f32tc_forward(F32TcModel* m, const F32TcLaunch& L, cudaStream_t s, std::string* err) {
   const long long nrows = L.g.count * L.g.nk;
   if (nrows <= 0) return true;
@@ -603,7 +622,7 @@ bool f32tc_forward(F32TcModel* m, const F32TcLaunch& L, cudaStream_t s, std::str
         P.partials = L.partials; P.sum = L.partials ? L.sum : nullptr; P.done = L.done;
       } else { P.c_mode = C_ROW_MAJOR; P.C = L.Y; P.ldc = n_out; }
     } else { P.c_mode = C_FEATURE_MAJOR; P.C = L.act[l & 1]; P.ldc = L.act_ld; }
-    linear_tf32x3_kernel<<<grid_for(nrows, T.g), kThreadsF, kSmemF, s>>>(P);
+    if (!launch_layer(P, grid_for(nrows, T.g), s)) { if (err) *err = "split-TF32 kernel launch failed"; return false; }
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("split-TF32 kernel launch: ") + cudaGetErrorString(e); return false; }
@@ -643,7 +662,7 @@ bool f32tc_gemm(const float* A, const float* W, float* C, long long M, int N, in
   P.g.count = M; P.g.nk = 1; P.g.ni = 1; P.g.kk0 = 0;
   P.a_mode = A_ROW_MAJOR; P.A = A; P.lda = K;
   P.c_mode = C_ROW_MAJOR; P.C = C; P.ldc = N;
-  linear_tf32x3_kernel<<<grid_for(M, c->g), kThreadsF, kSmemF, s>>>(P);
+  launch_layer(P, grid_for(M, c->g), s, false);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("split-TF32 kernel launch: ") + cudaGetErrorString(e); return false; }
   return true;
