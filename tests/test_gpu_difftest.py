@@ -4,6 +4,8 @@ lists) with a small random MLP behind them, run through the library and through 
 The reference tests its compiler the same way, fused against unfused on random programs
 (tests/difftest/gen_difftest.py:35-120, bar 5e-6); here gather and scatter have to be bit-exact and the forward within
 the fp32 bar, in the three-call form and in the fused step, with host arrays and with device arrays."""
+import os
+
 import numpy as np
 import pytest
 
@@ -14,7 +16,9 @@ import fortis_b200
 from fortis_b200 import descriptors as D
 from oracle import fortis_oracle as fo
 
-NCASES = 48
+# a longer sweep with other seeds: FORTIS_DIFFTEST_CASES=400 FORTIS_DIFFTEST_SEED=1 python -m pytest tests/test_gpu_difftest.py -m gpu
+NCASES = int(os.environ.get("FORTIS_DIFFTEST_CASES", "200"))
+SEED0 = 9000 + 1000 * int(os.environ.get("FORTIS_DIFFTEST_SEED", "0"))
 
 
 def dev(a):
@@ -32,7 +36,7 @@ def make_arrays(J, rng, lo=-2.0, hi=2.0):
 
 @pytest.mark.parametrize("block", range(4))
 def test_random_descriptors_against_the_interpreter(block):
-    rng = np.random.default_rng(9000 + block)
+    rng = np.random.default_rng(SEED0 + block)
     h = fortis_b200.Host()
     for case in range(NCASES // 4):
         G, S, Lp, K, nargs, planes = D.random_case(rng)
