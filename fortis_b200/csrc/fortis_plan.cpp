@@ -170,8 +170,19 @@ double eval_prog_host(const ExprProg& P, double tv, const double* sc, const doub
       case OP_EXP_F: st[sp - 1] = (double)std::exp((float)st[sp - 1]); break;
       case OP_LOG_F: st[sp - 1] = (double)std::log((float)st[sp - 1]); break;
       case OP_TANH_F: st[sp - 1] = (double)std::tanh((float)st[sp - 1]); break;
-      case OP_MAX_F: sp--; st[sp - 1] = (double)std::fmax((float)st[sp - 1], (float)st[sp]); break;
-      case OP_MIN_F: sp--; st[sp - 1] = (double)std::fmin((float)st[sp - 1], (float)st[sp]); break;
+      // as the device computes them: +0 > -0 (PTX max.f32 / min.f32), where the host's fmax may return either zero
+      case OP_MAX_F: {
+        sp--;
+        const float a = (float)st[sp - 1], b = (float)st[sp];
+        st[sp - 1] = (a == 0.f && b == 0.f) ? ((std::signbit(a) && std::signbit(b)) ? -0.0 : 0.0) : (double)std::fmax(a, b);
+        break;
+      }
+      case OP_MIN_F: {
+        sp--;
+        const float a = (float)st[sp - 1], b = (float)st[sp];
+        st[sp - 1] = (a == 0.f && b == 0.f) ? ((std::signbit(a) || std::signbit(b)) ? -0.0 : 0.0) : (double)std::fmin(a, b);
+        break;
+      }
       case OP_END_EXPR: tv = st[--sp]; break;
     }
   }

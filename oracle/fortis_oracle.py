@@ -132,6 +132,23 @@ def parse_expr(text: str):
     return out
 
 
+def fmax_cuda(a, b):
+    """fmaxf as the GPU computes it (the reference's expressions run in its generated CUDA kernels): the number when
+    one operand is NaN, and +0 > -0 (PTX max.f32), where C's fmax may return either zero."""
+    a, b = np.asarray(a), np.asarray(b)
+    r = np.fmax(a, b)
+    zeros = (a == 0) & (b == 0)
+    return np.where(zeros, np.where(np.signbit(a) & np.signbit(b), -0.0, 0.0).astype(r.dtype), r)
+
+
+def fmin_cuda(a, b):
+    """fminf as the GPU computes it: -0 < +0 (PTX min.f32)."""
+    a, b = np.asarray(a), np.asarray(b)
+    r = np.fmin(a, b)
+    zeros = (a == 0) & (b == 0)
+    return np.where(zeros, np.where(np.signbit(a) | np.signbit(b), -0.0, 0.0).astype(r.dtype), r)
+
+
 def eval_expr(ast, tv, scalars: Dict[int, Any], dtype=np.float32):
     """Evaluate an AST in `dtype`, one IEEE operation per node (numpy never contracts a*b+c)."""
     k = ast[0]
@@ -158,9 +175,9 @@ def eval_expr(ast, tv, scalars: Dict[int, Any], dtype=np.float32):
         with np.errstate(divide="ignore", invalid="ignore"):
             return a / b
     if k == "max":
-        return np.fmax(a, b)
+        return fmax_cuda(a, b)
     if k == "min":
-        return np.fmin(a, b)
+        return fmin_cuda(a, b)
     raise ValueError(k)
 
 
@@ -300,7 +317,7 @@ def _eval_typed(ast, tv, scal):
     a, da = _eval_typed(ast[1], tv, scal)
     b, db = _eval_typed(ast[2], tv, scal)
     if k in ("max", "min"):
-        f = np.fmax if k == "max" else np.fmin
+        f = fmax_cuda if k == "max" else fmin_cuda
         return f(np.asarray(a).astype(np.float32), np.asarray(b).astype(np.float32)).astype(np.float32), False
     d = da or db
     dt = np.float64 if d else np.float32

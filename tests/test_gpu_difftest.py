@@ -57,7 +57,11 @@ def test_random_descriptors_against_the_interpreter(block):
         assert X.tobytes() == Xo.tobytes(), tag
         h.forward_batched()
         Y = h.model_output(rows, nout)
-        assert fo.rel_l2(Y, fo.mlp_forward(layers, X)) < 1e-5, tag
+        # the fp32 bar; where the outputs nearly cancel (constant inputs, tiny norms) a relative error means little, and
+        # the library only has to be about as close to an fp64 forward as the fp32 oracle itself is
+        Y64 = fo.mlp_forward(layers, X, dtype=np.float64)
+        e_lib, e_ora = fo.rel_l2(Y, Y64), fo.rel_l2(fo.mlp_forward(layers, X), Y64)
+        assert e_lib < 1e-5 or e_lib < 8 * e_ora + 1e-6, tag
         work, ref = [a.copy(order="F") for a in sin], [a.copy(order="F") for a in sin]
         for k in (range(P["klo"], P["klo"] + P["nk"]) if P["kdist"] else [a0[0] if a0 else 1]):
             h.scatter(work, args=(k,) if (P["kdist"] or a0) else ())
@@ -67,8 +71,11 @@ def test_random_descriptors_against_the_interpreter(block):
         # ---- fused step, host arrays then device arrays: the whole chain against the interpreter
         full = [a.copy(order="F") for a in sin]
         Yo = fo.mlp_forward(layers, Xo)
+        full64 = [a.copy(order="F") for a in sin]
+        Yo64 = fo.mlp_forward(layers, Xo, dtype=np.float64).astype(np.float32)
         for k in (range(P["klo"], P["klo"] + P["nk"]) if P["kdist"] else [a0[0] if a0 else 1]):
             fo.scatter(S, Lp, K, Yo, full, args=(k,))
+            fo.scatter(S, Lp, K, Yo64, full64, args=(k,))
         for resident in (False, True):
             w2 = [a.copy(order="F") for a in sin]
             g_arr = [dev(a) for a in gin] if resident else gin
@@ -76,7 +83,7 @@ def test_random_descriptors_against_the_interpreter(block):
             h.step(g_arr, s_arr, args=a0)
             h.sync()
             got = [back(t, a) for t, a in zip(s_arr, w2)] if resident else w2
-            for a, b, orig in zip(got, full, sin):
+            for a, b, c, orig in zip(got, full, full64, sin):
                 assert np.array_equal(a != orig, b != orig) or fo.rel_l2(a, b) < 1e-6, tag      # the same cells were written
-                assert fo.rel_l2(a, b) < 1e-5, tag
+                assert fo.rel_l2(a, b) < 1e-5 or fo.rel_l2(a, c) < 8 * fo.rel_l2(b, c) + 1e-6, tag
     h.reset()
