@@ -4,6 +4,8 @@ Bars (the tolerances the benchmark definition states): bf16 <= 5e-3, FP8-E4M3 we
 tests additionally compare with the oracle's model of the reduced-precision arithmetic (bf16 activations, bf16 or
 E4M3 weights, wide accumulation), which isolates indexing / layout mistakes from rounding.
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -192,3 +194,33 @@ def test_layers_wider_than_the_fused_kernel_run_layer_by_layer(host, capfd):
     host.step([a], [b])
     assert fo.rel_l2(b, ref[0]) <= 1e-5
     assert "one by one" in capfd.readouterr().err
+
+
+@pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_TC_SWEEP", "10"))))
+def test_random_shapes_against_the_low_precision_model(host, seed):
+    """Random depths (1-7 layers), widths (1-768, so every padding and chunk count), row counts (1-4000, so ragged
+    last tiles and CTAs with zero to several tiles), activations and precisions: the fused kernel against the oracle's
+    model of its arithmetic, in the array form and, for the fused step, through an identity-layout descriptor."""
+    rng = np.random.default_rng(4200 + seed)
+    nl = int(rng.integers(1, 8))
+    dims = [int(rng.integers(1, 257))] + [int(rng.choice([1, 7, 64, 65, 128, 200, 256, 257, 300, 512, 513, 700, 768])) for _ in range(nl - 1)] + [int(rng.integers(1, 129))]
+    rows = int(rng.choice([1, 2, 127, 128, 129, 500, 1000, 2500, 4000]))
+    precision = str(rng.choice(["bf16", "fp16", "fp8w"]))
+    act = str(rng.choice(["relu", "leaky"]))
+    layers = fortis_b200.mlp_layers(dims, seed=int(rng.integers(1 << 30)), act=act, slope=float(rng.uniform(0.01, 0.3)), bias="uniform", scale=0.1)
+    X = rng.normal(size=(rows, dims[0])).astype(np.float32)
+    model = fo.mlp_forward_lowp(layers, X, precision)
+    tag = "seed %d dims %s rows %d %s %s" % (seed, dims, rows, precision, act)
+    Y = run_array_form(host, layers, X, precision)
+    assert fo.rel_l2(Y, model) < MODEL_TOL, tag
+    # the same through gather -> forward -> scatter of a (features, columns) Fortran array
+    G, S, Lp, K = fo.identity_descriptors(dims[0], dims[-1], rows)
+    a = np.asfortranarray(X.T.copy())
+    b = np.zeros((dims[-1], rows), np.float32, order="F")
+    host.reset()
+    host.configure(gather=G, scatter=S, loop=Lp)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", precision)
+    host.step([a], [b])
+    assert fo.rel_l2(b.T, model) < MODEL_TOL, tag
+    assert fo.rel_l2(b.T, Y) < 1e-6, tag
