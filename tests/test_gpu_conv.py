@@ -262,3 +262,29 @@ def test_2d_operator_networks_through_the_whole_array_entry(host, golden_dir):
     with pytest.raises(fortis_b200.FortisError):
         host.option("precision", "bf16")
         host.forward(np.zeros((2, 2, 12, 10), np.float32), np.zeros((2, 5, 6, 5), np.float32))
+
+
+@pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_CONV_SWEEP", "6"))))
+def test_conv_net_random_extents_against_the_low_precision_model(host, seed):
+    """Random batch and spatial extents (every residue of the padded row pitch, volumes smaller than one tile pair and
+    larger than a round of tiles), channel counts of the edge layers, depth and 16-bit format: the tensor-core network
+    against the oracle's model of its arithmetic; a second call must reproduce the first bit for bit."""
+    rng = np.random.default_rng(5100 + seed)
+    shape = (int(rng.integers(1, 4)), int(rng.integers(1, 11)), int(rng.integers(1, 13)), int(rng.integers(1, 41)))
+    cin, cout, blocks = int(rng.integers(1, 17)), int(rng.integers(1, 17)), int(rng.integers(1, 3))
+    mode = str(rng.choice(["bf16", "fp16"]))
+    layers = fortis_b200.conv_layers(cin, 64, cout, nblocks=blocks, seed=int(rng.integers(1 << 30)))
+    for L in layers:
+        L["b"] = (rng.normal(size=L["b"].shape) * 0.05).astype(np.float32)
+    x = rng.normal(size=shape + (cin,)).astype(np.float32)
+    model = fo.convnet_forward_lowp(layers, x, mode=mode)
+    host.load_model(fortis_b200.write_blob(layers))
+    host.option("precision", mode)
+    host.option("conv_shape", "%d,%d,%d,%d" % shape)
+    y, y2 = np.zeros(shape + (cout,), np.float32), np.zeros(shape + (cout,), np.float32)
+    host.forward(x, y)
+    host.forward(x, y2)
+    tag = "seed %d shape %s cin %d cout %d blocks %d %s" % (seed, shape, cin, cout, blocks, mode)
+    assert y2.tobytes() == y.tobytes(), tag
+    assert fo.rel_l2(y, model) < 2e-3, tag + " %.3e" % fo.rel_l2(y, model)
+    assert host.L.fortis_device_status() == 0, tag
