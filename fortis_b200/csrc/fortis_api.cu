@@ -1431,6 +1431,7 @@ int fortis_set_option(const char* key, const char* value) {
   else if (k == "graph") { s.graph = v != "0"; drop_graph(); }
   else if (k == "async") { s.async = v != "0"; }
   else if (k == "stencil_tc") { s.use_stencil_tc = v != "0"; drop_graph(); }
+  else if (k == "tc_pair") { tc_set_pair_mode(v == "default" ? -1 : (v != "0")); free_model_dev(); drop_graph(); }
   else if (k == "host_access") {
     if (v == "copy") s.host_access = 0;
     else if (v == "mapped_out") s.host_access = 1;
@@ -1452,6 +1453,7 @@ int fortis_set_option(const char* key, const char* value) {
 
 void fortis_reset(void) {
   g_tc_test = TcTestKnobs{0u, 0};
+  tc_set_pair_mode(-1);
   if (!g_S) return;
   if (g_stream) cudaStreamSynchronize(g_stream);
   Session& s = S();

@@ -71,6 +71,9 @@ constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 
 #ifndef FORTIS_TC_DEEP_RING
 #define FORTIS_TC_DEEP_RING 0
 #endif
+#ifndef FORTIS_TC_PAIR_DEFAULT
+#define FORTIS_TC_PAIR_DEFAULT 0
+#endif
 constexpr bool kRegRealloc = FORTIS_TC_DEEP_RING != 0;
 #ifdef FORTIS_TC_INLINE_WAIT
 constexpr bool kInlineWait = true;
@@ -158,8 +161,9 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t saddr) {
 
 // instruction descriptor: D = f32, A and B both bf16 (format code 1) or both IEEE half (code 0), both K-major,
 // N = 64, M = 128
-template <bool F16> struct MlpIdesc {
-  static constexpr uint32_t value = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(kChunkN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+template <bool F16, bool PAIR = false> struct MlpIdesc {
+  static constexpr uint32_t value = (1u << 4) | (F16 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(kChunkN >> 3) << 17) |
+                                    ((uint32_t)((PAIR ? 2 * kTileM : kTileM) >> 4) << 24);
 };
 // two consecutive k values as one 32-bit tensor-memory column, in the kernel's 16-bit operand format
 template <bool F16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
@@ -205,9 +209,20 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 // ---------------------------------------------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------------------------------------------
-template <bool HAS_SCALE, bool F16>
+//
+// PAIR: the same kernel as clusters of two CTAs (cta_group::2).  Each CTA owns a 128-row tile with its own A, accumulators,
+// epilogue and parked chunks; the leader (cluster rank 0) issues every MMA over both CTAs' rows (M = 256), and a chunk's
+// 64 weight rows come half from each CTA's shared memory, so each SM streams HALF of the weights (16 KB stages, six of
+// them).  Copies are plain tensor copies whose completion is counted on the leader's barriers; the leader's commits
+// arrive on the barriers of both CTAs; the row warps of both CTAs hand accumulators and A blocks back on the leader's
+// barriers, one arrival per warp.
+template <bool HAS_SCALE, bool F16, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
-  constexpr uint32_t kIdesc = MlpIdesc<F16>::value;
+  constexpr uint32_t kIdesc = MlpIdesc<F16, PAIR>::value;
+  constexpr int kStg = PAIR ? 2 * kStages : kStages;                 // ring depth in stages
+  constexpr int kStgBytes = PAIR ? kStageBytes / 2 : kStageBytes;    // this CTA's part of a stage
+  constexpr int kSubB = PAIR ? kSubBytes / 2 : kSubBytes;            // one 64-wide k sub-tile of it
+  constexpr int kRowArrivals = PAIR ? 16 : kEpiThreads;              // arrivals that hand an accumulator / an A block back
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t base = smem_u32(smem);                         // parked chunks: kSmemChunks x 16 KB at offset 0
   if (base & 1023u) {                                           // the swizzled weight stages need 1024-byte alignment
@@ -221,9 +236,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   // Every stage has one "full" barrier PER ISSUER: a parity wait can only tell a barrier's current phase from the
   // previous one, so each barrier needs a single waiter that sees every one of its phases; the TMA warp arms the
   // barrier of the issuer that will consume the stage.
-  static_assert(8 * ((kIssuers + 1) * kStages + 9) <= 256, "the barriers must fit the first 256 bytes of the barrier block");
-  const uint32_t bar_full = bars, bar_empty = bars + 8 * kIssuers * kStages;
-  const uint32_t bar_acc_full = bar_empty + 8 * kStages, bar_acc_empty = bar_acc_full + 16;
+  static_assert(8 * ((kIssuers + 1) * kStg + 9) <= 256, "the barriers must fit the first 256 bytes of the barrier block");
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kIssuers * kStg;
+  const uint32_t bar_acc_full = bar_empty + 8 * kStg, bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
   uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 256);
   volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 260);
@@ -238,12 +253,18 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long ntiles = (P.nrows + kTileM - 1) / kTileM;
+  // work units: tiles, or (PAIR) pairs of tiles 2 u and 2 u + 1, one per CTA of the cluster
+  uint32_t crank = 0;
+  if constexpr (PAIR) crank = cluster_ctarank();
+  const long long nunits = PAIR ? (ntiles + 1) / 2 : ntiles;
+  const long long unit0 = PAIR ? (long long)(blockIdx.x >> 1) : (long long)blockIdx.x;
+  const long long ustep = PAIR ? (long long)(gridDim.x >> 1) : (long long)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kIssuers * kStages; s++) mbar_init(bar_full + 8 * s, 1);
-    for (int s = 0; s < kStages; s++) mbar_init(bar_empty + 8 * s, 1);
-    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kEpiThreads); }
-    for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kEpiThreads);
+    for (int s = 0; s < kIssuers * kStg; s++) mbar_init(bar_full + 8 * s, 1);
+    for (int s = 0; s < kStg; s++) mbar_init(bar_empty + 8 * s, 1);
+    for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kRowArrivals); }
+    for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kRowArrivals);
     for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, kIssuers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -275,11 +296,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   if (warp == 8 && lane < P.nlayers)
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&P.maps[lane])) : "memory");
   if (warp == 9) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();      // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
@@ -293,43 +320,53 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       uint32_t s = 0, ph = 0, acc_it = 0;
       PROF_DECL(blockIdx.x == 0 && lane == 0);
       bool stop = false;
-      for (long long tile = blockIdx.x; tile < ntiles && !stop; tile += gridDim.x)
+      uint32_t full_leader = bar_full;           // PAIR: the leader's barriers collect both CTAs' copies
+      if constexpr (PAIR) full_leader = map_to_cta(bar_full, 0);
+      for (long long u = unit0; u < nunits && !stop; u += ustep)
         for (int l = 0; l < P.nlayers && !stop; l++) {
           const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const CUtensorMap* map = &P.maps[l];
           const uint8_t* wtiled = P.layer[l].wtiled;
           (void)map; (void)wtiled;
           for (int c = 0; c < nchunks && !stop; c++, acc_it++) {
-            const uint32_t full_c = bar_full + 8 * kStages * (acc_it & 1);      // the barriers of the issuer that owns this chunk
+            const uint32_t full_off = 8 * kStg * (acc_it & 1);      // the barriers of the issuer that owns this chunk
             for (int ks = 0; ks < nkb * kSubStages; ks++) {
               PROF_ADD(17);
               if (!wait_bar(bar_empty + 8 * s, ph ^ 1, abort_flag, P.status, ST_EMPTY, P.wait_limit)) { stop = true; break; }
               PROF_ADD(16);
-              const bool skip = P.test_skip_stage && blockIdx.x == 0 && tile == 0 && l == 0 && c == 0 && ks == 0;   // test only
-              if (!skip) {
-                mbar_expect_tx(full_c + 8 * s, kStageBytes);
+              const bool skip = P.test_skip_stage && blockIdx.x == 0 && u == unit0 && l == 0 && c == 0 && ks == 0;   // test only
+              if constexpr (PAIR) {
+                // the leader arms its barrier for both halves; each CTA copies its 32 of the chunk's 64 weight rows
+                if (crank == 0) mbar_expect_tx(bar_full + full_off + 8 * s, 2 * kStgBytes);
+                if (!skip)
+                  tma_load_3d_pair(ring + s * kStgBytes, map, 0, c * kChunkN + (int)crank * (kChunkN / 2), ks * (kStageK / 64),
+                                   full_leader + full_off + 8 * s);
+              } else if (!skip) {
+                mbar_expect_tx(bar_full + full_off + 8 * s, kStageBytes);
 #if FORTIS_TC_TILED_W
-                bulk_load(ring + s * kStageBytes, wtiled + (size_t)(c * (nkb * kSubStages) + ks) * kStageBytes, kStageBytes, full_c + 8 * s);
+                bulk_load(ring + s * kStageBytes, wtiled + (size_t)(c * (nkb * kSubStages) + ks) * kStageBytes, kStageBytes, bar_full + full_off + 8 * s);
 #else
-                tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), full_c + 8 * s);
+                tma_load_3d(ring + s * kStageBytes, map, 0, c * kChunkN, ks * (kStageK / 64), bar_full + full_off + 8 * s);
 #endif
               }
-              if (++s == kStages) { s = 0; ph ^= 1; }
+              if (++s == kStg) { s = 0; ph ^= 1; }
             }
           }
         }
-    } else if (warp < 9 + kIssuers) {
-      // ---------------------------------------------------------------- MMA issuers (whole warps, one lane issues)
+    } else if (warp < 9 + kIssuers && crank == 0) {
+      // ---------------------------------------------------------------- MMA issuers (whole warps, one lane issues; PAIR: the leader's only)
       // Two warps issue: a 128 x 64 x 16 MMA keeps the tensor pipe busy for 32 cycles, less than one warp needs to wait
       // for a stage, issue sixteen MMAs and commit.  Chunks alternate between the two accumulators, so issuer w simply
       // owns accumulator w and all chunks that land in it; the pipe sees one in-order stream.  Both walk the same
       // chunk / stage sequence and skip what is not theirs.
       const uint32_t me = (uint32_t)(warp - 9);
-      const uint32_t my_full = bar_full + 8 * kStages * me;
+      const uint32_t my_full = bar_full + 8 * kStg * me;
       uint32_t s = 0, full_par = 0, acc_it = 0, lay_it = 0;     // full_par: bit s = parity of this issuer's next phase of stage s
       const uint64_t desc_hi = make_b_desc(0) & 0xFFFFFFFF00000000ull;
       PROF_DECL(blockIdx.x == 0 && lane == 0 && me == 0);
-      for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x)
+      // commits arrive on this CTA's barrier or (PAIR) on the barrier at the same offset in both CTAs
+      auto commit = [&](uint32_t bar) { if constexpr (PAIR) tc_commit_pair(bar); else tc_commit(bar); };
+      for (long long u = unit0; u < nunits; u += ustep)
         for (int l = 0; l < P.nlayers; l++, lay_it++) {
           const int nchunks = P.layer[l].N / kChunkN, nkb = P.layer[l].K / kBlockK;
           const uint32_t lph = lay_it & 1;
@@ -337,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           for (int c = 0; c < nchunks; c++, acc_it++) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             if (b != me) {                                    // the other issuer's chunk: step over its stages
-              s = (s + (uint32_t)(nkb * kSubStages)) % kStages;
+              s = (s + (uint32_t)(nkb * kSubStages)) % kStg;
               continue;
             }
             any = true;
@@ -363,15 +400,22 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 tc_fence_after();
                 // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
                 // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
-                const uint32_t sb = ring + s * kStageBytes;
+                const uint32_t sb = ring + s * kStgBytes;
                 const uint64_t bd0 = desc_hi | (uint64_t)((sb >> 4) & 0x3FFF);
                 const uint32_t a0 = tmem + kb * (kBlockK / 2) + sub * (kStageK / 2);
-                tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)(kb | sub));
+                if constexpr (PAIR) {
+                  tc_mma_ts_first_pair<kIdesc>(d_tmem, a0, bd0, (uint32_t)(kb | sub));
 #pragma unroll
-                for (int j = 1; j < kStageK / 16; j++)
-                  tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
-                tc_commit(bar_empty + 8 * s);                 // stage reusable once these MMAs have read it
-                if (++s == kStages) s = 0;
+                  for (int j = 1; j < kStageK / 16; j++)
+                    tc_mma_ts_acc_pair<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubB >> 4) + (j & 3) * 2));
+                } else {
+                  tc_mma_ts_first<kIdesc>(d_tmem, a0, bd0, (uint32_t)(kb | sub));
+#pragma unroll
+                  for (int j = 1; j < kStageK / 16; j++)
+                    tc_mma_ts_acc<kIdesc>(d_tmem, a0 + j * 8, bd0 + (uint64_t)((j >> 2) * (kSubBytes >> 4) + (j & 3) * 2));
+                }
+                commit(bar_empty + 8 * s);                    // stage reusable once these MMAs have read it
+                if (++s == kStg) s = 0;
               }
               if (mine_last) {
                 // this issuer's last MMAs on K-block kb in this layer: once both issuers' have retired, those columns
@@ -379,14 +423,14 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 // with the last one, which keeps every barrier at one phase per layer.
                 // (a one-chunk layer has one working issuer, which then signals for both)
                 for (int rep = 0; rep < (nchunks < kIssuers ? kIssuers : 1); rep++) {
-                  if (kb < kMaxKBlocks - 1) tc_commit(bar_a_dead + 8 * kb);
+                  if (kb < kMaxKBlocks - 1) commit(bar_a_dead + 8 * kb);
                   if (kb == nkb - 1)
-                    for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) tc_commit(bar_a_dead + 8 * k2);
+                    for (int k2 = kb + 1; k2 < kMaxKBlocks - 1; k2++) commit(bar_a_dead + 8 * k2);
                 }
               }
             }
             first = false;
-            tc_commit(bar_acc_full + 8 * b);                  // accumulator complete
+            commit(bar_acc_full + 8 * b);                     // accumulator complete
           }
           if (!any)                                           // a one-chunk layer: the idle issuer still sees the layer's phases complete
             for (int kb = 0; kb < nkb; kb++) wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY, P.wait_limit);
@@ -403,6 +447,17 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     PROF_DECL(blockIdx.x == 0 && threadIdx.x == 0);
     const int per0 = P.layer[0].K / 2;                        // model inputs per half row (padded)
     const bool can_prefetch = P.layer[0].K == kBlockK;        // one K-block of inputs: 64 packed registers per thread
+    // Hands an accumulator or a block of A back to the issuers.  One CTA: every row thread arrives on the CTA's barrier.
+    // PAIR: the issuers are the leader's, so the arrival goes to the leader's barrier, one per warp; it publishes no
+    // generic-memory writes (the thread has completed its tensor-memory accesses: tcgen05.wait + fence), so it is relaxed.
+    auto signal = [&](uint32_t bar) {
+      if constexpr (PAIR) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(bar, 0));
+      } else {
+        mbar_arrive(bar);
+      }
+    };
 
     // position of row `row_` in the host arrays, once per stride class of the gather
     auto locate_in = [&](long long row_, bool& live_, long long& p0, long long& p1) {
@@ -443,11 +498,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       tc_fence_before();
       // block 0 last: a waiter that has seen block 0's phase complete has thereby seen the others'
 #pragma unroll
-      for (int k = kMaxKBlocks - 1; k >= 0; k--) mbar_arrive(bar_a_ready + 8 * k);
+      for (int k = kMaxKBlocks - 1; k >= 0; k--) signal(bar_a_ready + 8 * k);
     };
 
     bool prefetched = false;
-    for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    for (long long u = unit0; u < nunits; u += ustep) {
+      const long long tile = PAIR ? 2 * u + crank : u;
       const long long row = tile * kTileM + r;
       const bool live = row < P.nrows;
       if (!prefetched) {
@@ -489,7 +545,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * b);               // the MMA warp may refill this accumulator
+            signal(bar_acc_empty + 8 * b);                    // the MMA warp may refill this accumulator
             if (HAS_SCALE) {
 #pragma unroll
               for (int j = 0; j < 8; j++) {
@@ -566,7 +622,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar_a_ready + 8 * kb2);
+            signal(bar_a_ready + 8 * kb2);
           };
           PROF_ADD(11);
           if (0 < wall) { wait_bar(bar_a_dead + 0, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit); tc_fence_after(); move_block(std::integral_constant<int, 0>{}); }
@@ -584,9 +640,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 }
             }
           }
-          if (wall <= 0 && 0 < nkb2) move_block(std::integral_constant<int, 0>{}); else if (nkb2 <= 0) mbar_arrive(bar_a_ready + 0);
-          if (wall <= 1 && 1 < nkb2) move_block(std::integral_constant<int, 1>{}); else if (nkb2 <= 1) mbar_arrive(bar_a_ready + 8);
-          if (2 < nkb2) move_block(std::integral_constant<int, 2>{}); else mbar_arrive(bar_a_ready + 16);   // blocks the next layer does not have stay in step
+          if (wall <= 0 && 0 < nkb2) move_block(std::integral_constant<int, 0>{}); else if (nkb2 <= 0) signal(bar_a_ready + 0);
+          if (wall <= 1 && 1 < nkb2) move_block(std::integral_constant<int, 1>{}); else if (nkb2 <= 1) signal(bar_a_ready + 8);
+          if (2 < nkb2) move_block(std::integral_constant<int, 2>{}); else signal(bar_a_ready + 16);   // blocks the next layer does not have stay in step
           PROF_ADD(12);
         } else {
           // ---- last layer: bias, output scaling / masks, then straight into the host arrays.  While its MMAs run, the
@@ -596,12 +652,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           if (live) row_to_pos(P.g, row, &ci, &cj, &kk);
           const long long opos0 = ci * P.cout[0].si + cj * P.cout[0].sj + kk * P.cout[0].sk;
           const long long opos1 = ci * P.cout[1].si + cj * P.cout[1].sj + kk * P.cout[1].sk;
-          const bool do_pre = can_prefetch && tile + gridDim.x < ntiles;
+          const bool do_pre = can_prefetch && u + ustep < nunits;
           // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
           // has been moved), in the park's thread-private layout, so no other thread ever touches them.
           static_assert(kBlockK / 2 / 32 == 4 && kSmemChunks >= 4, "the prefetch uses four park slots of 32 inputs per half row");
           if (do_pre) {
-            const long long nrow = (tile + gridDim.x) * kTileM + r;
+            const long long nrow = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM + r;
             bool lv; long long p0, p1;
             locate_in(nrow, lv, p0, p1);
 #pragma unroll 1
@@ -646,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             tmem_ld32(lane_addr + kAccCol0 + b * kChunkN + half * 32, a);
             tmem_ld_wait();
             tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * b);
+            signal(bar_acc_empty + 8 * b);
             float v[32];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
@@ -723,9 +779,11 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     for (int i = 0; i < 2000; i++) __nanosleep(1000);
   }
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();      // neither CTA leaves while its partner can still signal its barriers
   if (warp == 9) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    if constexpr (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -847,7 +905,16 @@ struct TcModel {
   TcLayer layer[kMaxLayers];
   CUtensorMap maps[kMaxLayers];
   bool has_scale = false, f16 = false;
+  bool pair = false;               // run as two-CTA clusters (row-major weights + tensor maps are on the device as well)
 };
+
+// Two-CTA clusters (each SM streams half of the weights) or one CTA per SM: option "tc_pair", else FORTIS_TC_PAIR=0|1.
+static int g_tc_pair = -1;          // -1: FORTIS_TC_PAIR from the environment, else the build's default
+void tc_set_pair_mode(int on) { g_tc_pair = on; }
+bool tc_pair_mode() {
+  static const bool dflt = [] { const char* e = std::getenv("FORTIS_TC_PAIR"); return e ? std::atoi(e) != 0 : FORTIS_TC_PAIR_DEFAULT != 0; }();
+  return g_tc_pair < 0 ? dflt : g_tc_pair != 0;
+}
 
 bool tc_model_supported(const ModelHost& M, std::string* why) {
   auto no = [&](const char* w) { if (why) *why = w; return false; };
@@ -868,6 +935,13 @@ int tc_grid(long long nrows) {
   int sms = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (tc_pair_mode()) {
+    // clusters of two CTAs, a pair of tiles per cluster and wave; the same evening-out over the clusters
+    const long long units = (tiles + 1) / 2, slots = sms / 2 > 0 ? sms / 2 : 1;
+    if (units <= slots) return (int)(2 * (units > 0 ? units : 1));
+    const long long waves = (units + slots - 1) / slots;
+    return (int)(2 * ((units + waves - 1) / waves));
+  }
   if (tiles <= sms) return (int)(tiles > 0 ? tiles : 1);
   // The launch lasts as long as the CTA with the most tiles: waves = ceil(tiles / SMs).  With that fixed, use only as
   // many CTAs as give every one of them `waves` tiles (384 tiles: 128 CTAs x 3 instead of 88 x 3 + 60 x 2): the idle SMs
@@ -890,18 +964,19 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
   (void)s;
   std::string why;
   if (!tc_model_supported(M, &why)) { if (err) *err = why; return nullptr; }
-#if !FORTIS_TC_TILED_W
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) { if (err) *err = "cuTensorMapEncodeTiled is not available from the driver"; return nullptr; }
-#endif
+  const bool pair = tc_pair_mode();
+  const bool want_maps = pair || !FORTIS_TC_TILED_W;
+  EncodeTiledFn enc = want_maps ? encode_fn() : nullptr;
+  if (want_maps && !enc) { if (err) *err = "cuTensorMapEncodeTiled is not available from the driver"; return nullptr; }
   TcModel* m = new TcModel();
+  m->pair = pair;
   m->nlayers = (int)M.layers.size(); m->n_in = M.n_in(); m->n_out = M.n_out();
   auto fail = [&](const std::string& w) { if (err) *err = w; tc_model_destroy(m); return (TcModel*)nullptr; };
   for (int l = 0; l < m->nlayers; l++) {
     const LayerHost& L = M.layers[l];
     PackedLayer Q;
     std::vector<uint16_t> wb;
-    const bool prepacked = FORTIS_TC_TILED_W && M.packed_precision == precision && l < (int)M.packed.size() &&
+    const bool prepacked = FORTIS_TC_TILED_W && !pair && M.packed_precision == precision && l < (int)M.packed.size() &&
                            M.packed[l].K == round_up(L.cin, kBlockK) &&
                            M.packed[l].N == (l + 1 < m->nlayers ? round_up(L.cout, kBlockK) : round_up(L.cout, kChunkN));
     if (prepacked) Q = M.packed[l];                        // the blob carries this precision's stage images
@@ -909,10 +984,12 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     const int K = Q.K, N = Q.N;
     const std::vector<uint16_t>& wt = Q.image;
     const std::vector<float>&bias = Q.bias, &scale = Q.scale;
-    // only the form this build streams goes to the device
+    // only the form this build streams goes to the device: the stage images, or (tensor copies: the two-CTA form) the
+    // row-major weights
     void *dw = nullptr, *dwt = nullptr; float *db = nullptr, *ds = nullptr;
-    const std::vector<uint16_t>& image = FORTIS_TC_TILED_W ? wt : wb;
-    void** slot = FORTIS_TC_TILED_W ? &dwt : &dw;
+    const bool tiled = FORTIS_TC_TILED_W && !pair;
+    const std::vector<uint16_t>& image = tiled ? wt : wb;
+    void** slot = tiled ? &dwt : &dw;
     if (cudaMalloc(slot, image.size() * 2) != cudaSuccess || cudaMalloc(&db, N * 4) != cudaSuccess)
       return fail("out of device memory for packed weights");
     m->w.push_back(*slot); m->bias.push_back(db);
@@ -926,17 +1003,18 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     TcLayer& T = m->layer[l];
     T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds; T.wtiled = (const uint8_t*)dwt;
     T.slope = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;      // act(v) = max(v, v * slope)
-#if !FORTIS_TC_TILED_W
-    // W[N][K] viewed as [K/64][N][64]: one box of {64 k, 64 rows, 4 k-blocks} lands in shared memory as four
-    // consecutive 64 x 64 sub-tiles, each in the 128-byte-swizzled K-major layout the MMA descriptor expects
-    const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
-    const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
-    const cuuint32_t box[3] = {64, (cuuint32_t)kChunkN, (cuuint32_t)(kStageK / 64)};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = enc(&m->maps[l], precision == PREC_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
-#endif
+    if (!tiled) {
+      // W[N][K] viewed as [K/64][N][64]: one box of {64 k, 64 rows (32: a CTA's half in the two-CTA form), 4 k-blocks}
+      // lands in shared memory as four consecutive sub-tiles, each in the 128-byte-swizzled K-major layout the MMA
+      // descriptor expects
+      const cuuint64_t dims[3] = {64, (cuuint64_t)N, (cuuint64_t)(K / 64)};
+      const cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+      const cuuint32_t box[3] = {64, (cuuint32_t)(pair ? kChunkN / 2 : kChunkN), (cuuint32_t)(kStageK / 64)};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const CUresult r = enc(&m->maps[l], precision == PREC_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dw, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    }
   }
   auto up = [&](const std::vector<float>& v) -> float* {
     if (v.empty()) return nullptr;
@@ -946,9 +1024,12 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     return d;
   };
   m->in_div = up(M.in_div); m->out_mul = up(M.out_mul); m->relu_mask = up(M.relu_mask);
-  if (cudaFuncSetAttribute(mlp_tc_fused_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(mlp_tc_fused_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
-      cudaFuncSetAttribute(mlp_tc_fused_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+  if (cudaFuncSetAttribute(mlp_tc_fused_kernel<false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<false, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+      cudaFuncSetAttribute(mlp_tc_fused_kernel<false, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
     return fail("cannot reserve " + std::to_string(kSmemBytes) + " bytes of shared memory for the tensor-core kernel");
   m->has_scale = precision == PREC_FP8W;
   m->f16 = precision == PREC_FP16;
@@ -989,9 +1070,19 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
     cudaMemsetAsync(dprof, 0, 32 * sizeof(long long), s);
     P.prof = dprof;
   }
-  if (m->has_scale) mlp_tc_fused_kernel<true, false><<<grid, kThreads, kSmemBytes, s>>>(P);
-  else if (m->f16) mlp_tc_fused_kernel<false, true><<<grid, kThreads, kSmemBytes, s>>>(P);
-  else mlp_tc_fused_kernel<false, false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  if (m->pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (m->has_scale) cudaLaunchKernelEx(&cfg, mlp_tc_fused_kernel<true, false, true>, P);
+    else if (m->f16) cudaLaunchKernelEx(&cfg, mlp_tc_fused_kernel<false, true, true>, P);
+    else cudaLaunchKernelEx(&cfg, mlp_tc_fused_kernel<false, false, true>, P);
+  } else if (m->has_scale) mlp_tc_fused_kernel<true, false, false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  else if (m->f16) mlp_tc_fused_kernel<false, true, false><<<grid, kThreads, kSmemBytes, s>>>(P);
+  else mlp_tc_fused_kernel<false, false, false><<<grid, kThreads, kSmemBytes, s>>>(P);
   if (want_prof) {
     long long h[32];
     cudaStreamSynchronize(s);

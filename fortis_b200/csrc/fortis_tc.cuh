@@ -256,6 +256,22 @@ __device__ __forceinline__ void tc_mma_ss_pair(uint32_t d_tmem, uint64_t a_desc,
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "n"(IDESC), "r"(accumulate) : "memory");
 }
 
+// the same with A in tensor memory: each CTA's 128 rows of A sit at the same columns of its own tensor memory
+template <uint32_t IDESC>
+__device__ __forceinline__ void tc_mma_ts_acc_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, 1;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC) : "memory");
+}
+template <uint32_t IDESC>
+__device__ __forceinline__ void tc_mma_ts_first_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\telect.sync _|p, 0xffffffff;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+      "@p tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, q;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "n"(IDESC), "r"(accumulate) : "memory");
+}
+
 // instruction descriptor: D = f32, A = B = bf16, both K-major
 constexpr uint32_t idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);

@@ -196,6 +196,34 @@ def test_layers_wider_than_the_fused_kernel_run_layer_by_layer(host, capfd):
     assert "one by one" in capfd.readouterr().err
 
 
+@pytest.mark.parametrize("precision", ["bf16", "fp8w", "fp16"])
+@pytest.mark.parametrize("ncol", [100, 1000, 40000])
+def test_two_cta_clusters_give_the_same_bits(host, precision, ncol):
+    """Option tc_pair: the kernel as clusters of two CTAs (each SM streams half of the weights).  Same arithmetic in the
+    same order, so outputs and step checksum are bit-identical to the one-CTA form: a single tile (the partner CTA idle
+    rows), an even and an odd number of tiles, and more pairs than clusters (CTAs with several tiles)."""
+    G, S, Lp, K, gin, sout, layers = column_case(ncol, seed=21)
+    blob = fortis_b200.write_blob(layers)
+    res = []
+    for pair in (0, 1):
+        host.reset()
+        host.configure(gather=G, scatter=S, loop=Lp)
+        host.load_model(blob)
+        host.option("precision", precision)
+        host.option("checksum", 1)
+        host.option("tc_pair", pair)
+        out = [np.zeros_like(a) for a in sout]
+        host.step(gin, out)
+        first = [a.copy() for a in out]
+        host.step(gin, out)
+        assert all(np.array_equal(a, b) for a, b in zip(out, first)), "the second call differs (pair %d)" % pair
+        assert host.L.fortis_device_status() == 0
+        res.append((out, host.step_checksum()))
+    assert all(np.array_equal(a, b) for a, b in zip(res[0][0], res[1][0]))
+    assert res[0][1] == res[1][1]
+    assert float(np.abs(np.concatenate([a.ravel() for a in res[1][0]])).sum()) > 0.0
+
+
 @pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_TC_SWEEP", "10"))))
 def test_random_shapes_against_the_low_precision_model(host, seed):
     """Random depths (1-7 layers), widths (1-768, so every padding and chunk count), row counts (1-4000, so ragged
