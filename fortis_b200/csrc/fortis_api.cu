@@ -752,7 +752,7 @@ void run_step_kernels(const StepArgs& A) {
                     L.store_by_slot = s.S.store_by_slot; std::memcpy(L.cout, s.S.cls, sizeof L.cout); }
     L.Y = fuse_out ? nullptr : s.dout;
     L.g = g;
-    ensure_aux(tc_grid(rows));
+    ensure_aux(tc_grid(s.tc, rows));
     L.partials = (fuse_out && s.want_checksum) ? s.d_partials : nullptr;
     L.sum = L.partials ? s.d_sum : nullptr; L.done = s.d_done;
     L.status = s.d_status;

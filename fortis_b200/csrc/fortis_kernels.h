@@ -109,9 +109,8 @@ struct TcLaunch {
   double* sum; unsigned int* done;                   // optional: fold the partials into *sum inside the kernel (done: zeroed counter)
   int* status;                                       // device word: 0 ok, else the code of the wait that gave up
 };
-int tc_grid(long long nrows);
-void tc_set_pair_mode(int on);                      // 1 / 0: two-CTA clusters or one CTA per SM for models created from now on; -1: the default
-bool tc_pair_mode();
+int tc_grid(const TcModel* m, long long nrows);
+void tc_set_pair_mode(int on);                      // 1 / 0: two-CTA clusters or one CTA per SM for models created from now on; -1: the default (clusters)
 bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err);
 
 // ---- fp32-class Linear layers on the tensor cores, three TF32 MMAs per product (fortis_mlp_f32tc.cu) ----------------

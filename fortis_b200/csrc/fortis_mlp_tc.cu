@@ -5,7 +5,9 @@
 // bias/activation epilogue kernel per layer (runtime/fortis_rt.c:45-75, compiler/FortisFuse.cpp:616-624, 687-760),
 // with fortis_gather_k in front and fortis_scatter_k behind (driver/fortis_gather_emit.py:52-62, 75-83).
 //
-// One persistent CTA per SM processes tiles of 128 columns (rows of the model batch).  Per tile and layer
+// One persistent CTA per SM processes tiles of 128 columns (rows of the model batch); by default the CTAs run as
+// clusters of two (cta_group::2) whose leader issues every MMA over both CTAs' tiles, each CTA streaming half of the
+// weights (see the kernel's template parameter PAIR).  Per tile and layer
 //     D[128 x N] = A[128 x K] . W[N x K]^T,  N processed in chunks of 64 output features.
 //   * A (the layer's input activations, bf16) lives in TENSOR MEMORY: lane = row, two K values per 32-bit column
 //     (K <= 768 -> 384 columns).  The MMAs take A from TMEM and B from shared memory, so shared-memory read
@@ -21,7 +23,8 @@
 //     slot is a coalesced load); the last layer's epilogue stores straight into the host arrays and accumulates
 //     the fp64 checksum.  This fusion is table-driven and covers fp32 arrays without lifted expressions; any other
 //     descriptor is served by the standalone gather / scatter kernels writing X / reading Y around this kernel.
-// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 96 KB parked chunks + 4 x 32 KB weight ring.
+// TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 3 x 32 KB weight ring (one CTA per
+// SM), 160 KB parked chunks + 4 x 16 KB ring (CTA of a pair).
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word, raises a CTA-wide
 // abort flag that turns all later waits into no-ops, and the CTA still frees its tensor memory and returns.
@@ -71,9 +74,6 @@ constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 
 #ifndef FORTIS_TC_DEEP_RING
 #define FORTIS_TC_DEEP_RING 0
 #endif
-#ifndef FORTIS_TC_PAIR_DEFAULT
-#define FORTIS_TC_PAIR_DEFAULT 0
-#endif
 constexpr bool kRegRealloc = FORTIS_TC_DEEP_RING != 0;
 #ifdef FORTIS_TC_INLINE_WAIT
 constexpr bool kInlineWait = true;
@@ -92,6 +92,12 @@ constexpr int kIssuers = 2;                 // MMA-issuing warps: issuer w owns 
 constexpr int kThreads = kEpiThreads + (kRegRealloc ? 128 : 96);   // + TMA warp + two MMA warps (+ an idle warp: register re-allocation works per warpgroup)
 constexpr int kParkBytes = kSmemChunks * kTileM * kChunkN * 2;      // 128 KB
 constexpr int kRingBytes = kStages * kStageBytes;                   // 96 KB
+#ifndef FORTIS_TC_PAIR_PARK
+#define FORTIS_TC_PAIR_PARK 10
+#endif
+constexpr int kPairParkChunks = FORTIS_TC_PAIR_PARK;                // two-CTA form: parked chunks in shared memory (8 or 10) ...
+constexpr int kPairStages = (kParkBytes + kRingBytes) / (kStageBytes / 2) - kPairParkChunks;   // ... and the 16 KB stages that fit beside them (6 or 4)
+static_assert(kPairStages >= 3 && kPairStages <= 6 && kPairParkChunks <= 12, "two-CTA form: ring depth");
 constexpr int kBarBytes = 384;             // barriers in the first 256 bytes, then the tensor-memory base, the abort flag and the checksum scratch
 constexpr int kFastIn = 256, kFastOut = 128;          // widest model input / output the fast I/O tables hold
 constexpr int kTabBytes = kFastIn * 5 + kFastOut * 5 + 2 * kMaxArrays * 8;   // uint32 offset + uint8 code per slot / store, array bases
@@ -110,6 +116,7 @@ struct TcLayer {
   const float* bias;       // [N] padded with zeros
   const float* scale;      // [N] per-output-channel dequantisation scale (fp8 weights) or null
   const uint8_t* wtiled;   // the weights as consecutive 32 KB stage images, [chunk of 64 features][256-wide K-block]
+  const uint8_t* wdev;     // whichever form of the 16-bit weights the kernel streams (N x K x 2 bytes), for the L2 prefetch
 };
 
 // Stride class of a fast gather / scatter: element offset of a row = ci*si + cj*sj + kk*sk
@@ -138,6 +145,7 @@ struct TcParams {
   int* status;
   unsigned int wait_limit;               // polls before a barrier wait gives up
   int test_skip_stage;                   // test only: CTA 0 never loads its first weight stage
+  int no_l2_prefetch;                    // FORTIS_TC_NO_L2_PREFETCH: do not ask for the weights to be brought into L2 at kernel start
   long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
   // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
   // (array, class, constant offset) triples are unpacked into shared memory once per CTA
@@ -219,18 +227,24 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 template <bool HAS_SCALE, bool F16, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_constant__ TcParams P) {
   constexpr uint32_t kIdesc = MlpIdesc<F16, PAIR>::value;
-  constexpr int kStg = PAIR ? 2 * kStages : kStages;                 // ring depth in stages
+  // Ring and park: one CTA per SM keeps 3 stages of 32 KB and parks 8 output chunks in shared memory (4 in registers).
+  // A CTA of a pair streams half the bytes, so 4 stages of 16 KB cover the same time; the 32 KB saved park two more
+  // chunks in shared memory (2 in registers), which takes the epilogue out of register spilling.
+  constexpr int kStg = PAIR ? kPairStages : kStages;                 // ring depth in stages
+  constexpr int kPark = PAIR ? kPairParkChunks : kSmemChunks;        // parked chunks held in shared memory; the rest in registers
+  constexpr int kParkB = kPark * kTileM * kChunkN * 2, kRingB = kStg * (PAIR ? kStageBytes / 2 : kStageBytes);
+  static_assert(kParkB + kRingB <= kParkBytes + kRingBytes, "the pair form must fit the same shared memory");
   constexpr int kStgBytes = PAIR ? kStageBytes / 2 : kStageBytes;    // this CTA's part of a stage
   constexpr int kSubB = PAIR ? kSubBytes / 2 : kSubBytes;            // one 64-wide k sub-tile of it
   constexpr int kRowArrivals = PAIR ? 16 : kEpiThreads;              // arrivals that hand an accumulator / an A block back
   extern __shared__ __align__(1024) uint8_t smem[];
-  const uint32_t base = smem_u32(smem);                         // parked chunks: kSmemChunks x 16 KB at offset 0
+  const uint32_t base = smem_u32(smem);                         // parked chunks: kPark x 16 KB at offset 0
   if (base & 1023u) {                                           // the swizzled weight stages need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(P.status, 0, ST_SMEM_ALIGN);
     return;
   }
-  const uint32_t ring = base + kParkBytes;                      // kStages x 32 KB
-  const uint32_t bars = ring + kRingBytes;
+  const uint32_t ring = base + kParkB;                      // kStages x 32 KB
+  const uint32_t bars = ring + kRingB;
   // barrier block: full [kIssuers][kStages] | empty [kStages] | acc_full [2] | acc_empty [2] | a_ready [3] | a_dead [2]
   // within the first 256 bytes; tmem base 256, abort flag 260, checksum scratch [272,336).
   // Every stage has one "full" barrier PER ISSUER: a parity wait can only tell a barrier's current phase from the
@@ -240,9 +254,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kIssuers * kStg;
   const uint32_t bar_acc_full = bar_empty + 8 * kStg, bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
-  uint32_t* tmem_slot = (uint32_t*)(smem + kParkBytes + kRingBytes + 256);
-  volatile int* abort_flag = (volatile int*)(smem + kParkBytes + kRingBytes + 260);
-  uint32_t* s_off = (uint32_t*)(smem + kParkBytes + kRingBytes + kBarBytes);          // [kFastIn] input slot offsets
+  uint32_t* tmem_slot = (uint32_t*)(smem + kParkB + kRingB + 256);
+  volatile int* abort_flag = (volatile int*)(smem + kParkB + kRingB + 260);
+  uint32_t* s_off = (uint32_t*)(smem + kParkB + kRingB + kBarBytes);          // [kFastIn] input slot offsets
   uint32_t* o_off = s_off + kFastIn;                                                  // [kFastOut] store offsets
   uint8_t* s_code = (uint8_t*)(o_off + kFastOut);                                     // array | class << 7, 0xFF: none
   uint8_t* o_code = s_code + kFastIn;
@@ -315,6 +329,18 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     // warps) keeps kRegsProducer registers per thread and hands the rest to the two row warpgroups, whose threads park
     // six output chunks (96 registers) next to the epilogue's working set.
     if constexpr (kRegRealloc) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
+    if (warp == 9 + kIssuers - 1 && !P.no_l2_prefetch) {
+      // A step usually starts with the weights out of L2 (the host's arrays have streamed through it since the last
+      // step), and every CTA then asks for the same stage at the same moment, one memory latency per stage.  Each CTA
+      // asks for its 1/gridDim slice of every layer's weights to be brought into L2 now, while the first inputs are
+      // gathered.
+      for (int l = 0; l < P.nlayers; l++) {
+        const unsigned long long bytes = (unsigned long long)P.layer[l].N * P.layer[l].K * 2;
+        const unsigned long long per = ((bytes + gridDim.x - 1) / gridDim.x + 127ull) & ~127ull;
+        const unsigned long long off = per * blockIdx.x;
+        if (off < bytes) l2_prefetch(P.layer[l].wdev + off, (uint32_t)(bytes - off < per ? bytes - off : per));
+      }
+    }
     if (warp == 8) {
       // ---------------------------------------------------------------- TMA producer (whole warp, one lane issues)
       uint32_t s = 0, ph = 0, acc_it = 0;
@@ -527,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         const float slope = L.slope;
         const uint32_t lph = lay_it & 1;
         if (!last) {
-          uint32_t kept[(kMaxChunks - kSmemChunks) * 16];     // this thread's parked chunks beyond those in shared memory (16-bit pairs)
+          uint32_t kept[(kMaxChunks - kPark) * 16];     // this thread's parked chunks beyond those in shared memory (16-bit pairs)
           // epilogue of one chunk: accumulator -> (x scale) + bias -> activation -> 16 packed 16-bit pairs
           auto chunk_epilogue = [&](int c, uint32_t (&pk)[16]) {
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
@@ -576,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           const int lastc = nchunks - 1;
           // all chunks but the last: those parked in shared memory in a rolled loop (the address depends on c only
           // arithmetically), those parked in registers unrolled so that `kept` is indexed statically
-          const int nsm = lastc < kSmemChunks ? lastc : kSmemChunks;
+          const int nsm = lastc < kPark ? lastc : kPark;
 #pragma unroll 1
           for (int c = 0; c < nsm; c++) {
             uint32_t pk[16];
@@ -584,12 +610,12 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             park_smem(c, pk);
           }
 #pragma unroll
-          for (int c = kSmemChunks; c < kMaxChunks; c++) {
+          for (int c = kPark; c < kMaxChunks; c++) {
             if (c < lastc) {
               uint32_t pk[16];
               chunk_epilogue(c, pk);
 #pragma unroll
-              for (int j = 0; j < 16; j++) kept[(c - kSmemChunks) * 16 + j] = pk[j];
+              for (int j = 0; j < 16; j++) kept[(c - kPark) * 16 + j] = pk[j];
             }
           }
           // The next layer's A, K-block by K-block (four output chunks each).  A block of A may be overwritten once
@@ -607,7 +633,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             for (int c4 = 0; c4 < 4; c4++) {
               const int c = 4 * kb2 + c4;                     // compile-time after unrolling
               uint32_t pk[16];
-              if (c < kSmemChunks) {
+              if (c < kPark) {
                 const uint8_t* src = smem + c * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
 #pragma unroll
                 for (int p = 0; p < 4; p++) {
@@ -616,7 +642,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
                 }
               } else {
 #pragma unroll
-                for (int j = 0; j < 16; j++) pk[j] = kept[(c - kSmemChunks) * 16 + j];
+                for (int j = 0; j < 16; j++) pk[j] = kept[(c - kPark) * 16 + j];
               }
               tmem_st16(lane_addr + (uint32_t)(c * (kChunkN / 2) + half * 16), pk);
             }
@@ -630,13 +656,13 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           {
             uint32_t pk[16];
             chunk_epilogue(lastc, pk);                        // waits for the layer's last accumulator: every MMA has retired
-            if (lastc < kSmemChunks) park_smem(lastc, pk);
+            if (lastc < kPark) park_smem(lastc, pk);
             else {
 #pragma unroll
-              for (int cc = kSmemChunks; cc < kMaxChunks; cc++)
+              for (int cc = kPark; cc < kMaxChunks; cc++)
                 if (lastc == cc) {
 #pragma unroll
-                  for (int j = 0; j < 16; j++) kept[(cc - kSmemChunks) * 16 + j] = pk[j];
+                  for (int j = 0; j < 16; j++) kept[(cc - kPark) * 16 + j] = pk[j];
                 }
             }
           }
@@ -655,7 +681,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           const bool do_pre = can_prefetch && u + ustep < nunits;
           // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
           // has been moved), in the park's thread-private layout, so no other thread ever touches them.
-          static_assert(kBlockK / 2 / 32 == 4 && kSmemChunks >= 4, "the prefetch uses four park slots of 32 inputs per half row");
+          static_assert(kBlockK / 2 / 32 == 4 && kPark >= 4, "the prefetch uses four park slots of 32 inputs per half row");
           if (do_pre) {
             const long long nrow = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM + r;
             bool lv; long long p0, p1;
@@ -746,7 +772,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     }
     if (P.partials) {
       // per-CTA checksum partial in a fixed order: shuffle tree per warp, then warp results in index order
-      double* wsum = (double*)(smem + kParkBytes + kRingBytes + 272);
+      double* wsum = (double*)(smem + kParkB + kRingB + 272);
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) csum += __shfl_down_sync(0xffffffffu, csum, o);
       if (lane == 0) wsum[warp] = csum;
@@ -908,12 +934,17 @@ struct TcModel {
   bool pair = false;               // run as two-CTA clusters (row-major weights + tensor maps are on the device as well)
 };
 
-// Two-CTA clusters (each SM streams half of the weights) or one CTA per SM: option "tc_pair", else FORTIS_TC_PAIR=0|1.
-static int g_tc_pair = -1;          // -1: FORTIS_TC_PAIR from the environment, else the build's default
+// Two-CTA clusters (each SM streams half of the weights; the default) or one CTA per SM: option "tc_pair", else
+// FORTIS_TC_PAIR=0|1.  Measured on the 244-768x4-128 net, 49,152 to 2^20 columns: the cluster form is 9-16 % faster in
+// bf16 / fp16 and 8-9 % faster with FP8 weights.
+static int g_tc_pair = -1;
 void tc_set_pair_mode(int on) { g_tc_pair = on; }
-bool tc_pair_mode() {
-  static const bool dflt = [] { const char* e = std::getenv("FORTIS_TC_PAIR"); return e ? std::atoi(e) != 0 : FORTIS_TC_PAIR_DEFAULT != 0; }();
-  return g_tc_pair < 0 ? dflt : g_tc_pair != 0;
+bool tc_pair_mode(int precision) {
+  static const int env = [] { const char* e = std::getenv("FORTIS_TC_PAIR"); return e ? (std::atoi(e) != 0 ? 1 : 0) : -1; }();
+  if (g_tc_pair >= 0) return g_tc_pair != 0;
+  if (env >= 0) return env != 0;
+  (void)precision;
+  return true;
 }
 
 bool tc_model_supported(const ModelHost& M, std::string* why) {
@@ -930,14 +961,36 @@ bool tc_model_supported(const ModelHost& M, std::string* why) {
   return true;
 }
 
-int tc_grid(long long nrows) {
+// how many two-CTA clusters of the kernel the device holds at once (the SMs of a cluster share a GPC, so this can be
+// fewer than half the SM count); 0 when the query fails
+int tc_max_clusters() {
+  static int cached[16] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 0;
+  if (cached[dev]) return cached[dev] > 0 ? cached[dev] : 0;
+  cudaFuncSetAttribute(mlp_tc_fused_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 148); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, mlp_tc_fused_kernel<false, false, true>, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = -1; }
+  cached[dev] = n;
+  if (std::getenv("FORTIS_TC_DEBUG")) std::fprintf(stderr, "fortis: %d two-CTA clusters of the fused MLP kernel fit the device\n", n);
+  return n > 0 ? n : 0;
+}
+
+int tc_grid(const TcModel* m, long long nrows) {
   const long long tiles = (nrows + kTileM - 1) / kTileM;
   int sms = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (tc_pair_mode()) {
+  if (m && m->pair) {
     // clusters of two CTAs, a pair of tiles per cluster and wave; the same evening-out over the clusters
-    const long long units = (tiles + 1) / 2, slots = sms / 2 > 0 ? sms / 2 : 1;
+    const int fit = tc_max_clusters();
+    const long long units = (tiles + 1) / 2, slots = fit > 0 ? fit : (sms / 2 > 0 ? sms / 2 : 1);
     if (units <= slots) return (int)(2 * (units > 0 ? units : 1));
     const long long waves = (units + slots - 1) / slots;
     return (int)(2 * ((units + waves - 1) / waves));
@@ -964,7 +1017,7 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
   (void)s;
   std::string why;
   if (!tc_model_supported(M, &why)) { if (err) *err = why; return nullptr; }
-  const bool pair = tc_pair_mode();
+  const bool pair = tc_pair_mode(precision);
   const bool want_maps = pair || !FORTIS_TC_TILED_W;
   EncodeTiledFn enc = want_maps ? encode_fn() : nullptr;
   if (want_maps && !enc) { if (err) *err = "cuTensorMapEncodeTiled is not available from the driver"; return nullptr; }
@@ -1002,6 +1055,7 @@ TcModel* tc_model_create(const ModelHost& M, int precision, cudaStream_t s, std:
     m->scale.push_back(ds);
     TcLayer& T = m->layer[l];
     T.K = K; T.N = N; T.n_real = L.cout; T.act = L.act; T.bias = db; T.scale = ds; T.wtiled = (const uint8_t*)dwt;
+    T.wdev = (const uint8_t*)*slot;
     T.slope = L.act == ACT_NONE ? 1.f : L.act == ACT_RELU ? 0.f : L.slope;      // act(v) = max(v, v * slope)
     if (!tiled) {
       // W[N][K] viewed as [K/64][N][64]: one box of {64 k, 64 rows (32: a CTA's half in the two-CTA form), 4 k-blocks}
@@ -1056,9 +1110,11 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   P.store_by_slot = L.store_by_slot;
   P.wait_limit = g_tc_test.wait_limit ? g_tc_test.wait_limit : kWaitLimit;
   P.test_skip_stage = g_tc_test.skip_stage;
+  static const bool no_prefetch = std::getenv("FORTIS_TC_NO_L2_PREFETCH") != nullptr;
+  P.no_l2_prefetch = no_prefetch;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
-  const int grid = tc_grid(nrows);
+  const int grid = tc_grid(m, nrows);
 #ifdef FORTIS_TC_PROF
   static const bool want_prof = std::getenv("FORTIS_TC_PROF") != nullptr;
 #else

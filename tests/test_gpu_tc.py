@@ -200,7 +200,7 @@ def test_layers_wider_than_the_fused_kernel_run_layer_by_layer(host, capfd):
 @pytest.mark.parametrize("ncol", [100, 1000, 40000])
 def test_two_cta_clusters_give_the_same_bits(host, precision, ncol):
     """Option tc_pair: the kernel as clusters of two CTAs (each SM streams half of the weights).  Same arithmetic in the
-    same order, so outputs and step checksum are bit-identical to the one-CTA form: a single tile (the partner CTA idle
+    same order, so the outputs are bit-identical to the one-CTA form: a single tile (the partner CTA has no live
     rows), an even and an odd number of tiles, and more pairs than clusters (CTAs with several tiles)."""
     G, S, Lp, K, gin, sout, layers = column_case(ncol, seed=21)
     blob = fortis_b200.write_blob(layers)
@@ -220,7 +220,8 @@ def test_two_cta_clusters_give_the_same_bits(host, precision, ncol):
         assert host.L.fortis_device_status() == 0
         res.append((out, host.step_checksum()))
     assert all(np.array_equal(a, b) for a, b in zip(res[0][0], res[1][0]))
-    assert res[0][1] == res[1][1]
+    # the checksum adds the same values grouped by CTA, and the two forms give a CTA different tiles
+    assert abs(res[0][1] - res[1][1]) <= 1e-12 * abs(res[0][1])
     assert float(np.abs(np.concatenate([a.ravel() for a in res[1][0]])).sum()) > 0.0
 
 
