@@ -71,6 +71,9 @@ constexpr int kSubBytes = kChunkN * 64 * 2;          // one 64 x 64 sub-tile, 8 
 #ifndef FORTIS_TC_TILED_W
 #define FORTIS_TC_TILED_W 1
 #endif
+#ifndef FORTIS_TC_GATHER64
+#define FORTIS_TC_GATHER64 1
+#endif
 #ifndef FORTIS_TC_DEEP_RING
 #define FORTIS_TC_DEEP_RING 0
 #endif
@@ -181,13 +184,6 @@ template <bool F16> __device__ __forceinline__ uint32_t pack16(float lo, float h
 
 __device__ __forceinline__ float act_f(float v, float slope) { return fmaxf(v, v * slope); }
 
-// A 16-byte read-only load that stays where it is written: the compiler hoists plain loads to the top of the epilogue,
-// where they would be live next to the parked chunks
-__device__ __forceinline__ float4 ldg4_here(const float* p) {
-  float4 v;
-  asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-  return v;
-}
 
 // A model input is read once per step: keep it out of L1, which is small beside 224 KB of shared memory and has to hold
 // the bias and scale vectors every chunk epilogue reads (measured in one call against the plain load: 0.2253 -> 0.2232 ms
@@ -518,6 +514,28 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
       for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
     };
+    // the same for inputs q0 .. q0 + 63 with all 64 loads issued before the first is used
+    auto gather_two_groups = [&](long long row_, bool live_, long long p0, long long p1, int q0, uint32_t (&pka)[16], uint32_t (&pkb)[16]) {
+      float v[64];
+      if (P.fast_in) {
+#pragma unroll
+        for (int j = 0; j < 64; j++) {
+          const uint32_t code = s_code[q0 + j];
+          v[j] = 0.f;
+          if (live_ && code != 0xFF)
+            v[j] = ldg_stream(s_base_in[code & 0x7F] + ((long long)s_off[q0 + j] + ((code & 0x80) ? p1 : p0)));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; j++) v[j] = (live_ && q0 + j < P.n_in) ? ldg_stream(P.X + row_ * P.n_in + q0 + j) : 0.f;
+      }
+      if (P.in_div) {
+#pragma unroll
+        for (int j = 0; j < 64; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j++) { pka[j] = pack16<F16>(v[2 * j], v[2 * j + 1]); pkb[j] = pack16<F16>(v[32 + 2 * j], v[33 + 2 * j]); }
+    };
     // layer 0's A is complete: release all K-block barriers (blocks the layer does not have stay in step)
     auto release_layer0 = [&]() {
       tmem_st_wait();
@@ -686,6 +704,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             const long long nrow = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM + r;
             bool lv; long long p0, p1;
             locate_in(nrow, lv, p0, p1);
+            // 64 loads in flight per thread (no parked chunk is live in registers here), two batches per tile
+#if !FORTIS_TC_GATHER64
 #pragma unroll 1
             for (int g = 0; g < 4; g++) {
               uint32_t pk[16];
@@ -695,9 +715,25 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               for (int p = 0; p < 4; p++)
                 *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[4 * p], pk[4 * p + 1], pk[4 * p + 2], pk[4 * p + 3]);
             }
+#else
+#pragma unroll 1
+            for (int g2 = 0; g2 < 2; g2++) {
+              uint32_t pk[2][16];
+              gather_two_groups(nrow, lv, p0, p1, half * per0 + 64 * g2, pk[0], pk[1]);
+#pragma unroll
+              for (int h = 0; h < 2; h++) {
+                uint8_t* dst = smem + (2 * g2 + h) * (kTileM * kChunkN * 2) + half * (kTileM * 64) + r * 16;
+#pragma unroll
+                for (int p = 0; p < 4; p++)
+                  *reinterpret_cast<uint4*>(dst + p * (kTileM * 16)) = make_uint4(pk[h][4 * p], pk[h][4 * p + 1], pk[h][4 * p + 2], pk[h][4 * p + 3]);
+              }
+            }
+#endif
           }
           for (int c = 0; c < nchunks; c++) {
-            if (c == nchunks - 1 && do_pre) {
+            // From the epilogue of chunk n - 2 on, both issuers' last chunks can run (their accumulators were read by
+            // the epilogues before), so the layer's last MMAs on K-block 0 retire without this thread's help.
+            if (c == (nchunks < 2 ? nchunks - 1 : nchunks - 2) && do_pre) {
               wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit);
               tc_fence_after();
 #pragma unroll 1
