@@ -89,6 +89,15 @@ __device__ __forceinline__ double scatter_value(const IoPlanDev& P, const ArrayT
 }
 
 __device__ __forceinline__ void row_to_pos(const RowGeom& g, long long row, long long* ci, long long* cj, long long* kk) {
+  if (((unsigned long long)row | (unsigned long long)g.count | (unsigned long long)g.ni) >> 31 == 0) {
+    // everything fits 32 bits (the usual case): four 32-bit divisions instead of four 64-bit ones
+    const unsigned r = (unsigned)row, cnt = (unsigned)g.count, ni = (unsigned)g.ni;
+    const unsigned k = r / cnt, col = r - k * cnt, j = col / ni;
+    *kk = g.kk0 + k;
+    *ci = col - j * ni;
+    *cj = j;
+    return;
+  }
   const long long col = row % g.count;
   *kk = g.kk0 + row / g.count;
   *ci = col % g.ni;

@@ -109,7 +109,7 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccCol0 = 384;
 
 // status codes (which wait gave up)
-enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6, ST_A_DEAD = 7 };
+enum { ST_OK = 0, ST_FULL = 1, ST_EMPTY = 2, ST_ACC_FULL = 3, ST_ACC_EMPTY = 4, ST_A_READY = 5, ST_SMEM_ALIGN = 6, ST_A_DEAD = 7, ST_IN = 8 };
 
 struct TcLayer {
   int K, N;                // padded: K multiple of 256, N multiple of 64 (hidden: multiple of 256)
@@ -149,6 +149,7 @@ struct TcParams {
   unsigned int wait_limit;               // polls before a barrier wait gives up
   int test_skip_stage;                   // test only: CTA 0 never loads its first weight stage
   int no_l2_prefetch;                    // FORTIS_TC_NO_L2_PREFETCH: do not ask for the weights to be brought into L2 at kernel start
+  int no_stage_inputs;                   // FORTIS_TC_NO_STAGE_INPUTS: fetch the next tile's inputs element by element
   long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
   // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
   // (array, class, constant offset) triples are unpacked into shared memory once per CTA
@@ -199,7 +200,11 @@ __device__ __forceinline__ float ldg_stream(const float* p) {
 #ifdef FORTIS_TC_PROF
 #define PROF_DECL(who) const bool prof_who = P.prof && (who); long long prof_t = clock64()
 #define PROF_ADD(slot) do { if (prof_who) { const long long n_ = clock64(); atomicAdd((unsigned long long*)&P.prof[slot], (unsigned long long)(n_ - prof_t)); prof_t = n_; } } while (0)
+// the same, also broken down by layer: prof[32 + 8 * slot + layer] for slots 0 .. 3 (the issuer's)
+#define PROF_ADDL(slot, l) do { if (prof_who) { const long long n_ = clock64(); atomicAdd((unsigned long long*)&P.prof[slot], (unsigned long long)(n_ - prof_t)); \
+    atomicAdd((unsigned long long*)&P.prof[32 + 8 * (slot) + (l)], (unsigned long long)(n_ - prof_t)); prof_t = n_; } } while (0)
 #else
+#define PROF_ADDL(slot, l) do { } while (0)
 #define PROF_DECL(who) do { } while (0)
 #define PROF_ADD(slot) do { } while (0)
 #endif
@@ -250,6 +255,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   const uint32_t bar_full = bars, bar_empty = bars + 8 * kIssuers * kStg;
   const uint32_t bar_acc_full = bar_empty + 8 * kStg, bar_acc_empty = bar_acc_full + 16;
   const uint32_t bar_a_ready = bar_acc_empty + 16, bar_a_dead = bar_a_ready + 24;
+  const uint32_t bar_park = bars + 240;                           // every row thread has read its parked chunks 0-7 of the last hidden layer
+  const uint32_t bar_in = bars + 248;                             // the staged inputs of the next tile have landed (one phase per staged tile)
   uint32_t* tmem_slot = (uint32_t*)(smem + kParkB + kRingB + 256);
   volatile int* abort_flag = (volatile int*)(smem + kParkB + kRingB + 260);
   uint32_t* s_off = (uint32_t*)(smem + kParkB + kRingB + kBarBytes);          // [kFastIn] input slot offsets
@@ -276,6 +283,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     for (int b = 0; b < 2; b++) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, kRowArrivals); }
     for (int k = 0; k < kMaxKBlocks; k++) mbar_init(bar_a_ready + 8 * k, kRowArrivals);
     for (int k = 0; k < kMaxKBlocks - 1; k++) mbar_init(bar_a_dead + 8 * k, kIssuers);
+    mbar_init(bar_in, kEpiThreads);
+    mbar_init(bar_park, kEpiThreads);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -283,6 +292,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     s_base_in[threadIdx.x] = (const float*)P.TG.base[threadIdx.x];
     s_base_out[threadIdx.x] = (float*)P.TS.base[threadIdx.x];
   }
+  // can a tile's inputs be staged by 16-byte asynchronous copies?  Every slot must run along the fastest loop index with
+  // unit stride and start 16-byte aligned wherever a tile starts on a multiple of four of that index.
+  int stage_bad = 0;
   if (P.fast_in)
     for (int q = threadIdx.x; q < kFastIn; q += kThreads) {
       uint8_t code = 0xFF; uint32_t off = 0;
@@ -290,6 +302,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         const Access a = P.slots[q];
         code = (uint8_t)(a.array | ((a.si == P.cin[0].si && a.sj == P.cin[0].sj && a.sk == P.cin[0].sk) ? 0 : 0x80));
         off = (uint32_t)a.off0;
+        const unsigned long long b0 = reinterpret_cast<unsigned long long>(P.TG.base[a.array]) + 4ull * (unsigned long long)a.off0;
+        if (a.si != 1 || (a.sj & 3) || (a.sk & 3) || (b0 & 15ull)) stage_bad = 1;
       }
       s_code[q] = code; s_off[q] = off;
     }
@@ -315,7 +329,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     }
   }
   tc_fence_before();
-  __syncthreads();
+  const int any_stage_bad = __syncthreads_or(stage_bad);                    // also the CTA's setup barrier
+  const bool can_stage = P.fast_in && !P.no_stage_inputs && any_stage_bad == 0;
   if constexpr (PAIR) cluster_sync_all();      // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
@@ -402,23 +417,23 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             any = true;
             // this issuer's last chunk of the layer: no later chunk lands in accumulator `me`
             const bool mine_last = c + kIssuers >= nchunks;
-            PROF_ADD(0);
+            PROF_ADDL(0, l);
             wait_bar(bar_acc_empty + 8 * b, aph ^ 1, abort_flag, P.status, ST_ACC_EMPTY, P.wait_limit);
-            PROF_ADD(2);
+            PROF_ADDL(2, l);
             tc_fence_after();
             const uint32_t d_tmem = tmem + kAccCol0 + b * kChunkN;
             for (int kb = 0; kb < nkb; kb++) {
               if (first) {                                    // K-block kb of this layer's A is in tensor memory
-                PROF_ADD(0);
+                PROF_ADDL(0, l);
                 wait_bar(bar_a_ready + 8 * kb, lph, abort_flag, P.status, ST_A_READY, P.wait_limit);
-                PROF_ADD(1);
+                PROF_ADDL(1, l);
               }
 #pragma unroll
               for (int sub = 0; sub < kSubStages; sub++) {
-                PROF_ADD(0);
+                PROF_ADDL(0, l);
                 wait_bar(my_full + 8 * s, (full_par >> s) & 1u, abort_flag, P.status, ST_FULL, P.wait_limit);
                 full_par ^= 1u << s;
-                PROF_ADD(3);
+                PROF_ADDL(3, l);
                 tc_fence_after();
                 // descriptor of the stage's first 64-wide k sub-tile; the next sub-tile starts kSubBytes further, and
                 // stepping k by 16 inside a 128-byte swizzle row adds 32 bytes (the address field is in 16-byte units)
@@ -546,6 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
     };
 
     bool prefetched = false;
+    uint32_t in_ph = 0, park_ph = 0;                          // parities of the next phases of bar_in and bar_park
     for (long long u = unit0; u < nunits; u += ustep) {
       const long long tile = PAIR ? 2 * u + crank : u;
       const long long row = tile * kTileM + r;
@@ -555,11 +571,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         //      tile's MMAs have all retired (its last accumulator was read), so A may be overwritten.
         bool lv; long long p0, p1;
         locate_in(row, lv, p0, p1);
+#if FORTIS_TC_GATHER64
+        for (int q0 = half * per0; q0 < (half + 1) * per0; q0 += 64) {     // K is a multiple of 256, so per0 of 128
+          uint32_t pka[16], pkb[16];
+          gather_two_groups(row, lv, p0, p1, q0, pka, pkb);
+          tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pka);
+          tmem_st16(lane_addr + (uint32_t)((q0 >> 1) + 16), pkb);
+        }
+#else
         for (int q0 = half * per0; q0 < (half + 1) * per0; q0 += 32) {
           uint32_t pk[16];
           gather_group(row, lv, p0, p1, q0, pk);
           tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
         }
+#endif
         release_layer0();
         PROF_ADD(9);
       }
@@ -686,6 +711,9 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           }
           if (wall <= 0 && 0 < nkb2) move_block(std::integral_constant<int, 0>{}); else if (nkb2 <= 0) signal(bar_a_ready + 0);
           if (wall <= 1 && 1 < nkb2) move_block(std::integral_constant<int, 1>{}); else if (nkb2 <= 1) signal(bar_a_ready + 8);
+          // Chunks 0-7 have left the park (what block 2 still reads lies behind them): the first 128 KB may take the next
+          // tile's staged inputs.  An arrive here and a wait before the copies, instead of a rendezvous there.
+          if (can_stage && l == P.nlayers - 2) mbar_arrive(bar_park);
           if (2 < nkb2) move_block(std::integral_constant<int, 2>{}); else signal(bar_a_ready + 16);   // blocks the next layer does not have stay in step
           PROF_ADD(12);
         } else {
@@ -700,7 +728,40 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
           // has been moved), in the park's thread-private layout, so no other thread ever touches them.
           static_assert(kBlockK / 2 / 32 == 4 && kPark >= 4, "the prefetch uses four park slots of 32 inputs per half row");
-          if (do_pre) {
+          // Staged form of that fetch: when the next tile is 128 whole rows that run along the fastest loop index, its
+          // inputs come as fp32 [input][row] into the park area by bulk copies, one 512-byte run per model input (the
+          // copy engine keeps far more bytes in flight than 128 loads per thread can, and nothing passes through
+          // registers), and are converted when they go into A.  Otherwise the row threads load them one element each
+          // as in the first tile.
+          bool staged = false;
+          if (do_pre && can_stage && P.nlayers >= 2) {
+            wait_bar(bar_park, park_ph, abort_flag, P.status, ST_IN, P.wait_limit);
+            park_ph ^= 1;
+          }
+          if (do_pre && can_stage) {
+            const long long first = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM;
+            if (first + kTileM <= P.nrows) {
+              long long ci, cj, kk, ci2, cj2, kk2;
+              row_to_pos(P.g, first, &ci, &cj, &kk);
+              row_to_pos(P.g, first + kTileM - 1, &ci2, &cj2, &kk2);
+              if (cj2 == cj && kk2 == kk && ci2 - ci == kTileM - 1 && (ci & 3) == 0) {
+                staged = true;
+                const long long pf0 = ci + cj * P.cin[0].sj + kk * P.cin[0].sk, pf1 = ci + cj * P.cin[1].sj + kk * P.cin[1].sk;
+                // thread q (0 .. 255: the row warps) copies input q's 512-byte run; all of them arrive on the barrier
+                const int q = (int)threadIdx.x;
+                const uint32_t code = s_code[q];
+                if (code != 0xFF) {
+                  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy writes what generic reads have just left
+                  mbar_arrive_expect_tx_thread(bar_in, kTileM * 4);
+                  bulk_load_thread(base + (uint32_t)(q * (kTileM * 4)),
+                                   s_base_in[code & 0x7F] + ((long long)s_off[q] + ((code & 0x80) ? pf1 : pf0)), kTileM * 4, bar_in);
+                } else {
+                  mbar_arrive(bar_in);
+                }
+              }
+            }
+          }
+          if (do_pre && !staged) {
             const long long nrow = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM + r;
             bool lv; long long p0, p1;
             locate_in(nrow, lv, p0, p1);
@@ -730,12 +791,34 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             }
 #endif
           }
+          PROF_ADD(20);
           for (int c = 0; c < nchunks; c++) {
             // From the epilogue of chunk n - 2 on, both issuers' last chunks can run (their accumulators were read by
             // the epilogues before), so the layer's last MMAs on K-block 0 retire without this thread's help.
             if (c == (nchunks < 2 ? nchunks - 1 : nchunks - 2) && do_pre) {
               wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit);
               tc_fence_after();
+              if (staged) {
+                wait_bar(bar_in, in_ph, abort_flag, P.status, ST_IN, P.wait_limit);   // every thread's copy has landed
+                in_ph ^= 1;
+#pragma unroll 1
+                for (int g = 0; g < 4; g++) {
+                  uint32_t pk[16];
+                  const int q0 = half * per0 + 32 * g;
+                  float v[32];
+#pragma unroll
+                  for (int j = 0; j < 32; j++)
+                    v[j] = s_code[q0 + j] != 0xFF ? *reinterpret_cast<const float*>(smem + (q0 + j) * (kTileM * 4) + r * 4) : 0.f;
+                  if (P.in_div) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+                  }
+#pragma unroll
+                  for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
+                  tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");       // all have read the staging area: it may be parked into again
+              } else
 #pragma unroll 1
               for (int g = 0; g < 4; g++) {
                 uint32_t pk[16];
@@ -749,6 +832,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               }
               release_layer0();
               prefetched = true;
+              PROF_ADD(21);
             }
             const uint32_t b = acc_it & 1, aph = (acc_it >> 1) & 1;
             acc_it++;
@@ -1148,6 +1232,8 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   P.test_skip_stage = g_tc_test.skip_stage;
   static const bool no_prefetch = std::getenv("FORTIS_TC_NO_L2_PREFETCH") != nullptr;
   P.no_l2_prefetch = no_prefetch;
+  static const bool no_stage_inputs = std::getenv("FORTIS_TC_NO_STAGE_INPUTS") != nullptr;
+  P.no_stage_inputs = no_stage_inputs || L.inputs_in_host_memory;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(m, nrows);
@@ -1158,8 +1244,8 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
 #endif
   static long long* dprof = nullptr;
   if (want_prof) {
-    if (!dprof) cudaMalloc(&dprof, 32 * sizeof(long long));
-    cudaMemsetAsync(dprof, 0, 32 * sizeof(long long), s);
+    if (!dprof) cudaMalloc(&dprof, 64 * sizeof(long long));
+    cudaMemsetAsync(dprof, 0, 64 * sizeof(long long), s);
     P.prof = dprof;
   }
   if (m->pair) {
@@ -1176,12 +1262,15 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   else if (m->f16) mlp_tc_fused_kernel<false, true, false><<<grid, kThreads, kSmemBytes, s>>>(P);
   else mlp_tc_fused_kernel<false, false, false><<<grid, kThreads, kSmemBytes, s>>>(P);
   if (want_prof) {
-    long long h[32];
+    long long h[64];
     cudaStreamSynchronize(s);
     cudaMemcpy(h, dprof, sizeof h, cudaMemcpyDeviceToHost);
     std::fprintf(stderr, "tc prof (cycles, CTA 0): mma issue %lld | wait a_ready %lld acc_empty %lld full %lld || rows: gather %lld | hidden wait %lld work %lld "
                  "transfer %lld | last wait %lld work %lld || tma wait-empty %lld issue %lld\n",
                  h[0], h[1], h[2], h[3], h[9], h[10], h[11], h[12], h[14], h[13], h[16], h[17]);
+    std::fprintf(stderr, "tc prof last layer: next tile's gather %lld, its move into tensor memory %lld\n", h[20], h[21]);
+    for (int l = 0; l < m->nlayers && l < 8; l++)
+      std::fprintf(stderr, "tc prof layer %d: issue %lld | wait a_ready %lld acc_empty %lld full %lld\n", l, h[32 + l], h[40 + l], h[48 + l], h[56 + l]);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { if (err) *err = std::string("tensor-core kernel launch: ") + cudaGetErrorString(e); return false; }
