@@ -560,8 +560,52 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       for (int k = kMaxKBlocks - 1; k >= 0; k--) signal(bar_a_ready + 8 * k);
     };
 
-    bool prefetched = false;
     uint32_t in_ph = 0, park_ph = 0;                          // parities of the next phases of bar_in and bar_park
+    // Staged fetch of a tile's inputs.  A tile qualifies when it is 128 whole rows that run along the fastest loop index
+    // (and the per-CTA conditions of can_stage hold): every model input is then one aligned 512-byte run.
+    auto stage_issue = [&](long long first) -> bool {
+      if (first + kTileM > P.nrows) return false;
+      long long ci, cj, kk, ci2, cj2, kk2;
+      row_to_pos(P.g, first, &ci, &cj, &kk);
+      row_to_pos(P.g, first + kTileM - 1, &ci2, &cj2, &kk2);
+      if (cj2 != cj || kk2 != kk || ci2 - ci != kTileM - 1 || (ci & 3) != 0) return false;
+      const long long pf0 = ci + cj * P.cin[0].sj + kk * P.cin[0].sk, pf1 = ci + cj * P.cin[1].sj + kk * P.cin[1].sk;
+      // thread q (0 .. 255: the row warps) copies input q's run into fp32 [input][row]; all of them arrive on the barrier
+      const int q = (int)threadIdx.x;
+      const uint32_t code = s_code[q];
+      if (code != 0xFF) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy writes what generic reads have just left
+        mbar_arrive_expect_tx_thread(bar_in, kTileM * 4);
+        bulk_load_thread(base + (uint32_t)(q * (kTileM * 4)),
+                         s_base_in[code & 0x7F] + ((long long)s_off[q] + ((code & 0x80) ? pf1 : pf0)), kTileM * 4, bar_in);
+      } else {
+        mbar_arrive(bar_in);
+      }
+      return true;
+    };
+    // the staged inputs, converted, into the A columns of K-block 0 (one K-block of inputs: can_prefetch)
+    auto stage_consume = [&]() {
+      wait_bar(bar_in, in_ph, abort_flag, P.status, ST_IN, P.wait_limit);   // every thread's copy has landed
+      in_ph ^= 1;
+#pragma unroll 1
+      for (int g = 0; g < 4; g++) {
+        uint32_t pk[16];
+        const int q0 = half * per0 + 32 * g;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+          v[j] = s_code[q0 + j] != 0xFF ? *reinterpret_cast<const float*>(smem + (q0 + j) * (kTileM * 4) + r * 4) : 0.f;
+        if (P.in_div) {
+#pragma unroll
+          for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
+        tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");       // all have read the staging area: it may be parked into again
+    };
+    bool prefetched = false;
     for (long long u = unit0; u < nunits; u += ustep) {
       const long long tile = PAIR ? 2 * u + crank : u;
       const long long row = tile * kTileM + r;
@@ -571,6 +615,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         //      tile's MMAs have all retired (its last accumulator was read), so A may be overwritten.
         bool lv; long long p0, p1;
         locate_in(row, lv, p0, p1);
+        if (can_stage && can_prefetch && stage_issue(tile * kTileM)) stage_consume();      // (the park area is not in use)
+        else
 #if FORTIS_TC_GATHER64
         for (int q0 = half * per0; q0 < (half + 1) * per0; q0 += 64) {     // K is a multiple of 256, so per0 of 128
           uint32_t pka[16], pkb[16];
@@ -738,29 +784,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             wait_bar(bar_park, park_ph, abort_flag, P.status, ST_IN, P.wait_limit);
             park_ph ^= 1;
           }
-          if (do_pre && can_stage) {
-            const long long first = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM;
-            if (first + kTileM <= P.nrows) {
-              long long ci, cj, kk, ci2, cj2, kk2;
-              row_to_pos(P.g, first, &ci, &cj, &kk);
-              row_to_pos(P.g, first + kTileM - 1, &ci2, &cj2, &kk2);
-              if (cj2 == cj && kk2 == kk && ci2 - ci == kTileM - 1 && (ci & 3) == 0) {
-                staged = true;
-                const long long pf0 = ci + cj * P.cin[0].sj + kk * P.cin[0].sk, pf1 = ci + cj * P.cin[1].sj + kk * P.cin[1].sk;
-                // thread q (0 .. 255: the row warps) copies input q's 512-byte run; all of them arrive on the barrier
-                const int q = (int)threadIdx.x;
-                const uint32_t code = s_code[q];
-                if (code != 0xFF) {
-                  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the copy writes what generic reads have just left
-                  mbar_arrive_expect_tx_thread(bar_in, kTileM * 4);
-                  bulk_load_thread(base + (uint32_t)(q * (kTileM * 4)),
-                                   s_base_in[code & 0x7F] + ((long long)s_off[q] + ((code & 0x80) ? pf1 : pf0)), kTileM * 4, bar_in);
-                } else {
-                  mbar_arrive(bar_in);
-                }
-              }
-            }
-          }
+          if (do_pre && can_stage) staged = stage_issue((PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM);
           if (do_pre && !staged) {
             const long long nrow = (PAIR ? 2 * (u + ustep) + crank : u + ustep) * kTileM + r;
             bool lv; long long p0, p1;
@@ -799,25 +823,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               wait_bar(bar_a_dead, lph, abort_flag, P.status, ST_A_DEAD, P.wait_limit);
               tc_fence_after();
               if (staged) {
-                wait_bar(bar_in, in_ph, abort_flag, P.status, ST_IN, P.wait_limit);   // every thread's copy has landed
-                in_ph ^= 1;
-#pragma unroll 1
-                for (int g = 0; g < 4; g++) {
-                  uint32_t pk[16];
-                  const int q0 = half * per0 + 32 * g;
-                  float v[32];
-#pragma unroll
-                  for (int j = 0; j < 32; j++)
-                    v[j] = s_code[q0 + j] != 0xFF ? *reinterpret_cast<const float*>(smem + (q0 + j) * (kTileM * 4) + r * 4) : 0.f;
-                  if (P.in_div) {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) if (q0 + j < P.n_in) v[j] = __fdiv_rn(v[j], __ldg(P.in_div + q0 + j));
-                  }
-#pragma unroll
-                  for (int j = 0; j < 16; j++) pk[j] = pack16<F16>(v[2 * j], v[2 * j + 1]);
-                  tmem_st16(lane_addr + (uint32_t)(q0 >> 1), pk);
-                }
-                asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");       // all have read the staging area: it may be parked into again
+                stage_consume();
               } else
 #pragma unroll 1
               for (int g = 0; g < 4; g++) {

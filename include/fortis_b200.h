@@ -137,6 +137,9 @@ int fortis_load_model_mem(const void* blob, long nbytes);
  *                 load from them as well); also FORTIS_HOST_ACCESS
  *   "stencil_tc"  "0" | "1"   3x3-stencil hosts with narrow MLPs: run the layers as TF32x3 tensor-core products instead
  *                 of packed FMAs (same <= 1e-5; measured slower for 27-20-20-3, default 0); also FORTIS_STENCIL_TC
+ *   "tc_pair"     "1" (default) | "0" | "default"   wide MLPs in 16-bit / FP8-weight precision: run the fused
+ *                 tensor-core kernel as clusters of two CTAs that share one stream of weights, or one CTA per SM (same
+ *                 results bit for bit; the cluster form is 9-16 % faster); also FORTIS_TC_PAIR
  *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model (NDHWC arrays); "N,1,H,W" for a network of 2-D operator
  *                 layers (Conv2d / transposed / pooling / upsampling; NCHW arrays in and out of mlp_forward)
  * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits (fortis_b200_test.h). */
