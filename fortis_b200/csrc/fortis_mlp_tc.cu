@@ -661,22 +661,15 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
             tmem_ld_wait();
             tc_fence_before();
             signal(bar_acc_empty + 8 * b);                    // the MMA warp may refill this accumulator
-            if (HAS_SCALE) {
-#pragma unroll
-              for (int j = 0; j < 8; j++) {
-                const float4 sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
-                a[4 * j] = __float_as_uint(__uint_as_float(a[4 * j]) * sq.x);
-                a[4 * j + 1] = __float_as_uint(__uint_as_float(a[4 * j + 1]) * sq.y);
-                a[4 * j + 2] = __float_as_uint(__uint_as_float(a[4 * j + 2]) * sq.z);
-                a[4 * j + 3] = __float_as_uint(__uint_as_float(a[4 * j + 3]) * sq.w);
-              }
-            }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-              const float v0 = act_f(__uint_as_float(a[4 * j]) + bq[j].x, slope);
-              const float v1 = act_f(__uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
-              const float v2 = act_f(__uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
-              const float v3 = act_f(__uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
+              // FP8 weights: acc * scale + bias as one fused multiply-add (the last layer's epilogue does the same)
+              float4 sq = make_float4(1.f, 1.f, 1.f, 1.f);
+              if (HAS_SCALE) sq = __ldg(reinterpret_cast<const float4*>(L.scale + n0) + j);
+              const float v0 = act_f(HAS_SCALE ? fmaf(__uint_as_float(a[4 * j]), sq.x, bq[j].x) : __uint_as_float(a[4 * j]) + bq[j].x, slope);
+              const float v1 = act_f(HAS_SCALE ? fmaf(__uint_as_float(a[4 * j + 1]), sq.y, bq[j].y) : __uint_as_float(a[4 * j + 1]) + bq[j].y, slope);
+              const float v2 = act_f(HAS_SCALE ? fmaf(__uint_as_float(a[4 * j + 2]), sq.z, bq[j].z) : __uint_as_float(a[4 * j + 2]) + bq[j].z, slope);
+              const float v3 = act_f(HAS_SCALE ? fmaf(__uint_as_float(a[4 * j + 3]), sq.w, bq[j].w) : __uint_as_float(a[4 * j + 3]) + bq[j].w, slope);
               pk[2 * j] = pack16<F16>(v0, v1);
               pk[2 * j + 1] = pack16<F16>(v2, v3);
             }
