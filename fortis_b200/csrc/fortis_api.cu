@@ -1443,6 +1443,7 @@ int fortis_set_option(const char* key, const char* value) {
   else if (k == "checksum") { s.want_checksum = v != "0"; drop_graph(); }
   else if (k == "test_wait_limit") { g_tc_test.wait_limit = (unsigned int)std::strtoul(v.c_str(), nullptr, 10); drop_graph(); }
   else if (k == "test_skip_stage") { g_tc_test.skip_stage = v != "0"; drop_graph(); }
+  else if (k == "test_no_stage") { g_tc_test.no_stage = v != "0"; drop_graph(); }
   else if (k == "conv_shape") {
     if (std::sscanf(v.c_str(), "%d,%d,%d,%d", &s.conv_shape[0], &s.conv_shape[1], &s.conv_shape[2], &s.conv_shape[3]) != 4)
       throw std::runtime_error("conv_shape must be N,D,H,W");
@@ -1453,7 +1454,7 @@ int fortis_set_option(const char* key, const char* value) {
 }
 
 void fortis_reset(void) {
-  g_tc_test = TcTestKnobs{0u, 0};
+  g_tc_test = TcTestKnobs{0u, 0, 0};
   tc_set_pair_mode(-1);
   if (!g_S) return;
   if (g_stream) cudaStreamSynchronize(g_stream);

@@ -982,7 +982,7 @@ float e4m3_round(float v) {
 
 }  // namespace
 
-TcTestKnobs g_tc_test = {0u, 0};
+TcTestKnobs g_tc_test = {0u, 0, 0};
 
 // One Linear layer converted for the tensor-core kernel: padded, rounded to the 16-bit operand type (FP8 weights: the
 // nearest E4M3 code of w / scale, which bf16 represents exactly), as row-major [N][K] (`rowmajor`, optional) and as
@@ -1232,7 +1232,7 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   static const bool no_prefetch = std::getenv("FORTIS_TC_NO_L2_PREFETCH") != nullptr;
   P.no_l2_prefetch = no_prefetch;
   static const bool no_stage_inputs = std::getenv("FORTIS_TC_NO_STAGE_INPUTS") != nullptr;
-  P.no_stage_inputs = no_stage_inputs || L.inputs_in_host_memory;
+  P.no_stage_inputs = no_stage_inputs || L.inputs_in_host_memory || g_tc_test.no_stage;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(m, nrows);

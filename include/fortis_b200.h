@@ -142,7 +142,8 @@ int fortis_load_model_mem(const void* blob, long nbytes);
  *                 results bit for bit; the cluster form is 9-16 % faster); also FORTIS_TC_PAIR
  *   "conv_shape"  "N,D,H,W"   input extent of a conv3d model (NDHWC arrays); "N,1,H,W" for a network of 2-D operator
  *                 layers (Conv2d / transposed / pooling / upsampling; NCHW arrays in and out of mlp_forward)
- * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits (fortis_b200_test.h). */
+ * The keys "test_wait_limit" and "test_skip_stage" exist for the tests of the bounded waits, "test_no_stage" for the test
+ * of the staged input fetch (fortis_b200_test.h). */
 int fortis_set_option(const char* key, const char* value);
 /* drop every descriptor, model, buffer registration and captured graph (device pool buffers stay pooled) */
 void fortis_reset(void);

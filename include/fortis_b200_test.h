@@ -22,6 +22,13 @@ int fortis_debug_plan(const char* desc_json, const char* loop_json, const char* 
 int fortis_debug_pack_layer(const float* W, const float* b, int cout, int cin, int last, int precision, unsigned short* image,
                             float* bias, float* scale, int* K, int* N);
 
+/* Test-only keys of fortis_set_option (cleared by fortis_reset):
+ *   "test_wait_limit"  N      polls before a bounded barrier wait of the tensor-core kernels gives up (0: the default)
+ *   "test_skip_stage"  0 | 1  the first CTA's copy warp leaves out its first stage, so that a wait runs out: the
+ *                             kernel returns, fortis_device_status() reports which wait gave up
+ *   "test_no_stage"    0 | 1  fused MLP kernel: fetch every tile's inputs element by element instead of staging whole
+ *                             tiles by bulk copies (same bits; for the comparison of the two paths) */
+
 #ifdef __cplusplus
 }
 #endif

@@ -225,6 +225,43 @@ def test_two_cta_clusters_give_the_same_bits(host, precision, ncol):
     assert float(np.abs(np.concatenate([a.ravel() for a in res[1][0]])).sum()) > 0.0
 
 
+@pytest.mark.parametrize("nx,ny,nz,halo", [(256, 40, 2, 0), (200, 60, 2, 0), (256, 40, 2, 1), (128, 160, 1, 0), (300, 70, 1, 0)])
+def test_staged_input_fetch_against_element_loads_and_the_oracle(host, nx, ny, nz, halo):
+    """The next tile's inputs arrive by bulk copies where a tile is 128 whole rows along the fastest loop index, and
+    element by element otherwise.  2-D loops with several tiles per CTA: every tile qualifies (nx a multiple of 128),
+    tiles that wrap around the row end mixed with ones that do not (nx = 200, 300), unaligned arrays (a halo shifts
+    every start by one element: no tile qualifies).  Staged = unstaged bit for bit, and both match the oracle."""
+    import fortis_b200.descriptors as D
+    nf, nout = 8, 3
+    G, S, Lp, K = D.stencil(nx, ny, nz, nfields=nf, nout=nout, halo=halo, radius=0)
+    rng = np.random.default_rng(77)
+    sx, sy = nx + 2 * halo, ny + 2 * halo
+    gin = [np.asfortranarray(rng.normal(size=(sx, sy, nz)).astype(np.float32)) for _ in range(nf)]
+    layers = fortis_b200.mlp_layers([nf, 256, 512, nout], seed=5, act="leaky", slope=0.1, bias="uniform", scale=0.2)
+    blob = fortis_b200.write_blob(layers)
+    outs = []
+    for no_stage in (0, 1):
+        host.reset()
+        host.configure(gather=G, scatter=S, loop=Lp, kdist=K)
+        host.load_model(blob)
+        host.option("precision", "bf16")
+        host.option("test_no_stage", no_stage)
+        # device-resident arrays: one launch over all planes, so CTAs get several tiles
+        to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
+        d_in = [to_dev(a) for a in gin]
+        d_out = [to_dev(np.full((sx, sy, nz), -7.0, np.float32, order="F")) for _ in range(nout)]
+        host.step(d_in, d_out)
+        host.sync()
+        assert host.L.fortis_device_status() == 0
+        outs.append([t.cpu().numpy().reshape((sx, sy, nz), order="F") for t in d_out])
+    for a, b in zip(outs[0], outs[1]):
+        assert np.array_equal(a, b)
+    model = [np.full((sx, sy, nz), -7.0, np.float32, order="F") for _ in range(nout)]
+    fo.full_step(G, S, Lp, K, layers, gin, model, forward=lambda L, X: fo.mlp_forward_lowp(L, X, "bf16"))
+    cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
+    assert fo.rel_l2(cat(outs[0]), cat(model)) < MODEL_TOL
+
+
 @pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_TC_SWEEP", "10"))))
 def test_random_shapes_against_the_low_precision_model(host, seed):
     """Random depths (1-7 layers), widths (1-768, so every padding and chunk count), row counts (1-4000, so ragged
