@@ -81,7 +81,7 @@ bool launch_stencil_tc(StencilTcModel* m, const StencilLaunch& S, int* status, c
 // Test knobs of the tensor-core kernels (set through fortis_set_option "test_wait_limit" / "test_skip_stage"; both 0
 // in normal operation): a short poll limit for the bounded barrier waits, and "the first CTA's TMA warp does not load
 // its first stage", which makes a wait run out so that the give-up path can be exercised without hanging anything.
-struct TcTestKnobs { unsigned int wait_limit; int skip_stage; int no_stage; };   // no_stage: fused MLP kernel, fetch every tile's inputs element by element
+struct TcTestKnobs { unsigned int wait_limit; int skip_stage; int no_stage; };   // no_stage: fused MLP kernel, move every tile's inputs and outputs element by element
 extern TcTestKnobs g_tc_test;
 
 // ---- tensor-core fused MLP (fortis_mlp_tc.cu) ----------------------------------------------------------------
@@ -108,6 +108,7 @@ struct TcLaunch {
   double* partials;                                  // per-CTA checksum partials (size >= tc_grid())
   double* sum; unsigned int* done;                   // optional: fold the partials into *sum inside the kernel (done: zeroed counter)
   int* status;                                       // device word: 0 ok, else the code of the wait that gave up
+  int outputs_in_host_memory;                        // the scatter arrays are mapped host pages: written by the threads' own stores
   int inputs_in_host_memory;                         // the gather arrays are mapped host pages: read by the threads' own loads, not by bulk copies
 };
 int tc_grid(const TcModel* m, long long nrows);

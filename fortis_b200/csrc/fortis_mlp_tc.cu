@@ -150,6 +150,7 @@ struct TcParams {
   int test_skip_stage;                   // test only: CTA 0 never loads its first weight stage
   int no_l2_prefetch;                    // FORTIS_TC_NO_L2_PREFETCH: do not ask for the weights to be brought into L2 at kernel start
   int no_stage_inputs;                   // FORTIS_TC_NO_STAGE_INPUTS: fetch the next tile's inputs element by element
+  int no_stage_outputs;                  // FORTIS_TC_NO_STAGE_OUTPUTS: store a tile's outputs element by element
   long long* prof;                       // optional cycle counters of CTA 0 (diagnostics; null in normal runs)
   // fast I/O: every access is fp32 without lifted expressions and uses one of two stride classes; the per-slot
   // (array, class, constant offset) triples are unpacked into shared memory once per CTA
@@ -307,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       }
       s_code[q] = code; s_off[q] = off;
     }
+  int stage_out_bad = 0;                      // the same question for the stores of a tile's outputs
   if (P.fast_out)
     for (int n = threadIdx.x; n < kFastOut; n += kThreads) {
       uint8_t code = 0xFF; uint32_t off = 0;
@@ -314,6 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
         const Access a = P.store_by_slot[n];
         code = (uint8_t)(a.array | ((a.si == P.cout[0].si && a.sj == P.cout[0].sj && a.sk == P.cout[0].sk) ? 0 : 0x80));
         off = (uint32_t)a.off0;
+        const unsigned long long b0 = reinterpret_cast<unsigned long long>(P.TS.base[a.array]) + 4ull * (unsigned long long)a.off0;
+        if (a.si != 1 || (a.sj & 3) || (a.sk & 3) || (b0 & 15ull)) stage_out_bad = 1;
       }
       o_code[n] = code; o_off[n] = off;
     }
@@ -331,6 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
   tc_fence_before();
   const int any_stage_bad = __syncthreads_or(stage_bad);                    // also the CTA's setup barrier
   const bool can_stage = P.fast_in && !P.no_stage_inputs && any_stage_bad == 0;
+  const bool can_stage_out = (__syncthreads_or(stage_out_bad) == 0) && P.fast_out && !P.no_stage_outputs && !P.Y;
   if constexpr (PAIR) cluster_sync_all();      // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
@@ -605,6 +610,19 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
       }
       asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");       // all have read the staging area: it may be parked into again
     };
+    // Staged stores of a tile's outputs: fp32 [output][row] in the last 64 KB of the park area, then one bulk store per
+    // model output.  The area is parked into again from chunk kOutSlot of the next tile's hidden layers on, and the
+    // next tile's staged inputs reach into it: before either, the stores must have read it.
+    constexpr int kOutSlot = kPark - 4;
+    constexpr uint32_t kOutStage = (uint32_t)kOutSlot * (kTileM * kChunkN * 2);
+    bool out_pending = false;
+    auto out_stage_drain = [&]() {
+      if (out_pending) {
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");
+        out_pending = false;
+      }
+    };
     bool prefetched = false;
     for (long long u = unit0; u < nunits; u += ustep) {
       const long long tile = PAIR ? 2 * u + crank : u;
@@ -689,6 +707,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           for (int c = 0; c < nsm; c++) {
             uint32_t pk[16];
             chunk_epilogue(c, pk);
+            if (c == kOutSlot) out_stage_drain();
             park_smem(c, pk);
           }
 #pragma unroll
@@ -738,7 +757,7 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           {
             uint32_t pk[16];
             chunk_epilogue(lastc, pk);                        // waits for the layer's last accumulator: every MMA has retired
-            if (lastc < kPark) park_smem(lastc, pk);
+            if (lastc < kPark) { if (lastc >= kOutSlot) out_stage_drain(); park_smem(lastc, pk); }
             else {
 #pragma unroll
               for (int cc = kPark; cc < kMaxChunks; cc++)
@@ -764,6 +783,20 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           const long long opos0 = ci * P.cout[0].si + cj * P.cout[0].sj + kk * P.cout[0].sk;
           const long long opos1 = ci * P.cout[1].si + cj * P.cout[1].sj + kk * P.cout[1].sk;
           const bool do_pre = can_prefetch && u + ustep < nunits;
+          out_stage_drain();
+          // this tile's outputs by bulk stores: 128 whole rows along the fastest loop index (as for the inputs)
+          bool out_staged = false;
+          long long of0 = 0, of1 = 0;
+          if (can_stage_out && tile * kTileM + kTileM <= P.nrows) {
+            long long c0, j0, k0, c2, j2, k2;
+            row_to_pos(P.g, tile * kTileM, &c0, &j0, &k0);
+            row_to_pos(P.g, tile * kTileM + kTileM - 1, &c2, &j2, &k2);
+            if (j2 == j0 && k2 == k0 && c2 - c0 == kTileM - 1 && (c0 & 3) == 0) {
+              out_staged = true;
+              of0 = c0 + j0 * P.cout[0].sj + k0 * P.cout[0].sk;
+              of1 = c0 + j0 * P.cout[1].sj + k0 * P.cout[1].sk;
+            }
+          }
           // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
           // has been moved), in the park's thread-private layout, so no other thread ever touches them.
           static_assert(kBlockK / 2 / 32 == 4 && kPark >= 4, "the prefetch uses four park slots of 32 inputs per half row");
@@ -873,7 +906,16 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
 #pragma unroll
                 for (int j = 0; j < 32; j++) if (n0 + j < P.n_out) P.Y[row * P.n_out + n0 + j] = v[j];
               }
-              if (P.fast_out) {
+              if (out_staged) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                  const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
+                  if (code != 0xFF) {
+                    *reinterpret_cast<float*>(smem + kOutStage + (n0 + j) * (kTileM * 4) + r * 4) = v[j];
+                    csum += (double)v[j];
+                  }
+                }
+              } else if (P.fast_out) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                   const uint32_t code = (n0 + j < kFastOut) ? o_code[n0 + j] : 0xFFu;
@@ -885,10 +927,24 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               }
             }
           }
+          if (out_staged) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");          // this thread's values, for the copy engine
+            asm volatile("bar.sync 1, %0;" ::"r"(kEpiThreads) : "memory");        // every row of every output is there
+            const int n = (int)threadIdx.x;
+            if (n < kFastOut) {
+              const uint32_t code = o_code[n];
+              if (code != 0xFF)
+                bulk_store_thread(s_base_out[code & 0x7F] + ((long long)o_off[n] + ((code & 0x80) ? of1 : of0)),
+                                  base + kOutStage + (uint32_t)(n * (kTileM * 4)), kTileM * 4);
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            out_pending = true;
+          }
           PROF_ADD(13);
         }
       }
     }
+    if (out_pending) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // the last tile's output stores are complete
     if (P.partials) {
       // per-CTA checksum partial in a fixed order: shuffle tree per warp, then warp results in index order
       double* wsum = (double*)(smem + kParkB + kRingB + 272);
@@ -1233,6 +1289,8 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   P.no_l2_prefetch = no_prefetch;
   static const bool no_stage_inputs = std::getenv("FORTIS_TC_NO_STAGE_INPUTS") != nullptr;
   P.no_stage_inputs = no_stage_inputs || L.inputs_in_host_memory || g_tc_test.no_stage;
+  static const bool no_stage_outputs = std::getenv("FORTIS_TC_NO_STAGE_OUTPUTS") != nullptr;
+  P.no_stage_outputs = no_stage_outputs || L.outputs_in_host_memory || g_tc_test.no_stage;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(m, nrows);

@@ -26,8 +26,8 @@ int fortis_debug_pack_layer(const float* W, const float* b, int cout, int cin, i
  *   "test_wait_limit"  N      polls before a bounded barrier wait of the tensor-core kernels gives up (0: the default)
  *   "test_skip_stage"  0 | 1  the first CTA's copy warp leaves out its first stage, so that a wait runs out: the
  *                             kernel returns, fortis_device_status() reports which wait gave up
- *   "test_no_stage"    0 | 1  fused MLP kernel: fetch every tile's inputs element by element instead of staging whole
- *                             tiles by bulk copies (same bits; for the comparison of the two paths) */
+ *   "test_no_stage"    0 | 1  fused MLP kernel: fetch every tile's inputs and store its outputs element by element
+ *                             instead of staging whole tiles by bulk copies (same bits; for the comparison of the paths) */
 
 #ifdef __cplusplus
 }
