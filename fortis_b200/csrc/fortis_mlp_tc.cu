@@ -16,13 +16,15 @@
 //     load per stage, no multicast).
 //   * D: two 64-column fp32 accumulators in TMEM; the epilogue of chunk c overlaps the MMAs of chunk c+1.
 //   * The epilogue (8 warps; thread = one row x 32 features) adds bias, applies the activation, rounds to bf16 and
-//     parks the chunk: chunks 0-7 in shared memory, chunks 8-11 in registers (A is still being read by later
-//     chunks, so the output cannot overwrite it).  When the layer's last MMA has retired, the parked chunks are
+//     parks the chunk: chunks 0-9 in shared memory, chunks 10-11 in registers (0-7 and 8-11 with one CTA per SM; A
+//     is still being read by later chunks, so the output cannot overwrite it).  When the layer's last MMA has retired, the parked chunks are
 //     written into the A columns with tcgen05.st and the next layer starts.
-//   * Layer 0's A is produced by the same threads straight from the host's Fortran arrays (thread = row, so every
-//     slot is a coalesced load); the last layer's epilogue stores straight into the host arrays and accumulates
-//     the fp64 checksum.  This fusion is table-driven and covers fp32 arrays without lifted expressions; any other
-//     descriptor is served by the standalone gather / scatter kernels writing X / reading Y around this kernel.
+//   * Layer 0's A is produced by the same threads straight from the host's Fortran arrays, and the last layer's
+//     epilogue stores straight into them and accumulates the fp64 checksum.  A tile of 128 whole rows along the
+//     fastest loop index moves as bulk copies (one 512-byte run per model input / output through an fp32 staging area
+//     in the park), any other tile element by element (thread = row, so every access is coalesced).  This fusion is
+//     table-driven and covers fp32 arrays without lifted expressions; any other descriptor is served by the
+//     standalone gather / scatter kernels writing X / reading Y around this kernel.
 // TMEM: 384 (A) + 2 x 64 (D) = 512 columns.  Shared memory: 128 KB parked chunks + 3 x 32 KB weight ring (one CTA per
 // SM), 160 KB parked chunks + 4 x 16 KB ring (CTA of a pair).
 //
