@@ -756,8 +756,6 @@ void run_step_kernels(const StepArgs& A) {
     L.partials = (fuse_out && s.want_checksum) ? s.d_partials : nullptr;
     L.sum = L.partials ? s.d_sum : nullptr; L.done = s.d_done;
     L.status = s.d_status;
-    L.inputs_in_host_memory = maps_host(s.G);
-    L.outputs_in_host_memory = maps_host(s.S);
     std::string err;
     if (!tc_forward(s.tc, L, st, &err)) throw std::runtime_error(err);
     if (A.fuse_scatter && !fuse_out) scatter_with_checksum(A, g);

@@ -108,8 +108,6 @@ struct TcLaunch {
   double* partials;                                  // per-CTA checksum partials (size >= tc_grid())
   double* sum; unsigned int* done;                   // optional: fold the partials into *sum inside the kernel (done: zeroed counter)
   int* status;                                       // device word: 0 ok, else the code of the wait that gave up
-  int outputs_in_host_memory;                        // the scatter arrays are mapped host pages: written by the threads' own stores
-  int inputs_in_host_memory;                         // the gather arrays are mapped host pages: read by the threads' own loads, not by bulk copies
 };
 int tc_grid(const TcModel* m, long long nrows);
 void tc_set_pair_mode(int on);                      // 1 / 0: two-CTA clusters or one CTA per SM for models created from now on; -1: the default (clusters)

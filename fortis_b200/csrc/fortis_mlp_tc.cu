@@ -1290,9 +1290,10 @@ bool tc_forward(TcModel* m, const TcLaunch& L, cudaStream_t s, std::string* err)
   static const bool no_prefetch = std::getenv("FORTIS_TC_NO_L2_PREFETCH") != nullptr;
   P.no_l2_prefetch = no_prefetch;
   static const bool no_stage_inputs = std::getenv("FORTIS_TC_NO_STAGE_INPUTS") != nullptr;
-  P.no_stage_inputs = no_stage_inputs || L.inputs_in_host_memory || g_tc_test.no_stage;
+  // (mapped host pages are staged the same way: bulk copies read them at 33 GB/s, the threads' own loads at 24)
+  P.no_stage_inputs = no_stage_inputs || g_tc_test.no_stage;
   static const bool no_stage_outputs = std::getenv("FORTIS_TC_NO_STAGE_OUTPUTS") != nullptr;
-  P.no_stage_outputs = no_stage_outputs || L.outputs_in_host_memory || g_tc_test.no_stage;
+  P.no_stage_outputs = no_stage_outputs || g_tc_test.no_stage;
   if (!P.fast_in && !P.X) { if (err) *err = "tensor-core step: no input"; return false; }
   if (!P.fast_out && !P.Y) { if (err) *err = "tensor-core step: no output"; return false; }
   const int grid = tc_grid(m, nrows);
