@@ -262,6 +262,49 @@ def test_staged_input_fetch_against_element_loads_and_the_oracle(host, nx, ny, n
     assert fo.rel_l2(cat(outs[0]), cat(model)) < MODEL_TOL
 
 
+@pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_STAGE_SWEEP", "4"))))
+def test_staged_tiles_random_layouts(host, seed):
+    """Random 2-D / 3-D extents, halos, field counts and precisions with several tiles per CTA: whole tiles moved by bulk
+    copies against every tile moved element by element (bit for bit), and against the oracle's model."""
+    import fortis_b200.descriptors as D
+    rng = np.random.default_rng(9100 + seed)
+    nx = int(rng.choice([128, 256, 384, 200, 300, 132, 64, 512]))
+    nz = int(rng.integers(1, 4))
+    ny = int(rng.integers(20000 // (nx * nz) + 1, 30000 // (nx * nz) + 2))
+    halo = int(rng.choice([0, 0, 0, 1, 4]))
+    nf, nout = int(rng.integers(1, 17)), int(rng.integers(1, 9))
+    precision = str(rng.choice(["bf16", "fp16", "fp8w"]))
+    hidden = [int(rng.choice([64, 256, 300, 512, 768])) for _ in range(int(rng.integers(1, 4)))]
+    G, S, Lp, K = D.stencil(nx, ny, nz, nfields=nf, nout=nout, halo=halo, radius=0)
+    sx, sy = nx + 2 * halo, ny + 2 * halo
+    gin = [np.asfortranarray(rng.normal(size=(sx, sy, nz)).astype(np.float32)) for _ in range(nf)]
+    layers = fortis_b200.mlp_layers([nf] + hidden + [nout], seed=int(rng.integers(1 << 30)), act="leaky", slope=0.1, bias="uniform", scale=0.2)
+    blob = fortis_b200.write_blob(layers)
+    tag = "seed %d nx %d ny %d nz %d halo %d nf %d nout %d hidden %s %s" % (seed, nx, ny, nz, halo, nf, nout, hidden, precision)
+    to_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a.reshape(-1, order="F"))).cuda()
+    outs = []
+    for no_stage in (0, 1):
+        host.reset()
+        host.configure(gather=G, scatter=S, loop=Lp, kdist=K)
+        host.load_model(blob)
+        host.option("precision", precision)
+        host.option("checksum", 1)
+        host.option("test_no_stage", no_stage)
+        d_in = [to_dev(a) for a in gin]
+        d_out = [to_dev(np.full((sx, sy, nz), -7.0, np.float32, order="F")) for _ in range(nout)]
+        host.step(d_in, d_out)
+        host.sync()
+        assert host.L.fortis_device_status() == 0, tag
+        outs.append(([t.cpu().numpy().reshape((sx, sy, nz), order="F") for t in d_out], host.step_checksum()))
+    for a, b in zip(outs[0][0], outs[1][0]):
+        assert np.array_equal(a, b), tag
+    assert outs[0][1] == outs[1][1], tag                      # same values added in the same order
+    model = [np.full((sx, sy, nz), -7.0, np.float32, order="F") for _ in range(nout)]
+    fo.full_step(G, S, Lp, K, layers, gin, model, forward=lambda L, X: fo.mlp_forward_lowp(L, X, precision))
+    cat = lambda arrs: np.concatenate([a.ravel() for a in arrs])
+    assert fo.rel_l2(cat(outs[0][0]), cat(model)) < MODEL_TOL, tag
+
+
 @pytest.mark.parametrize("seed", range(int(os.environ.get("FORTIS_TC_SWEEP", "10"))))
 def test_random_shapes_against_the_low_precision_model(host, seed):
     """Random depths (1-7 layers), widths (1-768, so every padding and chunk count), row counts (1-4000, so ragged
