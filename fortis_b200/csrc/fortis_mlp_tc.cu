@@ -777,8 +777,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
           if (2 < nkb2) move_block(std::integral_constant<int, 2>{}); else signal(bar_a_ready + 16);   // blocks the next layer does not have stay in step
           PROF_ADD(12);
         } else {
-          // ---- last layer: bias, output scaling / masks, then straight into the host arrays.  While its MMAs run, the
-          //      next tile's inputs are fetched into registers; they go into A as soon as the layer's last MMAs on
+          // ---- last layer: bias, output scaling / masks, then into the host arrays.  While its MMAs run, the next
+          //      tile's inputs are fetched into the park area; they go into A as soon as the layer's last MMAs on
           //      K-block 0 have retired, so that the next tile's first layer runs under this tile's scatter.
           long long ci = 0, cj = 0, kk = 0;
           if (live) row_to_pos(P.g, row, &ci, &cj, &kk);
@@ -799,8 +799,8 @@ __global__ void __launch_bounds__(kThreads, 1) mlp_tc_fused_kernel(const __grid_
               of1 = c0 + j0 * P.cout[1].sj + k0 * P.cout[1].sk;
             }
           }
-          // The fetched inputs wait in the shared-memory park area (free during the last layer: every parked chunk
-          // has been moved), in the park's thread-private layout, so no other thread ever touches them.
+          // Fetched element by element, the inputs wait in the park area (free during the last layer: every parked
+          // chunk has been moved) in the park's thread-private layout, so no other thread ever touches them.
           static_assert(kBlockK / 2 / 32 == 4 && kPark >= 4, "the prefetch uses four park slots of 32 inputs per half row");
           // Staged form of that fetch: when the next tile is 128 whole rows that run along the fastest loop index, its
           // inputs come as fp32 [input][row] into the park area by bulk copies, one 512-byte run per model input (the
