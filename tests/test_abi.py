@@ -73,3 +73,16 @@ def test_fortran_interface_module_names_exported_entries():
         assert hasattr(L, n), "libfortis_b200.so does not export %s" % n
     # subroutine / function ... end pairs balance (no Fortran compiler in this image: a structural check only)
     assert len(re.findall(r"^\s*(subroutine|function)\s", text, re.M)) == len(re.findall(r"^\s*end (subroutine|function)", text, re.M))
+
+
+def test_every_option_key_is_documented_in_a_header():
+    """fortis_set_option's keys, read off the source, all appear in the option lists of the headers under include/."""
+    src = open(os.path.join(ROOT, "fortis_b200", "csrc", "fortis_api.cu")).read()
+    body = src[src.index("int fortis_set_option("):]
+    body = body[:body.index("void fortis_reset(")]
+    keys = set(re.findall(r'k == "(\w+)"', body))
+    assert {"precision", "graph", "checksum", "host_access", "tc_pair"} <= keys
+    inc = os.path.join(ROOT, "include")
+    docs = "\n".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
+    missing = [k for k in sorted(keys) if '"%s"' % k not in docs]
+    assert not missing, "option keys without a line in include/*.h: %s" % missing
