@@ -26,7 +26,9 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) double g_noalloc_partials[kNoAllocSlots];
 
 // Device address of the array per device.  In host code the symbol's name is only a handle: the address a kernel
-// can use has to be asked for, once per device, with that device current.
+// can use has to be asked for, once per device, with that device current.  The address is cached per device ordinal
+// for the life of the process: a host that destroys the device's primary context (cudaDeviceReset) and goes on must
+// not call this entry again, the cached address would belong to the old context.
 double* g_scratch_addr[kMaxDevices] = {};
 
 __global__ void __launch_bounds__(256) noalloc_partial_kernel(const void* __restrict__ data, long n, int elt, double* __restrict__ partials) {
